@@ -1,0 +1,25 @@
+"""Shared pytest configuration: marker registration and import paths."""
+
+import os
+import sys
+
+import pytest
+
+REPO_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PACKAGE_ROOT = os.path.join(REPO_ROOT, "ml-flashpoint_b200")
+GOLDEN_DIR = os.path.join(REPO_ROOT, "tests", "golden")
+
+for _p in (REPO_ROOT, PACKAGE_ROOT, GOLDEN_DIR, os.path.join(REPO_ROOT, "oracle")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+os.environ.setdefault("MLFLASHPOINT_LOG_LEVEL", "WARNING")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture
+def golden_dir():
+    return GOLDEN_DIR
