@@ -1,0 +1,172 @@
+/*
+ * mlf_b200.h - C ABI of the B200 data path for ML Flashpoint checkpoint objects.
+ *
+ * One shared library (libmlf_b200.so) exports everything below with C linkage. Signatures use
+ * plain pointers and integer sizes only; CUDA handles (streams, events) cross as `void*` so a
+ * caller needs no CUDA headers. Every function that can fail returns an int32 status: 0 on
+ * success, a negative MLF_ERR_* otherwise, and records a human-readable message retrievable with
+ * mlf_last_error() on the same thread. No exception ever crosses this boundary.
+ *
+ * Each group names the interface of the reference implementation (google/ml-flashpoint, paths
+ * relative to src/ml_flashpoint/) that it stands in for.
+ */
+#ifndef MLF_B200_H_
+#define MLF_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status codes */
+#define MLF_OK 0
+#define MLF_ERR_INVALID (-1)     /* bad argument */
+#define MLF_ERR_IO (-2)          /* open/ftruncate/mmap/... failed; message carries errno text */
+#define MLF_ERR_CUDA (-3)        /* a CUDA runtime call failed; message carries its error string */
+#define MLF_ERR_BOUNDS (-4)      /* a descriptor would touch bytes outside the image window */
+#define MLF_ERR_CLOSED (-5)      /* operation on a closed buffer */
+#define MLF_ERR_EXISTS (-6)      /* create without overwrite found an existing file */
+#define MLF_ERR_TIMEOUT (-7)     /* a bounded device-side wait ran out; the context stays usable */
+#define MLF_ERR_TOO_LARGE (-8)   /* request exceeds a fixed capacity of the entry point */
+#define MLF_ERR_READONLY (-9)    /* write-type operation on a read-only mapping */
+
+/* Message for the last failure on the calling thread (never NULL). */
+const char* mlf_last_error(void);
+/* Library build tag, e.g. "mlf_b200 sm_100a". */
+const char* mlf_version(void);
+
+/* ------------------------------------------------------------------ buffer objects
+ * Replaces the pybind11 class `BufferObject`
+ * (checkpoint_object_manager/buffer_object/buffer_object.h:24-85, bindings.cpp:27-100;
+ * file handling in buffer_helper.cpp:43-314): a file mapped MAP_SHARED that backs one
+ * checkpoint object. Added here: the mapping can be page-locked and mapped into the CUDA
+ * address space so kernels and copy engines write checkpoint bytes into it directly. */
+typedef struct mlf_buf mlf_buf;
+
+/* BufferObject(object_id, capacity, overwrite): create (O_EXCL unless overwrite, then O_TRUNC),
+ * size with ftruncate and map read-write. Creates parent directories. capacity must be > 0. */
+int32_t mlf_buf_create(const char* object_id, uint64_t capacity, int32_t overwrite, mlf_buf** out);
+/* BufferObject(object_id): open an existing non-empty file read-only; capacity = file size. */
+int32_t mlf_buf_open_ro(const char* object_id, mlf_buf** out);
+/* resize(new_capacity): unmap, ftruncate, map again. The address may change. A CUDA registration
+ * is dropped first and re-established afterwards if one was active. */
+int32_t mlf_buf_resize(mlf_buf* b, uint64_t new_capacity);
+/* close(truncate_size): unmap, optionally ftruncate (truncate_size >= 0, writable only), close the
+ * descriptor. Idempotent; never fails hard (problems are reported through the status only). */
+int32_t mlf_buf_close(mlf_buf* b, int64_t truncate_size);
+/* Destructor: closes if needed and frees the handle. */
+void mlf_buf_destroy(mlf_buf* b);
+const char* mlf_buf_id(const mlf_buf* b);
+uint64_t mlf_buf_capacity(const mlf_buf* b); /* 0 once closed */
+void* mlf_buf_host_ptr(const mlf_buf* b);    /* NULL once closed */
+int32_t mlf_buf_is_closed(const mlf_buf* b);
+int32_t mlf_buf_is_readonly(const mlf_buf* b);
+/* Page-lock the mapping and map it for the current CUDA device (cudaHostRegister with the
+ * portable+mapped flags, plus read-only for RO mappings). Pages are touched first so that
+ * registration does not fault them in one by one. No-op if already registered. */
+int32_t mlf_buf_register(mlf_buf* b);
+int32_t mlf_buf_unregister(mlf_buf* b);
+int32_t mlf_buf_is_registered(const mlf_buf* b);
+/* Device-visible address of byte 0 of the mapping (requires registration). */
+int32_t mlf_buf_dev_ptr(const mlf_buf* b, void** out);
+
+/* ------------------------------------------------------------------ copy plans
+ * Replace the per-tensor host copies on the save and restore paths:
+ *   save    `_save_tensor_optimized`: header write + `dest.copy_(tensor)` into the mapping
+ *           (core/checkpoint_saver.py:764-800, loop at :667-698)
+ *   restore `read_tensor` + `narrow_tensor_by_index` + `target.copy_`
+ *           (core/checkpoint_loader.py:177-219, :331-336)
+ * A plan is a list of N-d box copies between tensors and one "image": the byte range of a
+ * checkpoint object (or its data section). It is built and uploaded once, then launched as ONE
+ * kernel per object as often as needed (the tensors of a training job keep their addresses). */
+#define MLF_MAX_DIMS 8
+
+#define MLF_PACK 0   /* tensors -> image */
+#define MLF_UNPACK 1 /* image -> tensors */
+
+typedef struct mlf_copy_desc {
+  uint64_t tensor_ptr;  /* device address of the tensor element with all indices 0 */
+  uint64_t image_off;   /* byte offset, in the image, of the box element with all indices 0;
+                           any byte alignment is allowed */
+  uint32_t elem_size;   /* bytes per element: 1, 2, 4, 8 or 16 */
+  uint32_t ndim;        /* 0..MLF_MAX_DIMS; 0 means a single element */
+  int64_t shape[MLF_MAX_DIMS];          /* extent of the box per dimension */
+  int64_t tensor_stride[MLF_MAX_DIMS];  /* in elements; any non-negative value (views, expands) */
+  int64_t image_stride[MLF_MAX_DIMS];   /* in elements; C order of the stored tensor */
+} mlf_copy_desc;
+
+typedef struct mlf_plan mlf_plan;
+
+/* Validates and canonicalises the descriptors (drops unit dims, merges mergeable ones, classifies
+ * each box as flat / rows / transposed / generic), cuts them into tiles and uploads the tables to
+ * the current device. `direction` is MLF_PACK or MLF_UNPACK. */
+int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t direction, mlf_plan** out);
+void mlf_plan_destroy(mlf_plan* p);
+/* One past the highest image byte any descriptor touches. */
+uint64_t mlf_plan_image_extent(const mlf_plan* p);
+/* Sum over descriptors of elements * elem_size. */
+uint64_t mlf_plan_payload_bytes(const mlf_plan* p);
+uint64_t mlf_plan_num_tiles(const mlf_plan* p);
+/* Launches the plan's single kernel on `stream` (a cudaStream_t; NULL = default stream).
+ * `image_base` is a device-visible address (HBM, or a registered host mapping) and
+ * `image_capacity` the bytes valid behind it: the launch is refused with MLF_ERR_BOUNDS if the
+ * plan's extent exceeds it. `max_ctas` limits the grid (0 = one wave sized from the SM count). */
+int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, void* stream, int32_t max_ctas);
+/* After the stream has been synchronised: 0, or the MLF_ERR_* a kernel recorded. Clears it. */
+int32_t mlf_plan_status(mlf_plan* p);
+/* Kernel launches issued by this library since load (for launch accounting in benchmarks). */
+uint64_t mlf_launch_count(void);
+
+/* ------------------------------------------------------------------ bulk movers
+ * Replace the byte movers around the object: the staging copy
+ * `tensor.to("cpu")` (adapter/pytorch/memory_storage_writer.py:211-233) and the replication
+ * transport `TransferService::AsyncPut` / `ExecutePutTask` / `HandleDataReceive`
+ * (replication/transfer_service/transfer_service.cpp:292-332, 632-690, 702-780) for peers that
+ * sit in the same NVLink domain. */
+#define MLF_COPY_D2H 0
+#define MLF_COPY_H2D 1
+#define MLF_COPY_D2D 2
+/* cudaMemcpyAsync on `stream` (copy-engine DMA). Host memory should be registered. */
+int32_t mlf_memcpy_async(void* dst, const void* src, uint64_t nbytes, int32_t kind, void* stream);
+/* Grid-sized 16-byte vector copy kernel between two device-visible addresses (own HBM, a peer
+ * GPU's memory opened through IPC or peer access, or registered host memory). Handles any
+ * alignment and size. Used for the NVLink replication hop and as the calibration copy. */
+int32_t mlf_copy_kernel_launch(void* dst, const void* src, uint64_t nbytes, void* stream, int32_t max_ctas);
+
+/* Device memory owned by the library (plain cudaMalloc so that IPC handles cover it). */
+int32_t mlf_dev_alloc(uint64_t nbytes, void** out);
+int32_t mlf_dev_free(void* p);
+/* Pinned host scratch (cudaHostAlloc), used for blobs and small uploads. */
+int32_t mlf_host_alloc(uint64_t nbytes, void** out);
+int32_t mlf_host_free(void* p);
+/* CUDA IPC: export an allocation made by mlf_dev_alloc / open one exported by another process. */
+#define MLF_IPC_HANDLE_BYTES 64
+int32_t mlf_ipc_export(void* dev_ptr, uint8_t handle_out[MLF_IPC_HANDLE_BYTES]);
+int32_t mlf_ipc_open(const uint8_t handle[MLF_IPC_HANDLE_BYTES], void** out);
+int32_t mlf_ipc_close(void* p);
+/* Enable direct access from the current device to `peer_device` (same process). */
+int32_t mlf_enable_peer_access(int32_t peer_device);
+
+/* ------------------------------------------------------------------ streams and events
+ * The "safe to mutate" signal of an overlapped save: record an event after the pack kernel and
+ * make the optimizer's stream wait on it. */
+int32_t mlf_set_device(int32_t device);
+int32_t mlf_get_device(int32_t* device);
+int32_t mlf_device_sm_count(int32_t* out);
+int32_t mlf_stream_create(void** out);
+int32_t mlf_stream_destroy(void* stream);
+int32_t mlf_stream_sync(void* stream);
+int32_t mlf_stream_wait_event(void* stream, void* event);
+int32_t mlf_event_create(void** out);
+int32_t mlf_event_destroy(void* event);
+int32_t mlf_event_record(void* event, void* stream);
+int32_t mlf_event_sync(void* event);
+/* 1 if complete, 0 if still pending, negative on error. */
+int32_t mlf_event_query(void* event);
+int32_t mlf_event_elapsed_ms(void* start, void* stop, float* ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLF_B200_H_ */

@@ -1,0 +1,289 @@
+// File-backed, CUDA-registrable buffer object behind the mlf_buf_* entry points.
+//
+// Behaviour follows the reference's BufferObject (checkpoint_object_manager/buffer_object/
+// buffer_object.cpp:25-198 with the file handling of buffer_helper.cpp:43-314): create with
+// O_EXCL or O_TRUNC + ftruncate + mmap(MAP_SHARED), read-only open sized by fstat, resize as
+// munmap/ftruncate/mmap, close with optional truncation. What is new is the page-locking
+// lifecycle: a mapping can be registered with CUDA so that the pack kernel and the copy engines
+// address it directly, and every operation that unmaps or shrinks the file drops the
+// registration first (pinned pages of a truncated tmpfs file would otherwise be orphaned).
+#include <errno.h>
+#include <fcntl.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "common.h"
+
+#ifndef MADV_POPULATE_READ
+#define MADV_POPULATE_READ 22
+#endif
+#ifndef MADV_POPULATE_WRITE
+#define MADV_POPULATE_WRITE 23
+#endif
+
+struct mlf_buf {
+  std::string id;
+  void* ptr = nullptr;
+  uint64_t capacity = 0;
+  int fd = -1;
+  bool readonly = false;
+  bool closed = true;
+  bool registered = false;
+};
+
+namespace {
+
+thread_local std::string t_error = "";
+
+int make_parent_dirs(const std::string& path) {
+  size_t slash = path.find_last_of('/');
+  if (slash == std::string::npos || slash == 0) return 0;
+  std::string dir = path.substr(0, slash);
+  for (size_t i = 1; i <= dir.size(); ++i) {
+    if (i == dir.size() || dir[i] == '/') {
+      std::string part = dir.substr(0, i);
+      if (mkdir(part.c_str(), 0777) != 0 && errno != EEXIST) return -1;
+    }
+  }
+  return 0;
+}
+
+// Faults every page of [p, p+n) in, several threads wide, so that page-locking afterwards does
+// not take the faults one at a time.
+void populate(void* p, uint64_t n, bool writable) {
+  const uint64_t kMinPerThread = 256ull << 20;
+  unsigned hw = std::thread::hardware_concurrency();
+  uint64_t want = n / kMinPerThread;
+  unsigned nthreads = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(want, std::min(hw ? hw : 1u, 16u)));
+  const long page = sysconf(_SC_PAGESIZE);
+  auto work = [=](uint64_t begin, uint64_t end) {
+    char* base = static_cast<char*>(p) + begin;
+    uint64_t len = end - begin;
+    if (madvise(base, len, writable ? MADV_POPULATE_WRITE : MADV_POPULATE_READ) == 0) return;
+    // Older kernels: touch one byte per page (a read is enough to instantiate a tmpfs page).
+    volatile char sink = 0;
+    for (uint64_t off = 0; off < len; off += page) sink += base[off];
+    (void)sink;
+  };
+  if (nthreads == 1) {
+    work(0, n);
+    return;
+  }
+  std::vector<std::thread> pool;
+  uint64_t per = ((n / nthreads) + page - 1) / page * page;
+  for (unsigned t = 0; t < nthreads; ++t) {
+    uint64_t b = std::min<uint64_t>(n, t * per), e = std::min<uint64_t>(n, (t + 1) * per);
+    if (t == nthreads - 1) e = n;
+    if (b < e) pool.emplace_back(work, b, e);
+  }
+  for (auto& th : pool) th.join();
+}
+
+int32_t drop_registration(mlf_buf* b) {
+  if (!b->registered) return MLF_OK;
+  cudaError_t e = cudaHostUnregister(b->ptr);
+  b->registered = false;
+  if (e != cudaSuccess) return mlf::cuda_fail(e, "cudaHostUnregister");
+  return MLF_OK;
+}
+
+int32_t do_register(mlf_buf* b) {
+  populate(b->ptr, b->capacity, !b->readonly);
+  unsigned flags = cudaHostRegisterPortable | cudaHostRegisterMapped;
+  if (b->readonly) flags |= cudaHostRegisterReadOnly;
+  cudaError_t e = cudaHostRegister(b->ptr, b->capacity, flags);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return mlf::cuda_fail(e, "cudaHostRegister");
+  }
+  b->registered = true;
+  return MLF_OK;
+}
+
+}  // namespace
+
+namespace mlf {
+std::atomic<uint64_t> g_launches{0};
+
+int32_t fail(int32_t code, const std::string& msg) {
+  t_error = msg;
+  return code;
+}
+int32_t fail_errno(int32_t code, const std::string& msg) {
+  t_error = msg + ": " + strerror(errno);
+  return code;
+}
+void clear_error() { t_error.clear(); }
+}  // namespace mlf
+
+extern "C" {
+
+const char* mlf_last_error(void) { return t_error.c_str(); }
+const char* mlf_version(void) { return "mlf_b200 sm_100a"; }
+uint64_t mlf_launch_count(void) { return mlf::g_launches.load(); }
+
+int32_t mlf_buf_create(const char* object_id, uint64_t capacity, int32_t overwrite, mlf_buf** out) {
+  if (!object_id || !out) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_create: null argument");
+  *out = nullptr;
+  if (capacity == 0)
+    return mlf::fail(MLF_ERR_INVALID, std::string("a buffer needs a capacity greater than 0: ") + object_id);
+  std::string id(object_id);
+  if (make_parent_dirs(id) != 0) return mlf::fail_errno(MLF_ERR_IO, "mkdir failed for parents of " + id);
+  int flags = O_CREAT | O_RDWR | O_CLOEXEC | (overwrite ? O_TRUNC : O_EXCL);
+  int fd = open(object_id, flags, 0666);
+  if (fd < 0) {
+    if (errno == EEXIST) return mlf::fail_errno(MLF_ERR_EXISTS, "open() failed, file exists and overwrite is off: " + id);
+    return mlf::fail_errno(MLF_ERR_IO, "open() failed for file: " + id);
+  }
+  if (ftruncate(fd, (off_t)capacity) != 0) {
+    int32_t rc = mlf::fail_errno(MLF_ERR_IO, "ftruncate() failed for file: " + id);
+    close(fd);
+    return rc;
+  }
+  void* p = mmap(nullptr, capacity, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (p == MAP_FAILED) {
+    int32_t rc = mlf::fail_errno(MLF_ERR_IO, "mmap() failed for file: " + id);
+    close(fd);
+    return rc;
+  }
+  mlf_buf* b = new mlf_buf();
+  b->id = id;
+  b->ptr = p;
+  b->capacity = capacity;
+  b->fd = fd;
+  b->readonly = false;
+  b->closed = false;
+  *out = b;
+  return MLF_OK;
+}
+
+int32_t mlf_buf_open_ro(const char* object_id, mlf_buf** out) {
+  if (!object_id || !out) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_open_ro: null argument");
+  *out = nullptr;
+  std::string id(object_id);
+  int fd = open(object_id, O_RDONLY | O_CLOEXEC);
+  if (fd < 0) return mlf::fail_errno(MLF_ERR_IO, "open() failed for file: " + id);
+  struct stat st;
+  if (fstat(fd, &st) != 0) {
+    int32_t rc = mlf::fail_errno(MLF_ERR_IO, "fstat() failed for file: " + id);
+    close(fd);
+    return rc;
+  }
+  if (!S_ISREG(st.st_mode)) {
+    close(fd);
+    return mlf::fail(MLF_ERR_IO, "not a regular file: " + id);
+  }
+  if (st.st_size == 0) {
+    close(fd);
+    return mlf::fail(MLF_ERR_INVALID, "file is empty, nothing to map: " + id);
+  }
+  void* p = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_SHARED, fd, 0);
+  if (p == MAP_FAILED) {
+    int32_t rc = mlf::fail_errno(MLF_ERR_IO, "mmap() failed for file: " + id);
+    close(fd);
+    return rc;
+  }
+  mlf_buf* b = new mlf_buf();
+  b->id = id;
+  b->ptr = p;
+  b->capacity = (uint64_t)st.st_size;
+  b->fd = fd;
+  b->readonly = true;
+  b->closed = false;
+  *out = b;
+  return MLF_OK;
+}
+
+int32_t mlf_buf_resize(mlf_buf* b, uint64_t new_capacity) {
+  if (!b) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_resize: null buffer");
+  if (b->closed) return mlf::fail(MLF_ERR_CLOSED, "cannot resize a closed buffer: " + b->id);
+  if (b->readonly) return mlf::fail(MLF_ERR_READONLY, "cannot resize a read-only buffer: " + b->id);
+  if (new_capacity == 0) return mlf::fail(MLF_ERR_INVALID, "cannot resize to 0 bytes: " + b->id);
+  if (new_capacity == b->capacity) return MLF_OK;
+  bool was_registered = b->registered;
+  int32_t rc = drop_registration(b);
+  if (rc != MLF_OK) return rc;
+  if (munmap(b->ptr, b->capacity) != 0) return mlf::fail_errno(MLF_ERR_IO, "munmap() failed during resize of " + b->id);
+  b->ptr = nullptr;
+  if (ftruncate(b->fd, (off_t)new_capacity) != 0) {
+    rc = mlf::fail_errno(MLF_ERR_IO, "ftruncate() failed during resize of " + b->id);
+    close(b->fd);
+    b->fd = -1;
+    b->capacity = 0;
+    b->closed = true;
+    return rc;
+  }
+  void* p = mmap(nullptr, new_capacity, PROT_READ | PROT_WRITE, MAP_SHARED, b->fd, 0);
+  if (p == MAP_FAILED) {
+    rc = mlf::fail_errno(MLF_ERR_IO, "mmap() failed during resize of " + b->id);
+    close(b->fd);
+    b->fd = -1;
+    b->capacity = 0;
+    b->closed = true;
+    return rc;
+  }
+  b->ptr = p;
+  b->capacity = new_capacity;
+  if (was_registered) return do_register(b);
+  return MLF_OK;
+}
+
+int32_t mlf_buf_close(mlf_buf* b, int64_t truncate_size) {
+  if (!b) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_close: null buffer");
+  if (b->closed) return MLF_OK;
+  int32_t rc = drop_registration(b);
+  if (b->ptr && munmap(b->ptr, b->capacity) != 0 && rc == MLF_OK)
+    rc = mlf::fail_errno(MLF_ERR_IO, "munmap() failed for " + b->id);
+  if (truncate_size >= 0 && !b->readonly && b->fd >= 0) {
+    if (ftruncate(b->fd, (off_t)truncate_size) != 0 && rc == MLF_OK)
+      rc = mlf::fail_errno(MLF_ERR_IO, "ftruncate() failed while closing " + b->id);
+  }
+  if (b->fd >= 0 && close(b->fd) != 0 && rc == MLF_OK) rc = mlf::fail_errno(MLF_ERR_IO, "close() failed for " + b->id);
+  b->ptr = nullptr;
+  b->capacity = 0;
+  b->fd = -1;
+  b->closed = true;
+  return rc;
+}
+
+void mlf_buf_destroy(mlf_buf* b) {
+  if (!b) return;
+  (void)mlf_buf_close(b, -1);
+  delete b;
+}
+
+const char* mlf_buf_id(const mlf_buf* b) { return b ? b->id.c_str() : ""; }
+uint64_t mlf_buf_capacity(const mlf_buf* b) { return (b && !b->closed) ? b->capacity : 0; }
+void* mlf_buf_host_ptr(const mlf_buf* b) { return (b && !b->closed) ? b->ptr : nullptr; }
+int32_t mlf_buf_is_closed(const mlf_buf* b) { return (!b || b->closed || b->fd < 0 || b->ptr == nullptr) ? 1 : 0; }
+int32_t mlf_buf_is_readonly(const mlf_buf* b) { return (b && b->readonly) ? 1 : 0; }
+int32_t mlf_buf_is_registered(const mlf_buf* b) { return (b && b->registered) ? 1 : 0; }
+
+int32_t mlf_buf_register(mlf_buf* b) {
+  if (!b) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_register: null buffer");
+  if (b->closed) return mlf::fail(MLF_ERR_CLOSED, "cannot register a closed buffer: " + b->id);
+  if (b->registered) return MLF_OK;
+  return do_register(b);
+}
+
+int32_t mlf_buf_unregister(mlf_buf* b) {
+  if (!b) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_unregister: null buffer");
+  return drop_registration(b);
+}
+
+int32_t mlf_buf_dev_ptr(const mlf_buf* b, void** out) {
+  if (!b || !out) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_dev_ptr: null argument");
+  *out = nullptr;
+  if (b->closed) return mlf::fail(MLF_ERR_CLOSED, "buffer is closed: " + b->id);
+  if (!b->registered) return mlf::fail(MLF_ERR_INVALID, "buffer is not registered with CUDA: " + b->id);
+  MLF_CUDA(cudaHostGetDevicePointer(out, b->ptr, 0));
+  return MLF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,35 @@
+// Shared helpers for the C-ABI translation units: thread-local error text and CUDA call checks.
+#ifndef MLF_COMMON_H_
+#define MLF_COMMON_H_
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+
+#include "mlf_b200.h"
+
+namespace mlf {
+
+// Stores `msg` for mlf_last_error() on this thread and returns `code`.
+int32_t fail(int32_t code, const std::string& msg);
+// errno-flavoured variant: appends ": <strerror(errno)>".
+int32_t fail_errno(int32_t code, const std::string& msg);
+void clear_error();
+
+extern std::atomic<uint64_t> g_launches;
+
+inline int32_t cuda_fail(cudaError_t e, const char* what) {
+  return fail(MLF_ERR_CUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+}  // namespace mlf
+
+#define MLF_CUDA(call)                                       \
+  do {                                                       \
+    cudaError_t _e = (call);                                 \
+    if (_e != cudaSuccess) return mlf::cuda_fail(_e, #call); \
+  } while (0)
+
+#endif  // MLF_COMMON_H_

@@ -1,0 +1,532 @@
+// Copy plans: the gather-pack (save) and scatter-unpack (restore) kernel and its host planner.
+//
+// A plan turns a list of N-d box copies between tensors and one checkpoint-object image into a
+// table of segments plus a tile index, uploads both once, and then runs as a single persistent
+// kernel per object: CTAs stride over the tiles, find the owning segment with a binary search
+// over the tile prefix, and move that tile. Four segment kinds exist:
+//   FLAT       both sides contiguous: 64 KiB byte runs, destination-aligned 16-byte vectors
+//   ROWS       innermost dimension contiguous on both sides: runs per row (or per row chunk)
+//   TRANSPOSE  the tensor's unit-stride dimension is not the image's: 64x64 element tiles through
+//              shared memory so both sides are touched along their contiguous direction
+//   GENERIC    anything else (stepped slices, expands): one element per thread
+// The image side has byte alignment only, because the object format is unpadded.
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "common.h"
+#include "copy_device.cuh"
+
+namespace {
+
+constexpr uint32_t kThreads = 256;
+constexpr uint64_t kTileBytes = 64 * 1024;    // FLAT tile and ROWS chunk
+constexpr uint64_t kRowSplitBytes = 16 * 1024;  // rows at least this long are cut into chunks
+constexpr int kTransTile = 64;                // TRANSPOSE tile edge, in elements
+constexpr uint64_t kGenericTile = 4096;       // GENERIC elements per tile
+
+enum SegKind : uint32_t { kFlat = 0, kRows = 1, kTranspose = 2, kGeneric = 3 };
+
+struct Seg {
+  uint64_t tensor;     // byte address of element 0
+  uint64_t image_off;  // byte offset of element 0 in the image
+  uint64_t a;          // FLAT: bytes | ROWS: row bytes | TRANSPOSE: tiles per batch | GENERIC: elements
+  uint32_t kind;
+  uint32_t esize;
+  uint32_t ndim;
+  uint32_t b;  // ROWS: rows per tile (0 = chunked rows) | TRANSPOSE: tiles along L
+  uint32_t c;  // ROWS: chunks per row                   | TRANSPOSE: index of dimension C
+  uint32_t image_aligned;  // 1 if every image element address is a multiple of esize
+  int64_t shape[MLF_MAX_DIMS];
+  int64_t tstride[MLF_MAX_DIMS];  // bytes
+  int64_t istride[MLF_MAX_DIMS];  // bytes
+};
+
+// ------------------------------------------------------------------------------------ device
+
+template <typename T>
+__device__ __forceinline__ T load_elem(const uint8_t* p, bool aligned) {
+  if (aligned) return *reinterpret_cast<const T*>(p);
+  T v;
+  uint8_t* b = reinterpret_cast<uint8_t*>(&v);
+#pragma unroll
+  for (int k = 0; k < (int)sizeof(T); ++k) b[k] = p[k];
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ void store_elem(uint8_t* p, T v, bool aligned) {
+  if (aligned) {
+    *reinterpret_cast<T*>(p) = v;
+    return;
+  }
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(&v);
+#pragma unroll
+  for (int k = 0; k < (int)sizeof(T); ++k) p[k] = b[k];
+}
+
+// One 64x64 element tile of a TRANSPOSE segment, as four 32x32 blocks through shared memory.
+// Dimension C is contiguous in the tensor, dimension L (the last) is contiguous in the image.
+template <typename T, int DIR>
+__device__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem_raw) {
+  T(*tile)[33] = reinterpret_cast<T(*)[33]>(smem_raw);
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransTile;
+  const int64_t l0 = (int64_t)(in_batch % g.b) * kTransTile;
+  int64_t toff = 0, ioff = 0;
+  for (int d = L - 1; d >= 0; --d) {
+    if (d == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[d]);
+    batch /= (uint64_t)g.shape[d];
+    toff += idx * g.tstride[d];
+    ioff += idx * g.istride[d];
+  }
+  const uint8_t* tbase_c = reinterpret_cast<const uint8_t*>(g.tensor) + toff;
+  uint8_t* tbase = reinterpret_cast<uint8_t*>(g.tensor) + toff;
+  uint8_t* ibase = image + g.image_off + ioff;
+  const int64_t nC = g.shape[C], nL = g.shape[L];
+  const int64_t tsL = g.tstride[L], isC = g.istride[C];
+  const bool ial = g.image_aligned != 0;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int sub = 0; sub < 4; ++sub) {
+    const int64_t cb = c0 + (sub >> 1) * 32, lb = l0 + (sub & 1) * 32;
+    if (cb >= nC || lb >= nL) continue;  // uniform across the CTA
+    if (DIR == MLF_PACK) {
+      for (int j = ty; j < 32; j += 8) {
+        const int64_t l = lb + j, c = cb + tx;
+        if (l < nL && c < nC) tile[j][tx] = *reinterpret_cast<const T*>(tbase_c + c * (int64_t)sizeof(T) + l * tsL);
+      }
+      __syncthreads();
+      for (int j = ty; j < 32; j += 8) {
+        const int64_t c = cb + j, l = lb + tx;
+        if (l < nL && c < nC) store_elem<T>(ibase + c * isC + l * (int64_t)sizeof(T), tile[tx][j], ial);
+      }
+    } else {
+      for (int j = ty; j < 32; j += 8) {
+        const int64_t c = cb + j, l = lb + tx;
+        if (l < nL && c < nC) tile[tx][j] = load_elem<T>(ibase + c * isC + l * (int64_t)sizeof(T), ial);
+      }
+      __syncthreads();
+      for (int j = ty; j < 32; j += 8) {
+        const int64_t l = lb + j, c = cb + tx;
+        if (l < nL && c < nC) *reinterpret_cast<T*>(tbase + c * (int64_t)sizeof(T) + l * tsL) = tile[j][tx];
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int DIR>
+__device__ void generic_tile(const Seg& g, uint32_t local, uint8_t* image) {
+  const uint64_t first = (uint64_t)local * kGenericTile;
+  const uint64_t last = min(first + kGenericTile, g.a);
+  const bool ial = g.image_aligned != 0;
+  for (uint64_t e = first + threadIdx.x; e < last; e += blockDim.x) {
+    uint64_t r = e;
+    int64_t toff = 0, ioff = 0;
+    for (int d = (int)g.ndim - 1; d >= 0; --d) {
+      const int64_t idx = (int64_t)(r % (uint64_t)g.shape[d]);
+      r /= (uint64_t)g.shape[d];
+      toff += idx * g.tstride[d];
+      ioff += idx * g.istride[d];
+    }
+    uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + toff;
+    uint8_t* ip = image + g.image_off + ioff;
+    if (DIR == MLF_PACK)
+      store_elem<T>(ip, *reinterpret_cast<const T*>(tp), ial);
+    else
+      *reinterpret_cast<T*>(tp) = load_elem<T>(ip, ial);
+  }
+}
+
+template <int DIR>
+__device__ __forceinline__ void rows_tile(const Seg& g, uint32_t local, uint8_t* image) {
+  const int outer = (int)g.ndim - 1;
+  if (g.b == 0) {
+    // long rows: this tile is one chunk of one row, moved by the whole CTA
+    uint64_t row = local / g.c;
+    const uint64_t chunk = local % g.c;
+    int64_t toff = 0, ioff = 0;
+    for (int d = outer - 1; d >= 0; --d) {
+      const int64_t idx = (int64_t)(row % (uint64_t)g.shape[d]);
+      row /= (uint64_t)g.shape[d];
+      toff += idx * g.tstride[d];
+      ioff += idx * g.istride[d];
+    }
+    const uint64_t off = chunk * kTileBytes;
+    const uint64_t len = min(kTileBytes, g.a - off);
+    uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + toff + off;
+    uint8_t* ip = image + g.image_off + ioff + off;
+    if (DIR == MLF_PACK)
+      mlf::copy_bytes(ip, tp, len, threadIdx.x, blockDim.x);
+    else
+      mlf::copy_bytes(tp, ip, len, threadIdx.x, blockDim.x);
+    return;
+  }
+  // short rows: a warp per row
+  uint64_t nrows = 1;
+  for (int d = 0; d < outer; ++d) nrows *= (uint64_t)g.shape[d];
+  const uint64_t r0 = (uint64_t)local * g.b;
+  const uint64_t r1 = min(r0 + g.b, nrows);
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (uint64_t r = r0 + warp; r < r1; r += nwarps) {
+    uint64_t row = r;
+    int64_t toff = 0, ioff = 0;
+    for (int d = outer - 1; d >= 0; --d) {
+      const int64_t idx = (int64_t)(row % (uint64_t)g.shape[d]);
+      row /= (uint64_t)g.shape[d];
+      toff += idx * g.tstride[d];
+      ioff += idx * g.istride[d];
+    }
+    uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + toff;
+    uint8_t* ip = image + g.image_off + ioff;
+    if (DIR == MLF_PACK)
+      mlf::copy_bytes(ip, tp, g.a, lane, 32);
+    else
+      mlf::copy_bytes(tp, ip, g.a, lane, 32);
+  }
+}
+
+template <int DIR>
+__global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restrict__ segs,
+                                                            const uint32_t* __restrict__ tile_begin, uint32_t nseg,
+                                                            uint32_t ntiles, uint8_t* __restrict__ image) {
+  __shared__ __align__(16) uint8_t smem[32 * 33 * 8];
+  __shared__ Seg g;
+  uint32_t cached = 0xffffffffu;
+  for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    uint32_t lo = 0, hi = nseg;
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (tile_begin[mid] <= tile)
+        lo = mid;
+      else
+        hi = mid;
+    }
+    if (lo != cached) {  // uniform: every thread ran the same search
+      __syncthreads();
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + lo);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
+      for (uint32_t w = threadIdx.x; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
+      __syncthreads();
+      cached = lo;
+    }
+    const uint32_t local = tile - tile_begin[lo];
+    switch (g.kind) {
+      case kFlat: {
+        const uint64_t off = (uint64_t)local * kTileBytes;
+        const uint64_t len = min(kTileBytes, g.a - off);
+        uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + off;
+        uint8_t* ip = image + g.image_off + off;
+        if (DIR == MLF_PACK)
+          mlf::copy_bytes(ip, tp, len, threadIdx.x, blockDim.x);
+        else
+          mlf::copy_bytes(tp, ip, len, threadIdx.x, blockDim.x);
+        break;
+      }
+      case kRows:
+        rows_tile<DIR>(g, local, image);
+        break;
+      case kTranspose:
+        switch (g.esize) {
+          case 1: transpose_tile<uint8_t, DIR>(g, local, image, smem); break;
+          case 2: transpose_tile<uint16_t, DIR>(g, local, image, smem); break;
+          case 4: transpose_tile<uint32_t, DIR>(g, local, image, smem); break;
+          default: transpose_tile<uint64_t, DIR>(g, local, image, smem); break;
+        }
+        break;
+      default:
+        switch (g.esize) {
+          case 1: generic_tile<uint8_t, DIR>(g, local, image); break;
+          case 2: generic_tile<uint16_t, DIR>(g, local, image); break;
+          case 4: generic_tile<uint32_t, DIR>(g, local, image); break;
+          default: generic_tile<uint64_t, DIR>(g, local, image); break;
+        }
+        break;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
+                                                                 const uint8_t* __restrict__ src, uint64_t nbytes) {
+  const uint64_t ntiles = (nbytes + kTileBytes - 1) / kTileBytes;
+  for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t off = t * kTileBytes;
+    mlf::copy_bytes(dst + off, src + off, min(kTileBytes, nbytes - off), threadIdx.x, blockDim.x);
+  }
+}
+
+// ------------------------------------------------------------------------------------ host
+
+// Grid for a persistent launch of `kernel`: one full wave (SMs x resident CTAs per SM), capped by
+// the tile count and by the caller's limit.
+template <typename K>
+int32_t wave_grid(K kernel, int32_t max_ctas, uint64_t ntiles, uint32_t* grid) {
+  int dev = 0, sms = 0, per_sm = 0;
+  MLF_CUDA(cudaGetDevice(&dev));
+  MLF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  MLF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int)kThreads, 0));
+  uint64_t g = (uint64_t)sms * (uint64_t)std::max(per_sm, 1);
+  if (max_ctas > 0) g = std::min<uint64_t>(g, (uint64_t)max_ctas);
+  g = std::max<uint64_t>(1, std::min<uint64_t>(g, ntiles));
+  *grid = (uint32_t)g;
+  return MLF_OK;
+}
+
+// Canonical form of one descriptor: unit dims dropped, mergeable neighbours merged, strides in bytes.
+struct Canon {
+  int ndim = 0;
+  int64_t shape[MLF_MAX_DIMS + 1];
+  int64_t ts[MLF_MAX_DIMS + 1];
+  int64_t is[MLF_MAX_DIMS + 1];
+};
+
+Canon canonicalise(uint32_t esize, const int64_t* shape, const int64_t* ts_elems, const int64_t* is_elems, int ndim) {
+  Canon c;
+  for (int k = 0; k < ndim; ++k) {
+    if (shape[k] == 1) continue;
+    const int64_t ts = ts_elems[k] * (int64_t)esize, is = is_elems[k] * (int64_t)esize;
+    if (c.ndim > 0 && c.ts[c.ndim - 1] == ts * shape[k] && c.is[c.ndim - 1] == is * shape[k]) {
+      c.shape[c.ndim - 1] *= shape[k];
+      c.ts[c.ndim - 1] = ts;
+      c.is[c.ndim - 1] = is;
+    } else {
+      c.shape[c.ndim] = shape[k];
+      c.ts[c.ndim] = ts;
+      c.is[c.ndim] = is;
+      ++c.ndim;
+    }
+  }
+  return c;
+}
+
+}  // namespace
+
+struct mlf_plan {
+  int direction = MLF_PACK;
+  int device = 0;
+  uint32_t nseg = 0;
+  uint32_t ntiles = 0;
+  uint64_t extent = 0;
+  uint64_t payload = 0;
+  Seg* d_segs = nullptr;
+  uint32_t* d_tile_begin = nullptr;
+  int32_t* d_status = nullptr;
+};
+
+extern "C" {
+
+int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t direction, mlf_plan** out) {
+  if (!out) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: null out");
+  *out = nullptr;
+  if (n > 0 && !descs) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: null descriptors");
+  if (direction != MLF_PACK && direction != MLF_UNPACK)
+    return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: direction must be MLF_PACK or MLF_UNPACK");
+
+  std::vector<Seg> segs;
+  std::vector<uint32_t> tile_begin;
+  segs.reserve(n);
+  tile_begin.reserve(n + 1);
+  uint64_t tiles = 0, extent = 0, payload = 0;
+
+  for (uint64_t i = 0; i < n; ++i) {
+    const mlf_copy_desc& d = descs[i];
+    const std::string where = "descriptor " + std::to_string(i);
+    if (d.ndim > MLF_MAX_DIMS) return mlf::fail(MLF_ERR_INVALID, where + ": ndim exceeds MLF_MAX_DIMS");
+    if (d.elem_size != 1 && d.elem_size != 2 && d.elem_size != 4 && d.elem_size != 8 && d.elem_size != 16)
+      return mlf::fail(MLF_ERR_INVALID, where + ": elem_size must be 1, 2, 4, 8 or 16");
+    uint64_t numel = 1;
+    uint64_t span = 0;  // highest element index touched on the image side
+    for (uint32_t k = 0; k < d.ndim; ++k) {
+      if (d.shape[k] < 0 || d.tensor_stride[k] < 0 || d.image_stride[k] < 0)
+        return mlf::fail(MLF_ERR_INVALID, where + ": negative extent or stride");
+      numel *= (uint64_t)d.shape[k];
+      if (d.shape[k] > 0) span += (uint64_t)(d.shape[k] - 1) * (uint64_t)d.image_stride[k];
+    }
+    if (numel == 0) continue;  // nothing to move; the format stores no payload for it either
+    if (d.tensor_ptr == 0) return mlf::fail(MLF_ERR_INVALID, where + ": null tensor pointer");
+    payload += numel * d.elem_size;
+    extent = std::max(extent, d.image_off + (span + 1) * d.elem_size);
+
+    // 16-byte elements are moved as pairs of 8-byte halves (an extra innermost dimension of 2)
+    int64_t shp[MLF_MAX_DIMS + 1], ts[MLF_MAX_DIMS + 1], is[MLF_MAX_DIMS + 1];
+    int nd = (int)d.ndim;
+    uint32_t esize = d.elem_size;
+    for (int k = 0; k < nd; ++k) {
+      shp[k] = d.shape[k];
+      ts[k] = d.tensor_stride[k];
+      is[k] = d.image_stride[k];
+    }
+    if (esize == 16) {
+      for (int k = 0; k < nd; ++k) {
+        ts[k] *= 2;
+        is[k] *= 2;
+      }
+      shp[nd] = 2;
+      ts[nd] = 1;
+      is[nd] = 1;
+      ++nd;
+      esize = 8;
+    }
+    const Canon c = canonicalise(esize, shp, ts, is, nd);
+    if (c.ndim > MLF_MAX_DIMS)
+      return mlf::fail(MLF_ERR_INVALID, where + ": too many dimensions after splitting 16-byte elements");
+
+    Seg g;
+    memset(&g, 0, sizeof(g));
+    g.tensor = d.tensor_ptr;
+    g.image_off = d.image_off;
+    g.esize = esize;
+    g.ndim = (uint32_t)c.ndim;
+    bool aligned = (d.image_off % esize) == 0;
+    for (int k = 0; k < c.ndim; ++k) {
+      g.shape[k] = c.shape[k];
+      g.tstride[k] = c.ts[k];
+      g.istride[k] = c.is[k];
+      if (c.is[k] % esize) aligned = false;
+    }
+    g.image_aligned = aligned ? 1u : 0u;
+    if ((d.tensor_ptr % esize) != 0)
+      return mlf::fail(MLF_ERR_INVALID, where + ": tensor pointer is not aligned to its element size");
+
+    const int last = c.ndim - 1;
+    const bool inner_contig = c.ndim == 0 || (c.ts[last] == (int64_t)esize && c.is[last] == (int64_t)esize);
+    uint64_t ntile = 0;
+    if (c.ndim == 0 || (c.ndim == 1 && inner_contig)) {
+      g.kind = kFlat;
+      g.a = numel * d.elem_size;
+      ntile = (g.a + kTileBytes - 1) / kTileBytes;
+    } else if (inner_contig) {
+      g.kind = kRows;
+      g.a = (uint64_t)c.shape[last] * esize;
+      uint64_t nrows = 1;
+      for (int k = 0; k < last; ++k) nrows *= (uint64_t)c.shape[k];
+      if (g.a >= kRowSplitBytes) {
+        g.b = 0;
+        g.c = (uint32_t)((g.a + kTileBytes - 1) / kTileBytes);
+        ntile = nrows * g.c;
+      } else {
+        g.b = (uint32_t)std::max<uint64_t>(1, kTileBytes / g.a);
+        ntile = (nrows + g.b - 1) / g.b;
+      }
+    } else {
+      int cdim = -1;
+      if (c.is[last] == (int64_t)esize)
+        for (int k = 0; k < last; ++k)
+          if (c.ts[k] == (int64_t)esize) cdim = k;
+      if (cdim >= 0) {
+        g.kind = kTranspose;
+        g.c = (uint32_t)cdim;
+        const uint64_t tc = ((uint64_t)c.shape[cdim] + kTransTile - 1) / kTransTile;
+        const uint64_t tl = ((uint64_t)c.shape[last] + kTransTile - 1) / kTransTile;
+        g.b = (uint32_t)tl;
+        g.a = tc * tl;
+        uint64_t batch = 1;
+        for (int k = 0; k < last; ++k)
+          if (k != cdim) batch *= (uint64_t)c.shape[k];
+        ntile = batch * g.a;
+        if (g.a > 0xffffffffull) return mlf::fail(MLF_ERR_TOO_LARGE, where + ": transposed box too large");
+      } else {
+        g.kind = kGeneric;
+        g.a = numel * (d.elem_size / esize);
+        ntile = (g.a + kGenericTile - 1) / kGenericTile;
+      }
+    }
+    if (tiles + ntile > 0xfffffff0ull) return mlf::fail(MLF_ERR_TOO_LARGE, "plan has too many tiles");
+    tile_begin.push_back((uint32_t)tiles);
+    segs.push_back(g);
+    tiles += ntile;
+  }
+  tile_begin.push_back((uint32_t)tiles);
+
+  mlf_plan* p = new mlf_plan();
+  p->direction = direction;
+  p->nseg = (uint32_t)segs.size();
+  p->ntiles = (uint32_t)tiles;
+  p->extent = extent;
+  p->payload = payload;
+  cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess && p->nseg > 0) {
+    e = cudaMalloc(&p->d_segs, segs.size() * sizeof(Seg));
+    if (e == cudaSuccess) e = cudaMalloc(&p->d_tile_begin, tile_begin.size() * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&p->d_status, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemcpy(p->d_segs, segs.data(), segs.size() * sizeof(Seg), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess)
+      e = cudaMemcpy(p->d_tile_begin, tile_begin.data(), tile_begin.size() * sizeof(uint32_t), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(p->d_status, 0, sizeof(int32_t));
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    mlf_plan_destroy(p);
+    return mlf::cuda_fail(e, "uploading the plan tables");
+  }
+  *out = p;
+  return MLF_OK;
+}
+
+void mlf_plan_destroy(mlf_plan* p) {
+  if (!p) return;
+  if (p->d_segs) cudaFree(p->d_segs);
+  if (p->d_tile_begin) cudaFree(p->d_tile_begin);
+  if (p->d_status) cudaFree(p->d_status);
+  delete p;
+}
+
+uint64_t mlf_plan_image_extent(const mlf_plan* p) { return p ? p->extent : 0; }
+uint64_t mlf_plan_payload_bytes(const mlf_plan* p) { return p ? p->payload : 0; }
+uint64_t mlf_plan_num_tiles(const mlf_plan* p) { return p ? p->ntiles : 0; }
+
+int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, void* stream, int32_t max_ctas) {
+  if (!p) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_launch: null plan");
+  if (p->extent > image_capacity)
+    return mlf::fail(MLF_ERR_BOUNDS, "plan touches " + std::to_string(p->extent) + " image bytes but only " +
+                                         std::to_string(image_capacity) + " are available");
+  if (p->ntiles == 0) return MLF_OK;
+  if (!image_base) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_launch: null image");
+  uint32_t grid = 1;
+  int32_t rc = p->direction == MLF_PACK ? wave_grid(mlf_plan_kernel<MLF_PACK>, max_ctas, p->ntiles, &grid)
+                                        : wave_grid(mlf_plan_kernel<MLF_UNPACK>, max_ctas, p->ntiles, &grid);
+  if (rc != MLF_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p->direction == MLF_PACK)
+    mlf_plan_kernel<MLF_PACK><<<grid, kThreads, 0, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles,
+                                                        static_cast<uint8_t*>(image_base));
+  else
+    mlf_plan_kernel<MLF_UNPACK><<<grid, kThreads, 0, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles,
+                                                          static_cast<uint8_t*>(image_base));
+  MLF_CUDA(cudaGetLastError());
+  mlf::g_launches.fetch_add(1);
+  return MLF_OK;
+}
+
+int32_t mlf_plan_status(mlf_plan* p) {
+  if (!p) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_status: null plan");
+  if (!p->d_status) return MLF_OK;
+  int32_t v = 0;
+  MLF_CUDA(cudaMemcpy(&v, p->d_status, sizeof(v), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    MLF_CUDA(cudaMemset(p->d_status, 0, sizeof(v)));
+    return mlf::fail(v, "a plan kernel recorded status " + std::to_string(v));
+  }
+  return MLF_OK;
+}
+
+int32_t mlf_copy_kernel_launch(void* dst, const void* src, uint64_t nbytes, void* stream, int32_t max_ctas) {
+  if (nbytes == 0) return MLF_OK;
+  if (!dst || !src) return mlf::fail(MLF_ERR_INVALID, "mlf_copy_kernel_launch: null pointer");
+  uint32_t grid = 1;
+  int32_t rc = wave_grid(mlf_flat_copy_kernel, max_ctas, (nbytes + kTileBytes - 1) / kTileBytes, &grid);
+  if (rc != MLF_OK) return rc;
+  mlf_flat_copy_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nbytes);
+  MLF_CUDA(cudaGetLastError());
+  mlf::g_launches.fetch_add(1);
+  return MLF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,476 @@
+"""GPU data mover for checkpoint objects: layout planning plus the CUDA pack / unpack engine.
+
+Two halves:
+
+* ``plan_object_layout`` is pure host arithmetic. It reproduces the byte layout the reference
+  saver produces for one object (core/checkpoint_saver.py:667-698 with ``_save_tensor_optimized``
+  :764-800): every tensor in bucket order as ``[u32 len][pickled TensorHeader][C-order bytes]``,
+  then every BYTE_IO item, no padding. It yields the storage records and, per tensor, the box-copy
+  descriptor the kernel needs. It touches no CUDA API.
+
+* ``CudaCopyEngine`` executes layouts. Save: ONE gather-pack kernel per object reads all tensors
+  (any strides) plus a pinned blob holding headers and byte items and writes the finished data
+  section, either straight into the page-locked object mapping ("direct") or into an HBM image
+  that a copy engine then drains to the mapping ("staged", the default: training may resume as
+  soon as the kernel is done, a few milliseconds, while the PCIe transfer continues).
+  Restore: the mirror scatter-unpack kernel, fed from an HBM copy of the needed image range.
+
+There is no CPU data path: without the native library or a CUDA device the engine raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import threading
+from collections import OrderedDict
+from typing import Any, List, Optional, Sequence, Tuple
+
+import torch
+
+from ml_flashpoint import _native
+from ml_flashpoint.core.mlf_logging import get_logger
+from ml_flashpoint.core.tensor_header import TensorHeader
+from ml_flashpoint.core.utils import get_env_val_int, get_env_val_str
+
+_LOGGER = get_logger(__name__)
+
+MAX_DIMS = _native.MLF_MAX_DIMS
+
+
+# ======================================================================================
+# Layout planning (host only)
+# ======================================================================================
+@dataclasses.dataclass
+class LayoutRecord:
+    """Where one item landed: the fields of the ``_StorageInfo`` / ``WriteResult`` for it."""
+
+    item: Any  # the WriteItem (or any caller token)
+    offset: int  # relative to the start of the data section
+    length: int  # header + payload for tensors, byte count for blobs
+
+
+@dataclasses.dataclass
+class TensorPlacement:
+    tensor: torch.Tensor
+    payload_offset: int  # data-section offset of the first payload byte
+
+
+@dataclasses.dataclass
+class HostChunk:
+    offset: int  # data-section offset
+    data: bytes
+
+
+@dataclasses.dataclass
+class ObjectLayout:
+    total_bytes: int
+    records: List[LayoutRecord]
+    tensors: List[TensorPlacement]
+    host_chunks: List[HostChunk]
+    payload_bytes: int
+
+    def host_blob_size(self) -> int:
+        return sum(len(c.data) for c in self.host_chunks)
+
+
+def plan_object_layout(
+    tensor_items: Sequence[Tuple[Any, torch.Tensor]],
+    bytes_items: Sequence[Tuple[Any, Any]],
+    start_offset: int = 0,
+) -> ObjectLayout:
+    """Lays out one object's data section: tensors first (bucket order), then byte items.
+
+    ``bytes_items`` values are ``io.BytesIO``-likes (read from position 0) or ``bytes``.
+    Zero-element tensors get a header and no payload, as in the reference (:789).
+    """
+    pos = start_offset
+    records: List[LayoutRecord] = []
+    placements: List[TensorPlacement] = []
+    chunks: List[HostChunk] = []
+    payload_total = 0
+    for item, tensor in tensor_items:
+        begin = pos
+        header = TensorHeader(dtype=tensor.dtype, shape=tensor.shape).to_bytes()
+        chunks.append(HostChunk(pos, header))
+        pos += len(header)
+        nbytes = tensor.numel() * tensor.element_size()
+        if nbytes:
+            placements.append(TensorPlacement(tensor, pos))
+            pos += nbytes
+            payload_total += nbytes
+        records.append(LayoutRecord(item, begin, pos - begin))
+    for item, blob in bytes_items:
+        if hasattr(blob, "seek"):
+            blob.seek(0)
+            data = blob.read()
+        else:
+            data = bytes(blob)
+        if data:
+            chunks.append(HostChunk(pos, data))
+        records.append(LayoutRecord(item, pos, len(data)))
+        pos += len(data)
+    return ObjectLayout(pos - start_offset, records, placements, chunks, payload_total)
+
+
+def c_strides(shape: Sequence[int]) -> List[int]:
+    out = [1] * len(shape)
+    for d in range(len(shape) - 2, -1, -1):
+        out[d] = out[d + 1] * max(int(shape[d + 1]), 1)
+    return out
+
+
+def fill_desc(
+    desc: _native.CopyDesc,
+    tensor_ptr: int,
+    image_off: int,
+    elem_size: int,
+    shape: Sequence[int],
+    tensor_stride: Sequence[int],
+    image_stride: Sequence[int],
+) -> None:
+    if len(shape) > MAX_DIMS:
+        raise ValueError(f"tensors with more than {MAX_DIMS} dimensions are not supported, got {len(shape)}")
+    desc.tensor_ptr = tensor_ptr
+    desc.image_off = image_off
+    desc.elem_size = elem_size
+    desc.ndim = len(shape)
+    for d in range(len(shape)):
+        desc.shape[d] = int(shape[d])
+        desc.tensor_stride[d] = int(tensor_stride[d])
+        desc.image_stride[d] = int(image_stride[d])
+
+
+# ======================================================================================
+# CUDA engine
+# ======================================================================================
+class _PinnedBlob:
+    """Page-locked, device-mapped host scratch for headers and byte items (kernel reads it in place)."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = max(nbytes, 1)
+        ptr = ctypes.c_void_p()
+        _native.check(_native.lib().mlf_host_alloc(self.nbytes, ctypes.byref(ptr)))
+        self.ptr = int(ptr.value)
+
+    def fill(self, chunks: Sequence[HostChunk]) -> None:
+        at = self.ptr
+        for c in chunks:
+            ctypes.memmove(at, c.data, len(c.data))
+            at += len(c.data)
+
+    def __del__(self):
+        try:
+            _native.lib().mlf_host_free(ctypes.c_void_p(self.ptr))
+        except Exception:
+            pass
+
+
+class _Plan:
+    def __init__(self, descs, n: int, direction: int):
+        handle = ctypes.c_void_p()
+        _native.check(_native.lib().mlf_plan_create(descs, n, direction, ctypes.byref(handle)))
+        self.handle = handle
+        self.extent = int(_native.lib().mlf_plan_image_extent(handle))
+        self.payload = int(_native.lib().mlf_plan_payload_bytes(handle))
+
+    def launch(self, image_base: int, capacity: int, stream: int, max_ctas: int = 0) -> None:
+        _native.check(
+            _native.lib().mlf_plan_launch(
+                self.handle, ctypes.c_void_p(image_base), capacity, ctypes.c_void_p(stream), max_ctas
+            )
+        )
+
+    def status(self) -> None:
+        _native.check(_native.lib().mlf_plan_status(self.handle))
+
+    def __del__(self):
+        try:
+            _native.lib().mlf_plan_destroy(self.handle)
+        except Exception:
+            pass
+
+
+@dataclasses.dataclass
+class _CachedPack:
+    plan: _Plan
+    blob: _PinnedBlob
+    keepalive: list  # device copies of CPU tensors referenced by the plan
+
+
+class PackTicket:
+    """Handle of an in-flight save of one object.
+
+    ``mutate_event`` fires when the pack kernel has read every source tensor: from then on the
+    training loop may overwrite parameters and optimizer state. ``done_event`` fires when the last
+    byte has reached the object mapping. ``wait()`` blocks on the latter and surfaces kernel status.
+    """
+
+    def __init__(self, engine: "CudaCopyEngine", cached: _CachedPack, mutate_event, done_event, nbytes: int):
+        self._engine = engine
+        self._cached = cached
+        self.mutate_event = mutate_event
+        self.done_event = done_event
+        self.nbytes = nbytes
+
+    def wait(self) -> None:
+        self.done_event.synchronize()
+        self._cached.plan.status()
+
+
+class CudaCopyEngine:
+    """Runs pack and unpack plans on one CUDA device.
+
+    ``mode`` is ``"staged"`` (kernel writes an HBM image, a copy engine moves it to the object
+    mapping) or ``"direct"`` (kernel writes the page-locked mapping itself). Environment override:
+    ``MLFLASHPOINT_GPU_PACK_MODE``. ``host_ctas`` bounds the grid of kernels that write to or read
+    from host memory, where a handful of CTAs saturate the link (``MLFLASHPOINT_GPU_HOST_CTAS``).
+    """
+
+    def __init__(self, device: Optional[torch.device] = None, mode: Optional[str] = None, plan_cache_size: int = 8):
+        _native.lib()  # fail here, loudly, if the native library is absent
+        if not torch.cuda.is_available():
+            raise RuntimeError(
+                "CudaCopyEngine needs a CUDA device: checkpoint bytes are moved by CUDA kernels and there is "
+                "no CPU data path in this package."
+            )
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.mode = (mode or get_env_val_str("GPU_PACK_MODE", "staged")).lower()
+        if self.mode not in ("staged", "direct"):
+            raise ValueError(f"unknown pack mode '{self.mode}' (expected 'staged' or 'direct')")
+        self.host_ctas = get_env_val_int("GPU_HOST_CTAS", 32)
+        self._lock = threading.RLock()
+        self._cache: "OrderedDict[tuple, _CachedPack]" = OrderedDict()
+        self._cache_size = plan_cache_size
+        self._staging: Optional[torch.Tensor] = None
+        self._last_mutate: Optional[torch.cuda.Event] = None  # last kernel that read a pinned blob
+        self._last_done: Optional[torch.cuda.Event] = None  # last transfer that read the HBM image
+        self._resident: Optional[tuple] = None  # (object id, image tensor, nbytes, done event) of the last staged save
+        with torch.cuda.device(self.device):
+            self._bind()
+            self.pack_stream = torch.cuda.Stream(device=self.device)
+            self.copy_stream = torch.cuda.Stream(device=self.device)
+
+    # ------------------------------------------------------------------ helpers
+    def _bind(self) -> None:
+        _native.check(_native.lib().mlf_set_device(self.device.index))
+
+    def staging(self, nbytes: int) -> torch.Tensor:
+        """HBM image buffer of at least ``nbytes`` (grown geometrically, reused across saves)."""
+        if self._staging is None or self._staging.numel() < nbytes:
+            self._staging = None
+            grown = max(nbytes, 1 << 20)
+            self._staging = torch.empty(grown, dtype=torch.uint8, device=self.device)
+        return self._staging
+
+    @staticmethod
+    def _tensor_key(t: torch.Tensor) -> tuple:
+        return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, t.device.type)
+
+    def _build_pack(self, layout: ObjectLayout) -> _CachedPack:
+        keepalive = []
+        n = len(layout.tensors) + len(layout.host_chunks)
+        descs = (_native.CopyDesc * max(n, 1))()
+        blob = _PinnedBlob(layout.host_blob_size())
+        k = 0
+        for placement in layout.tensors:
+            t = placement.tensor
+            if t.device.type != "cuda":
+                # host-resident tensors ride through HBM like everything else
+                t = t.to(self.device, non_blocking=False)
+                keepalive.append(t)
+            elif t.device != self.device:
+                raise ValueError(f"tensor lives on {t.device}, engine on {self.device}")
+            fill_desc(descs[k], t.data_ptr(), placement.payload_offset, t.element_size(), t.shape, t.stride(), c_strides(t.shape))
+            k += 1
+        at = blob.ptr
+        for chunk in layout.host_chunks:
+            fill_desc(descs[k], at, chunk.offset, 1, (len(chunk.data),), (1,), (1,))
+            at += len(chunk.data)
+            k += 1
+        return _CachedPack(_Plan(descs, n, _native.MLF_PACK), blob, keepalive)
+
+    def _pack_entry(self, layout: ObjectLayout) -> _CachedPack:
+        has_host_tensor = any(p.tensor.device.type != "cuda" for p in layout.tensors)
+        key = (
+            tuple(self._tensor_key(p.tensor) + (p.payload_offset,) for p in layout.tensors),
+            tuple((c.offset, len(c.data)) for c in layout.host_chunks),
+        )
+        entry = None if has_host_tensor else self._cache.get(key)
+        if entry is None:
+            entry = self._build_pack(layout)
+            if not has_host_tensor:
+                self._cache[key] = entry
+                while len(self._cache) > self._cache_size:
+                    self._cache.popitem(last=False)
+        else:
+            self._cache.move_to_end(key)
+        entry.blob.fill(layout.host_chunks)
+        return entry
+
+    # ------------------------------------------------------------------ save
+    def pack_async(self, layout: ObjectLayout, buffer_io, start_pos: int = 0, object_id: Optional[str] = None) -> PackTicket:
+        """Starts writing ``layout`` at stream position ``start_pos`` of ``buffer_io``.
+
+        The bytes must already be claimed in ``buffer_io`` (its cursor moved past them). Source
+        tensors are read on a side stream ordered after the caller's current stream. If
+        ``object_id`` is given and the save is staged, the HBM image stays registered under that id
+        until the next save or restore reuses the buffer, so that replication can send it from
+        HBM (``resident_image``).
+        """
+        with self._lock, torch.cuda.device(self.device):
+            self._bind()
+            self._resident = None
+            if self._last_mutate is not None:
+                # the previous kernel may still be reading the pinned blob this save is about to refill
+                self._last_mutate.synchronize()
+            entry = self._pack_entry(layout)
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(self.device))
+            self.pack_stream.wait_event(ready)
+            if self._last_done is not None:
+                # the HBM image is reused: the previous drain must have finished reading it
+                self.pack_stream.wait_event(self._last_done)
+            mutate_event = torch.cuda.Event()
+            done_event = torch.cuda.Event()
+            total = layout.total_bytes
+            if total == 0:
+                mutate_event.record(self.pack_stream)
+                done_event.record(self.pack_stream)
+                return PackTicket(self, entry, mutate_event, done_event, 0)
+            if self.mode == "direct":
+                base = buffer_io.device_address(start_pos)
+                entry.plan.launch(base, total, self.pack_stream.cuda_stream, self.host_ctas)
+                mutate_event.record(self.pack_stream)
+                done_event.record(self.pack_stream)
+            else:
+                image = self.staging(total)
+                entry.plan.launch(image.data_ptr(), total, self.pack_stream.cuda_stream)
+                mutate_event.record(self.pack_stream)
+                self.copy_stream.wait_event(mutate_event)
+                _native.check(
+                    _native.lib().mlf_memcpy_async(
+                        ctypes.c_void_p(buffer_io.host_address(start_pos)),
+                        ctypes.c_void_p(image.data_ptr()),
+                        total,
+                        _native.MLF_COPY_D2H,
+                        ctypes.c_void_p(self.copy_stream.cuda_stream),
+                    )
+                )
+                done_event.record(self.copy_stream)
+                if object_id is not None and start_pos == 0:
+                    self._resident = (str(object_id), image, total, done_event)
+            self._last_mutate, self._last_done = mutate_event, done_event
+            return PackTicket(self, entry, mutate_event, done_event, total)
+
+    def pack(self, layout: ObjectLayout, buffer_io, start_pos: int = 0, object_id: Optional[str] = None) -> None:
+        self.pack_async(layout, buffer_io, start_pos, object_id).wait()
+
+    def resident_image(self, object_id: str, nbytes: int) -> Optional["_ResidentLease"]:
+        """Lease on the HBM image of ``object_id``'s data section, if the last staged save left one
+        of exactly ``nbytes``. While the lease is held no other save or restore can reuse the buffer."""
+        held = self._resident
+        if held is None or held[0] != str(object_id) or held[2] != nbytes:
+            return None
+        return _ResidentLease(self, held)
+
+    # ------------------------------------------------------------------ restore
+    def unpack(self, reads: Sequence[Tuple[torch.Tensor, int, Sequence[int], Sequence[int]]], buffer_io) -> None:
+        """Scatters stored tensors (or sub-blocks) from ``buffer_io`` into target tensors.
+
+        Each read is ``(target, image_off, stored_shape, storage_offsets)``: ``image_off`` is the
+        data-section offset of the stored tensor's first payload byte, ``stored_shape`` its shape as
+        saved, ``storage_offsets`` where the wanted block starts in it; the block's extent is
+        ``target.shape``. Targets may be strided; host targets are filled through a device
+        temporary. Returns when all targets hold their data.
+        """
+        reads = [r for r in reads if r[0].numel() > 0]
+        if not reads:
+            return
+        with self._lock, torch.cuda.device(self.device):
+            self._bind()
+            self._resident = None
+            lo = None
+            hi = 0
+            prepared = []
+            for target, image_off, stored_shape, storage_offsets in reads:
+                esize = target.element_size()
+                istr = c_strides(stored_shape)
+                first = image_off + sum(int(o) * s for o, s in zip(storage_offsets, istr)) * esize
+                span = sum((int(n) - 1) * s for n, s in zip(target.shape, istr)) + 1
+                lo = first if lo is None else min(lo, first)
+                hi = max(hi, first + span * esize)
+                prepared.append((target, first, istr))
+            lo -= lo % 16  # keep image offsets congruent mod 16 between the mapping and the HBM copy
+            image = self.staging(hi - lo)
+            stream = self.pack_stream
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(self.device))
+            stream.wait_event(ready)
+            _native.check(
+                _native.lib().mlf_memcpy_async(
+                    ctypes.c_void_p(image.data_ptr()),
+                    ctypes.c_void_p(buffer_io.host_address(lo)),
+                    hi - lo,
+                    _native.MLF_COPY_H2D,
+                    ctypes.c_void_p(stream.cuda_stream),
+                )
+            )
+            descs = (_native.CopyDesc * len(prepared))()
+            host_targets = []
+            for k, (target, first, istr) in enumerate(prepared):
+                dev_target = target
+                if target.device.type != "cuda":
+                    dev_target = torch.empty(target.shape, dtype=target.dtype, device=self.device)
+                    host_targets.append((target, dev_target))
+                elif target.device != self.device:
+                    raise ValueError(f"target lives on {target.device}, engine on {self.device}")
+                fill_desc(descs[k], dev_target.data_ptr(), first - lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
+            plan = _Plan(descs, len(prepared), _native.MLF_UNPACK)
+            plan.launch(image.data_ptr(), hi - lo, stream.cuda_stream)
+            done = torch.cuda.Event()
+            done.record(stream)
+            done.synchronize()
+            plan.status()
+            for target, dev_target in host_targets:
+                target.copy_(dev_target)
+            # later work on the caller's stream must see the restored values
+            torch.cuda.current_stream(self.device).wait_event(done)
+
+
+class _ResidentLease:
+    """Context manager yielding the device address of a resident object image (see ``resident_image``)."""
+
+    def __init__(self, engine: CudaCopyEngine, held: tuple):
+        self._engine = engine
+        self._held = held
+
+    def __enter__(self) -> int:
+        self._engine._lock.acquire()
+        if self._engine._resident is not self._held:
+            self._engine._lock.release()
+            raise RuntimeError("the resident image was overwritten before it could be leased")
+        self._held[3].synchronize()  # the image is complete once its drain to the host has finished
+        return self._held[1].data_ptr()
+
+    def __exit__(self, *exc) -> None:
+        self._engine._lock.release()
+
+
+_default_engine: Optional[CudaCopyEngine] = None
+_default_engine_lock = threading.Lock()
+
+
+def default_engine() -> CudaCopyEngine:
+    """Process-wide engine on the current CUDA device, created on first use."""
+    global _default_engine
+    with _default_engine_lock:
+        if _default_engine is None:
+            _default_engine = CudaCopyEngine()
+        return _default_engine
+
+
+def resident_image(object_id: str, nbytes: int) -> Optional[_ResidentLease]:
+    """``CudaCopyEngine.resident_image`` of the process-wide engine, or None if there is no engine yet."""
+    engine = _default_engine
+    return None if engine is None else engine.resident_image(object_id, nbytes)

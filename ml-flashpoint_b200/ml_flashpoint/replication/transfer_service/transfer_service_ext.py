@@ -1,0 +1,382 @@
+"""``TransferService``: moves whole checkpoint objects between ranks of one NVLink domain.
+
+Same four-call surface as the reference's compiled service of this name and module path
+(replication/transfer_service/bindings.cpp:23-80, transfer_service.h:57-186): ``initialize`` returns
+the bound control port (or -1), ``async_put`` / ``async_get`` return ``concurrent.futures.Future``s
+that resolve to a ``TransferResult`` or carry an exception, ``shutdown`` fails what is pending. The
+receiver writes ``<object>.tmp`` and renames it once complete, as the reference does
+(transfer_service.cpp:702-780).
+
+The reference streams the object through TCP sockets in 1 MiB ``send()`` calls. Here only a few
+small JSON control messages travel over a socket; the object itself goes GPU to GPU:
+
+  sender HBM image --(copy kernel, 16-byte stores to the peer's HBM over NVLink)--> receiver HBM
+  receiver HBM --(copy engine, PCIe)--> receiver's object mapping --rename--> done
+
+The sender reuses the HBM image the save just produced when it is still resident (see
+``gpu_engine.resident_image``); otherwise the object is first brought into HBM from the host
+pointer that was passed in. The receiving buffer is exported with CUDA IPC and opened by the
+sender; peers inside one process exchange the raw device pointer instead.
+"""
+
+from __future__ import annotations
+
+import concurrent.futures
+import ctypes
+import json
+import os
+import socket
+import struct
+import threading
+import uuid
+from typing import Callable, Dict, Optional, Tuple
+
+from ml_flashpoint import _native
+from ml_flashpoint.core.mlf_logging import get_logger
+
+_LOGGER = get_logger(__name__)
+
+METADATA_SIZE = 4096
+_LEN = struct.Struct("<I")
+_MAX_MESSAGE = 1 << 20
+
+
+class TransferResult:
+    """Outcome of one transfer (reference: ``TransferResult`` in transfer_service.h:50-54)."""
+
+    def __init__(self, task_id: str = "", success: bool = False, error_message: str = ""):
+        self.task_id = task_id
+        self.success = success
+        self.error_message = error_message
+
+    def __repr__(self) -> str:
+        return f"TransferResult(task_id={self.task_id!r}, success={self.success}, error_message={self.error_message!r})"
+
+
+def _send_msg(sock: socket.socket, payload: dict) -> None:
+    raw = json.dumps(payload).encode()
+    sock.sendall(_LEN.pack(len(raw)) + raw)
+
+
+def _recv_exact(sock: socket.socket, n: int) -> bytes:
+    parts = []
+    while n:
+        chunk = sock.recv(n)
+        if not chunk:
+            raise ConnectionError("peer closed the control connection")
+        parts.append(chunk)
+        n -= len(chunk)
+    return b"".join(parts)
+
+
+def _recv_msg(sock: socket.socket) -> dict:
+    (n,) = _LEN.unpack(_recv_exact(sock, _LEN.size))
+    if n > _MAX_MESSAGE:
+        raise ValueError(f"control message of {n} bytes exceeds the limit")
+    return json.loads(_recv_exact(sock, n))
+
+
+def _split_address(address: str) -> Tuple[str, int]:
+    host, _, port = address.rpartition(":")
+    if not host or not port.isdigit():
+        raise ValueError(f"address must look like '<host>:<port>', got '{address}'")
+    return host, int(port)
+
+
+class _DeviceBuffer:
+    """Device memory from plain ``cudaMalloc`` (so that an IPC handle can be exported for it)."""
+
+    def __init__(self, nbytes: int):
+        ptr = ctypes.c_void_p()
+        _native.check(_native.lib().mlf_dev_alloc(nbytes, ctypes.byref(ptr)))
+        self.ptr = int(ptr.value)
+        self.nbytes = nbytes
+        handle = (ctypes.c_uint8 * _native.MLF_IPC_HANDLE_BYTES)()
+        _native.check(_native.lib().mlf_ipc_export(ctypes.c_void_p(self.ptr), handle))
+        self.ipc_hex = bytes(handle).hex()
+
+    def free(self) -> None:
+        if self.ptr:
+            _native.lib().mlf_dev_free(ctypes.c_void_p(self.ptr))
+            self.ptr = 0
+
+
+class TransferService:
+    def __init__(self, replica_path_mapper: Optional[Callable[[str, int], str]] = None):
+        """``replica_path_mapper(object_id, source_rank) -> path`` decides where a received object is
+        stored. The default keeps the sender's path, which is right when peers have separate
+        filesystems; ranks that share one must map replicas elsewhere or they would overwrite the
+        primary copy."""
+        self._map_path = replica_path_mapper or (lambda object_id, source_rank: object_id)
+        self._listener: Optional[socket.socket] = None
+        self._accept_thread: Optional[threading.Thread] = None
+        self._workers: Optional[concurrent.futures.ThreadPoolExecutor] = None
+        self._running = False
+        self._rank = -1
+        self._device = 0
+        self._host = "127.0.0.1"
+        self._port = -1
+        self._lock = threading.Lock()
+        self._pending: Dict[str, concurrent.futures.Future] = {}
+        self._inbound: Dict[int, _DeviceBuffer] = {}  # per source rank
+        self._inbound_locks: Dict[int, threading.Lock] = {}
+        self._opened_ipc: Dict[str, int] = {}
+        self._bounce: Optional[_DeviceBuffer] = None
+        self._stream = ctypes.c_void_p()
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self, listen_port: int = 0, threads: int = 16, conn_pool_per_peer: int = 16, global_rank: int = -1) -> int:
+        """Binds the control socket and starts the workers. Returns the port, or -1 on failure.
+
+        The CUDA device current on the calling thread becomes the service's device.
+        ``conn_pool_per_peer`` is accepted for signature compatibility; control connections are
+        short-lived and not pooled.
+        """
+        try:
+            dev = ctypes.c_int32()
+            _native.check(_native.lib().mlf_get_device(ctypes.byref(dev)))
+            self._device = dev.value
+            _native.check(_native.lib().mlf_stream_create(ctypes.byref(self._stream)))
+            self._rank = global_rank
+            self._host = os.environ.get("MLFLASHPOINT_REPL_HOST", "127.0.0.1")
+            listener = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+            listener.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+            listener.bind((self._host, listen_port))
+            listener.listen(128)
+            listener.settimeout(0.2)
+            self._listener = listener
+            self._port = listener.getsockname()[1]
+            self._workers = concurrent.futures.ThreadPoolExecutor(max_workers=max(2, threads), thread_name_prefix="mlf-xfer")
+            self._running = True
+            self._accept_thread = threading.Thread(target=self._accept_loop, name="mlf-xfer-accept", daemon=True)
+            self._accept_thread.start()
+            return self._port
+        except Exception:
+            _LOGGER.exception("TransferService failed to initialize")
+            return -1
+
+    @property
+    def address(self) -> str:
+        return f"{self._host}:{self._port}"
+
+    def shutdown(self) -> None:
+        """Stops accepting, fails every pending future, releases device buffers."""
+        with self._lock:
+            if not self._running:
+                return
+            self._running = False
+            pending = list(self._pending.values())
+            self._pending.clear()
+        for f in pending:
+            if not f.done():
+                f.set_exception(RuntimeError("TransferService is shutting down"))
+        if self._accept_thread:
+            self._accept_thread.join(timeout=2.0)
+        if self._listener:
+            self._listener.close()
+        if self._workers:
+            self._workers.shutdown(wait=True, cancel_futures=True)
+        _native.lib().mlf_set_device(self._device)
+        for ptr in self._opened_ipc.values():
+            _native.lib().mlf_ipc_close(ctypes.c_void_p(ptr))
+        self._opened_ipc.clear()
+        for buf in list(self._inbound.values()) + ([self._bounce] if self._bounce else []):
+            buf.free()
+        self._inbound.clear()
+        self._bounce = None
+        if self._stream:
+            _native.lib().mlf_stream_destroy(self._stream)
+            self._stream = ctypes.c_void_p()
+
+    # ------------------------------------------------------------------ public transfers
+    def async_put(self, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str) -> concurrent.futures.Future:
+        """Copies ``data_size`` bytes at host address ``data_ptr`` to the peer as ``dest_object_id``.
+
+        The memory is borrowed until the future completes.
+        """
+        return self._submit(self._run_put, int(data_ptr), int(data_size), dest_address, dest_object_id)
+
+    def async_get(self, remote_object_id_to_get_obj_from: str, source_address: str, local_object_id_to_save_received_obj: str) -> concurrent.futures.Future:
+        """Asks the peer at ``source_address`` to send one of its objects here."""
+        return self._submit(self._run_get, remote_object_id_to_get_obj_from, source_address, local_object_id_to_save_received_obj)
+
+    def _submit(self, fn, *args) -> concurrent.futures.Future:
+        future: concurrent.futures.Future = concurrent.futures.Future()
+        task_id = uuid.uuid4().hex
+        with self._lock:
+            if not self._running:
+                future.set_exception(RuntimeError("TransferService is not running"))
+                return future
+            self._pending[task_id] = future
+
+        def _run():
+            try:
+                fn(task_id, *args)
+                outcome, error = TransferResult(task_id, True, ""), None
+            except Exception as e:  # surfaces on the future, as the reference's service does
+                _LOGGER.exception("transfer task %s failed", task_id)
+                outcome, error = None, e
+            with self._lock:
+                self._pending.pop(task_id, None)
+            if future.done():
+                return
+            if error is None:
+                future.set_result(outcome)
+            else:
+                future.set_exception(RuntimeError(str(error)))
+
+        self._workers.submit(_run)
+        return future
+
+    # ------------------------------------------------------------------ sender side
+    def _connect(self, address: str) -> socket.socket:
+        host, port = _split_address(address)
+        last = None
+        for _ in range(5):  # the reference retries connects 5 times, 100 ms apart
+            try:
+                return socket.create_connection((host, port), timeout=30.0)
+            except OSError as e:
+                last = e
+                threading.Event().wait(0.1)
+        raise ConnectionError(f"cannot reach transfer service at {address}: {last}")
+
+    def _peer_pointer(self, reply: dict) -> int:
+        if reply["pid"] == os.getpid():
+            if reply["device"] != self._device:
+                _native.check(_native.lib().mlf_enable_peer_access(reply["device"]))
+            return int(reply["ptr"])
+        key = reply["ipc"]
+        if key not in self._opened_ipc:
+            out = ctypes.c_void_p()
+            handle = (ctypes.c_uint8 * _native.MLF_IPC_HANDLE_BYTES).from_buffer_copy(bytes.fromhex(key))
+            _native.check(_native.lib().mlf_ipc_open(handle, ctypes.byref(out)))
+            self._opened_ipc[key] = int(out.value)
+        return self._opened_ipc[key]
+
+    def _run_put(self, task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, exact_path: bool = False) -> None:
+        from ml_flashpoint.core import gpu_engine
+
+        if data_size <= 0 or not data_ptr:
+            raise ValueError("async_put needs a non-empty source")
+        lib = _native.lib()
+        _native.check(lib.mlf_set_device(self._device))
+        with self._connect(dest_address) as sock:
+            _send_msg(sock, {"op": "put_begin", "obj": dest_object_id, "size": data_size, "src_rank": self._rank, "task": task_id, "exact_path": exact_path})
+            reply = _recv_msg(sock)
+            if not reply.get("ok"):
+                raise RuntimeError(f"peer refused put of '{dest_object_id}': {reply.get('error')}")
+            peer = self._peer_pointer(reply)
+            stream = self._stream
+            twin = None if exact_path else gpu_engine.resident_image(dest_object_id, data_size - METADATA_SIZE)
+            if twin is not None:
+                # metadata block from the host mapping, data section from the HBM image of the save
+                with twin as image_ptr:
+                    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(peer), ctypes.c_void_p(data_ptr), METADATA_SIZE, _native.MLF_COPY_H2D, stream))
+                    _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer + METADATA_SIZE), ctypes.c_void_p(image_ptr), data_size - METADATA_SIZE, stream, 0))
+                    _native.check(lib.mlf_stream_sync(stream))
+            else:
+                with self._lock:
+                    if self._bounce is None or self._bounce.nbytes < data_size:
+                        if self._bounce:
+                            self._bounce.free()
+                        self._bounce = _DeviceBuffer(data_size)
+                    bounce = self._bounce
+                _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(bounce.ptr), ctypes.c_void_p(data_ptr), data_size, _native.MLF_COPY_H2D, stream))
+                _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer), ctypes.c_void_p(bounce.ptr), data_size, stream, 0))
+                _native.check(lib.mlf_stream_sync(stream))
+            _send_msg(sock, {"op": "put_commit", "token": reply["token"]})
+            final = _recv_msg(sock)
+            if not final.get("ok"):
+                raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
+
+    def _run_get(self, task_id: str, remote_object_id: str, source_address: str, local_object_id: str) -> None:
+        with self._connect(source_address) as sock:
+            _send_msg(sock, {"op": "get", "obj": remote_object_id, "dest_obj": local_object_id, "reply_to": self.address, "task": task_id, "src_rank": self._rank})
+            reply = _recv_msg(sock)
+            if not reply.get("ok"):
+                raise RuntimeError(f"peer could not serve '{remote_object_id}': {reply.get('error')}")
+
+    # ------------------------------------------------------------------ receiver side
+    def _accept_loop(self) -> None:
+        while self._running:
+            try:
+                conn, _ = self._listener.accept()
+            except socket.timeout:
+                continue
+            except OSError:
+                return
+            conn.settimeout(60.0)
+            try:
+                self._workers.submit(self._serve, conn)
+            except RuntimeError:
+                conn.close()
+                return
+
+    def _serve(self, conn: socket.socket) -> None:
+        with conn:
+            try:
+                request = _recv_msg(conn)
+                if request["op"] == "put_begin":
+                    self._serve_put(conn, request)
+                elif request["op"] == "get":
+                    self._serve_get(conn, request)
+                else:
+                    _send_msg(conn, {"ok": False, "error": f"unknown op {request['op']}"})
+            except Exception as e:
+                _LOGGER.exception("transfer service request failed")
+                try:
+                    _send_msg(conn, {"ok": False, "error": str(e)})
+                except OSError:
+                    pass
+
+    def _serve_put(self, conn: socket.socket, request: dict) -> None:
+        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+        lib = _native.lib()
+        _native.check(lib.mlf_set_device(self._device))
+        size = int(request["size"])
+        source = int(request.get("src_rank", -1))
+        with self._lock:
+            gate = self._inbound_locks.setdefault(source, threading.Lock())
+        with gate:  # one inbound object per source at a time: they share the landing buffer
+            landing = self._inbound.get(source)
+            if landing is None or landing.nbytes < size:
+                if landing:
+                    landing.free()
+                landing = _DeviceBuffer(size)
+                self._inbound[source] = landing
+            token = uuid.uuid4().hex
+            _send_msg(conn, {"ok": True, "token": token, "ipc": landing.ipc_hex, "ptr": landing.ptr, "pid": os.getpid(), "device": self._device})
+            commit = _recv_msg(conn)
+            if commit.get("op") != "put_commit" or commit.get("token") != token:
+                raise RuntimeError("put was not committed by the sender")
+            final_path = request["obj"] if request.get("exact_path") else self._map_path(request["obj"], source)
+            tmp_path = final_path + ".tmp"
+            target = BufferObject(tmp_path, size, overwrite=True)
+            try:
+                stream = ctypes.c_void_p()
+                _native.check(lib.mlf_stream_create(ctypes.byref(stream)))
+                try:
+                    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(target.get_data_ptr()), ctypes.c_void_p(landing.ptr), size, _native.MLF_COPY_D2H, stream))
+                    _native.check(lib.mlf_stream_sync(stream))
+                finally:
+                    lib.mlf_stream_destroy(stream)
+            finally:
+                target.close()
+            os.rename(tmp_path, final_path)
+        _send_msg(conn, {"ok": True})
+
+    def _serve_get(self, conn: socket.socket, request: dict) -> None:
+        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+        # the object itself, or the replica this service keeps on behalf of the asking rank
+        candidates = [request["obj"], self._map_path(request["obj"], int(request.get("src_rank", -1)))]
+        path = next((c for c in candidates if os.path.exists(c)), None)
+        if path is None:
+            raise FileNotFoundError(f"object '{request['obj']}' is not held here")
+        source = BufferObject(path)
+        try:
+            self._run_put(request.get("task", ""), source.get_data_ptr(), source.get_capacity(), request["reply_to"], request["dest_obj"], exact_path=True)
+        finally:
+            source.close()
+        _send_msg(conn, {"ok": True})

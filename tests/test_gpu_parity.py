@@ -1,0 +1,222 @@
+"""GPU parity: the CUDA pack / unpack path against the golden vectors and the CPU oracle.
+
+Everything here goes through the C ABI of libmlf_b200.so (directly via ctypes plans, or through the
+saver / loader, which call the same entry points). Integer/byte work: the bar is bit-exact.
+"""
+
+import ctypes
+import hashlib
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import mlf_oracle as oracle
+from helpers import case_to_device, golden_object_bytes, load_golden, make_loader, make_saver, tensor_bytes
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def engine():
+    from ml_flashpoint.core.gpu_engine import CudaCopyEngine
+
+    return CudaCopyEngine(mode="staged")
+
+
+@pytest.fixture(scope="module")
+def direct_engine():
+    from ml_flashpoint.core.gpu_engine import CudaCopyEngine
+
+    return CudaCopyEngine(mode="direct")
+
+
+def _save(case, tmp_path, engine, **kw):
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+
+    saver, com = make_saver(copy_engine=engine, **kw)
+    ckpt = CheckpointContainerId(str(tmp_path / "step-1_ckpt"))
+    saver.initialize_checkpoint(ckpt)
+    items, resolver = cases.write_items_and_resolver(case)
+    buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=case["bucket_count"])
+    results = saver.write_data(ckpt, buckets, replicate_after_write=False, thread_count=1)
+    return saver, com, ckpt, buckets, results
+
+
+@pytest.mark.parametrize("mode", ["staged", "direct"])
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_saved_objects_match_reference_bytes(name, mode, tmp_path, golden_dir, engine, direct_engine):
+    gold = load_golden(golden_dir, f"{name}.json")
+    case = case_to_device(cases.CASES[name](), "cuda")
+    _, _, ckpt, buckets, results = _save(case, tmp_path, engine if mode == "staged" else direct_engine)
+    assert [b.object_name for b in buckets] == [o["name"] for o in gold["objects"]]
+    for bucket, g in zip(buckets, gold["objects"]):
+        with open(str(bucket.object_id), "rb") as f:
+            data = f.read()
+        assert len(data) == g["size"]
+        if "file" in g:
+            want = golden_object_bytes(golden_dir, g)
+            if data != want:
+                first = next(i for i in range(len(want)) if data[i] != want[i])
+                pytest.fail(f"{bucket.object_name}: first differing byte at {first}")
+        assert hashlib.sha256(data).hexdigest() == g["sha256"]
+    got = sorted((r.storage_data.relative_path, r.storage_data.offset, r.storage_data.length, r.index.fqn, r.size_in_bytes) for r in results)
+    want = [(w["relative_path"], w["offset"], w["length"], w["index"]["fqn"], w["size_in_bytes"]) for w in gold["write_results"]]
+    assert got == want
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_restore_round_trip_is_bit_exact(name, tmp_path, engine):
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    case = case_to_device(cases.CASES[name](), "cuda")
+    _, com, ckpt, buckets, results = _save(case, tmp_path, engine)
+    loader = make_loader(com, copy_engine=engine)
+    storage = {r.index: r.storage_data for r in results}
+    by_fqn = {r.index.fqn: r.index for r in results}
+    targets, blobs = {}, {}
+
+    class _Planner:
+        def resolve_tensor(self, req):
+            return targets[req.dest_index.fqn]
+
+        def commit_tensor(self, req, tensor):
+            pass
+
+        def load_bytes(self, req, value):
+            blobs[req.dest_index.fqn] = value.read()
+
+    per_object = {}
+    for fqn, t in case["tensors"].items():
+        if t.numel() == 0:
+            continue  # zero-element tensors cannot be loaded by the reference either
+        idx = by_fqn[fqn]
+        # strided targets on purpose for 2-D tensors: restore must honour destination strides
+        if t.dim() == 2:
+            targets[fqn] = torch.zeros((t.shape[1], t.shape[0]), dtype=t.dtype, device="cuda").t()
+        else:
+            targets[fqn] = torch.zeros(t.shape, dtype=t.dtype, device="cuda")
+        req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0] * t.dim()), idx, torch.Size([0] * t.dim()), torch.Size(t.shape))
+        per_object.setdefault(storage[idx].relative_path, []).append(req)
+    for fqn in case["blobs"]:
+        idx = by_fqn[fqn]
+        req = ReadItem(LoadItemType.BYTE_IO, idx, None, idx, None, None)
+        per_object.setdefault(storage[idx].relative_path, []).append(req)
+    for bucket in buckets:
+        loader.read_data(bucket.object_id, per_object.get(bucket.object_name, []), _Planner(), storage)
+    torch.cuda.synchronize()
+    for fqn, target in targets.items():
+        assert tensor_bytes(target) == tensor_bytes(case["tensors"][fqn]), fqn
+    assert blobs == dict(case["blobs"])
+
+
+def test_narrow_reads_match_reference(tmp_path, golden_dir, engine):
+    from torch.distributed.checkpoint.metadata import MetadataIndex
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    rows = load_golden(golden_dir, "narrow.json")
+    tensors = {f"n.{i}": cases.narrow_source(i).cuda() for i in range(len(cases.NARROW_CASES))}
+    _, com, ckpt, buckets, results = _save({"tensors": tensors, "blobs": {}, "bucket_count": 1}, tmp_path, engine)
+    loader = make_loader(com, copy_engine=engine)
+    storage = {r.index: r.storage_data for r in results}
+    for device in ("cuda", "cpu"):
+        for row in rows:
+            shape, dtype, offs, lens = cases.NARROW_CASES[row["i"]]
+            idx = MetadataIndex(f"n.{row['i']}", torch.Size([0] * len(shape)))
+            target = torch.zeros(lens, dtype=dtype, device=device)
+            req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0] * len(lens)), idx, torch.Size(offs), torch.Size(lens))
+
+            class _Planner:
+                def resolve_tensor(self, r):
+                    return target
+
+                def commit_tensor(self, r, t):
+                    pass
+
+            loader.read_data(buckets[0].object_id, [req], _Planner(), {idx: storage[idx]})
+            assert tensor_bytes(target).hex() == row["hex"], (device, row["i"])
+
+
+def _flat_copy(dst_ptr, src_ptr, n):
+    from ml_flashpoint import _native
+
+    _native.check(_native.lib().mlf_copy_kernel_launch(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), n, None, 0))
+
+
+def test_flat_copy_every_misalignment_and_small_size():
+    """All 16 x 16 source/destination residues, sizes 0..257 and around the tile size."""
+    torch.cuda.synchronize()
+    g = torch.Generator().manual_seed(7)
+    src_host = torch.randint(0, 256, (1 << 18,), generator=g, dtype=torch.uint8)
+    src = src_host.cuda()
+    sizes = list(range(0, 258)) + [4095, 4096, 4097, 65535, 65536, 65537, 131072 + 5]
+    for so in range(16):
+        for do in range(16):
+            dst = torch.full((1 << 18,), 0xA5, dtype=torch.uint8, device="cuda")
+            # a few sizes per residue pair keeps the sweep fast; every size is hit for some pair
+            picked = sizes[(so * 16 + do) % 7 :: 7] + [257, 65537]
+            pos = 64
+            spans = []
+            for n in picked:
+                if pos + do + n + 64 > dst.numel():
+                    break
+                _flat_copy(dst.data_ptr() + pos + do, src.data_ptr() + 32 + so, n)
+                spans.append((pos + do, n))
+                pos += ((n + do + 31) // 16 + 2) * 16
+            torch.cuda.synchronize()
+            out = dst.cpu()
+            expect = torch.full_like(out, 0xA5)
+            for at, n in spans:
+                expect[at : at + n] = src_host[32 + so : 32 + so + n]
+            assert torch.equal(out, expect), (so, do)  # also proves nothing outside the spans was touched
+
+
+def test_plan_rejects_out_of_window_launch(engine):
+    from ml_flashpoint import _native
+
+    t = torch.arange(1024, dtype=torch.int32, device="cuda")
+    desc = (_native.CopyDesc * 1)()
+    from ml_flashpoint.core.gpu_engine import fill_desc
+
+    fill_desc(desc[0], t.data_ptr(), 100, 4, (1024,), (1,), (1,))
+    plan = ctypes.c_void_p()
+    lib = _native.lib()
+    _native.check(lib.mlf_plan_create(desc, 1, _native.MLF_PACK, ctypes.byref(plan)))
+    try:
+        assert lib.mlf_plan_image_extent(plan) == 100 + 4096
+        assert lib.mlf_plan_payload_bytes(plan) == 4096
+        image = torch.zeros(8192, dtype=torch.uint8, device="cuda")
+        rc = lib.mlf_plan_launch(plan, ctypes.c_void_p(image.data_ptr()), 4000, None, 0)
+        assert rc == _native.MLF_ERR_BOUNDS
+        assert b"only 4000" in lib.mlf_last_error()
+        _native.check(lib.mlf_plan_launch(plan, ctypes.c_void_p(image.data_ptr()), 8192, None, 0))
+        torch.cuda.synchronize()
+        assert bytes(image[100 : 100 + 4096].cpu().numpy()) == t.cpu().numpy().tobytes()
+        assert int(image[:100].sum()) == 0 and int(image[4196:].sum()) == 0
+    finally:
+        lib.mlf_plan_destroy(plan)
+
+
+@pytest.mark.parametrize("esize,dtype", [(1, torch.uint8), (2, torch.int16), (4, torch.int32), (8, torch.int64)])
+def test_large_transposed_and_row_sliced_sources(esize, dtype, engine, tmp_path):
+    """Transposes larger than one tile, ragged edges, every image residue class via a blob prefix."""
+    g = torch.Generator().manual_seed(esize)
+    for prefix in (0, 1, 3, 6, 13):
+        base = torch.randint(0, 120, (201, 333), generator=g, dtype=torch.int64).to(dtype).cuda()
+        big = torch.randint(0, 120, (70, 5000), generator=g, dtype=torch.int64).to(dtype).cuda()
+        tensors = {
+            "pad": torch.zeros(prefix, dtype=torch.uint8, device="cuda"),
+            "t": base.t(),
+            "rows": big[:, 17:4900],
+            "rows_long": big[3:60, 8:],
+            "batch_t": torch.randint(0, 99, (3, 65, 130), generator=g, dtype=torch.int64).to(dtype).cuda().transpose(1, 2),
+        }
+        case = {"tensors": tensors, "blobs": {}, "bucket_count": 1}
+        _, _, _, buckets, _ = _save(case, tmp_path / f"p{prefix}", engine)
+        with open(str(buckets[0].object_id), "rb") as f:
+            data = f.read()
+        cpu_case = {"tensors": {k: v.cpu() for k, v in tensors.items()}, "blobs": {}, "bucket_count": 1}
+        ((_, want, _),) = oracle.save_case(cpu_case)
+        assert data == want, (esize, prefix)
