@@ -129,6 +129,13 @@ uint64_t mlf_launch_count(void);
 #define MLF_COPY_D2D 2
 /* cudaMemcpyAsync on `stream` (copy-engine DMA). Host memory should be registered. */
 int32_t mlf_memcpy_async(void* dst, const void* src, uint64_t nbytes, int32_t kind, void* stream);
+/* Blocking transfer between device memory and host memory that is NOT registered with CUDA (for
+ * example the read-only mapping of an object opened after a restart). `nthreads` CPU threads
+ * (0 = half the cores) move 16 MiB chunks through a ring of page-locked slots while copy engines
+ * carry the previous chunks, so the transfer runs at the slower of host memcpy and the host link
+ * instead of the driver's pageable path. to_device = 1: host -> device, 0: device -> host.
+ * The device range must not be in use by other work while the call runs. */
+int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t to_device, int32_t nthreads);
 /* Grid-sized 16-byte vector copy kernel between two device-visible addresses (own HBM, a peer
  * GPU's memory opened through IPC or peer access, or registered host memory). Handles any
  * alignment and size. Used for the NVLink replication hop and as the calibration copy. */

@@ -30,6 +30,16 @@ __device__ __forceinline__ void st_vec(uint4* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// The vector held by the next higher lane (undefined for lane 31).
+__device__ __forceinline__ uint4 shfl_down1(const uint4& v) {
+  uint4 o;
+  o.x = __shfl_down_sync(0xffffffffu, v.x, 1);
+  o.y = __shfl_down_sync(0xffffffffu, v.y, 1);
+  o.z = __shfl_down_sync(0xffffffffu, v.z, 1);
+  o.w = __shfl_down_sync(0xffffffffu, v.w, 1);
+  return o;
+}
+
 // 16 bytes starting `shift` bytes (1..15) into the 32-byte window {lo, hi}.
 __device__ __forceinline__ uint4 realign(const uint4& lo, const uint4& hi, unsigned shift) {
   const unsigned bits = (shift & 3u) * 8u;
@@ -68,8 +78,11 @@ __device__ __forceinline__ uint4 realign(const uint4& lo, const uint4& hi, unsig
 // Reads never leave the 16-byte granules that hold at least one source byte.
 __device__ __forceinline__ void copy_bytes(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, uint64_t len,
                                            unsigned tid, unsigned nthr) {
-  const unsigned head = (unsigned)min((uint64_t)((16u - (unsigned)((uintptr_t)dst & 15u)) & 15u), len);
-  if (tid < head) dst[tid] = src[tid];
+  // bring the destination to a 128-byte line for long runs (every warp store then covers whole
+  // lines), to 16 bytes for short ones
+  const unsigned want = len >= 1024 ? 128u : 16u;
+  const unsigned head = (unsigned)min((uint64_t)((want - (unsigned)((uintptr_t)dst & (want - 1u))) & (want - 1u)), len);
+  for (unsigned k = tid; k < head; k += nthr) dst[k] = src[k];
   dst += head;
   src += head;
   len -= head;
@@ -92,14 +105,28 @@ __device__ __forceinline__ void copy_bytes(uint8_t* __restrict__ dst, const uint
     }
     for (; i < nvec; i += nthr) st_vec(d4 + i, ld_vec(s4 + i));
   } else {
+    // Shifted source: output vector i needs aligned source vectors i and i+1. In the main loop a
+    // lane takes vector i+1 from its right neighbour's registers; only lane 31 loads it.
     const uint4* __restrict__ s4 = reinterpret_cast<const uint4*>(src - shift);
+    const unsigned lane = tid & 31u;
     uint64_t i = tid;
     const uint64_t step = (uint64_t)nthr * 2;
-    for (; i + nthr < nvec; i += step) {
-      uint4 a0 = ld_vec_keep(s4 + i), a1 = ld_vec_keep(s4 + i + 1);
-      uint4 b0 = ld_vec_keep(s4 + i + nthr), b1 = ld_vec_keep(s4 + i + nthr + 1);
-      st_vec(d4 + i, realign(a0, a1, shift));
-      st_vec(d4 + i + nthr, realign(b0, b1, shift));
+    // warp-uniform bound: all 32 lanes of the warp must be inside for the shuffles
+    for (; (i - lane) + (uint64_t)nthr + 31u < nvec; i += step) {
+      uint4 a = ld_vec(s4 + i);
+      uint4 b = ld_vec(s4 + i + nthr);
+      uint4 an = a, bn = b;
+      if (lane == 31u) {
+        an = ld_vec(s4 + i + 1);
+        bn = ld_vec(s4 + i + nthr + 1);
+      }
+      const uint4 as = shfl_down1(a), bs = shfl_down1(b);
+      if (lane != 31u) {
+        an = as;
+        bn = bs;
+      }
+      st_vec(d4 + i, realign(a, an, shift));
+      st_vec(d4 + i + nthr, realign(b, bn, shift));
     }
     for (; i < nvec; i += nthr) {
       uint4 a0 = ld_vec_keep(s4 + i), a1 = ld_vec_keep(s4 + i + 1);
@@ -110,7 +137,7 @@ __device__ __forceinline__ void copy_bytes(uint8_t* __restrict__ dst, const uint
   if (tid < tail) {
     const uint64_t o = (nvec << 4) + tid;
     dst[o] = src[o];
-  }
+  }  // tail < 16 <= nthr
 }
 
 }  // namespace mlf

@@ -3,9 +3,41 @@
 // Python host code decides what overlaps with what.
 #include <string.h>
 
+#include <algorithm>
+#include <atomic>
+#include <mutex>
 #include <string>
+#include <thread>
+#include <vector>
 
 #include "common.h"
+
+namespace {
+
+// Page-locked bounce slots for transfers to or from host memory that is NOT registered with CUDA
+// (a read-only object mapping opened after a restart cannot be registered, and registering costs
+// more than the transfer for anything read once). Each worker thread owns two slots and
+// alternates: the CPU fills/drains one while the copy engine works on the other.
+constexpr uint64_t kSlotBytes = 16ull << 20;
+constexpr int kMaxWorkers = 16;
+
+struct BounceRing {
+  std::mutex mu;          // one pipelined copy at a time per process
+  void* slots[kMaxWorkers * 2] = {nullptr};
+  int device = -1;
+};
+BounceRing g_ring;
+
+cudaError_t ensure_slots(int workers) {
+  for (int i = 0; i < workers * 2; ++i) {
+    if (g_ring.slots[i]) continue;
+    cudaError_t e = cudaHostAlloc(&g_ring.slots[i], kSlotBytes, cudaHostAllocPortable);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -20,6 +52,78 @@ int32_t mlf_memcpy_async(void* dst, const void* src, uint64_t nbytes, int32_t ki
     default: return mlf::fail(MLF_ERR_INVALID, "mlf_memcpy_async: unknown copy kind");
   }
   MLF_CUDA(cudaMemcpyAsync(dst, src, nbytes, k, static_cast<cudaStream_t>(stream)));
+  return MLF_OK;
+}
+
+int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t to_device, int32_t nthreads) {
+  if (nbytes == 0) return MLF_OK;
+  if (!dev_ptr || !host_ptr) return mlf::fail(MLF_ERR_INVALID, "mlf_bounce_copy: null pointer");
+  int workers = nthreads > 0 ? nthreads : (int)std::max(1u, std::thread::hardware_concurrency() / 2);
+  workers = std::min(workers, kMaxWorkers);
+  const uint64_t nchunks = (nbytes + kSlotBytes - 1) / kSlotBytes;
+  workers = (int)std::min<uint64_t>((uint64_t)workers, nchunks);
+  int dev = 0;
+  MLF_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> hold(g_ring.mu);
+  MLF_CUDA(ensure_slots(workers));
+
+  std::atomic<int> first_error{(int)cudaSuccess};
+  auto run = [&](int w) {
+    cudaError_t e = cudaSetDevice(dev);
+    cudaStream_t stream = nullptr;
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+    for (int k = 0; k < 2 && e == cudaSuccess; ++k) e = cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming);
+    bool used[2] = {false, false};
+    uint64_t pending_off[2] = {0, 0}, pending_len[2] = {0, 0};
+    int turn = 0;
+    for (uint64_t c = (uint64_t)w; c < nchunks && e == cudaSuccess; c += (uint64_t)workers, turn ^= 1) {
+      const uint64_t off = c * kSlotBytes;
+      const uint64_t len = std::min(kSlotBytes, nbytes - off);
+      char* slot = static_cast<char*>(g_ring.slots[w * 2 + turn]);
+      if (used[turn]) {
+        e = cudaEventSynchronize(done[turn]);  // the slot's previous transfer has left (or arrived)
+        if (e != cudaSuccess) break;
+        if (!to_device) memcpy(static_cast<char*>(host_ptr) + pending_off[turn], slot, pending_len[turn]);
+      }
+      if (to_device) {
+        memcpy(slot, static_cast<const char*>(host_ptr) + off, len);
+        e = cudaMemcpyAsync(static_cast<char*>(dev_ptr) + off, slot, len, cudaMemcpyHostToDevice, stream);
+      } else {
+        e = cudaMemcpyAsync(slot, static_cast<const char*>(dev_ptr) + off, len, cudaMemcpyDeviceToHost, stream);
+        pending_off[turn] = off;
+        pending_len[turn] = len;
+      }
+      if (e == cudaSuccess) e = cudaEventRecord(done[turn], stream);
+      used[turn] = true;
+    }
+    if (e == cudaSuccess && stream) e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess && !to_device) {
+      // drain what is still parked in the slots, oldest first
+      for (int k = 0; k < 2; ++k) {
+        const int t = turn ^ k;
+        if (used[t] && pending_len[t]) {
+          memcpy(static_cast<char*>(host_ptr) + pending_off[t], g_ring.slots[w * 2 + t], pending_len[t]);
+          pending_len[t] = 0;
+        }
+      }
+    }
+    for (int k = 0; k < 2; ++k)
+      if (done[k]) cudaEventDestroy(done[k]);
+    if (stream) cudaStreamDestroy(stream);
+    if (e != cudaSuccess) {
+      int expected = (int)cudaSuccess;
+      first_error.compare_exchange_strong(expected, (int)e);
+    }
+  };
+  std::vector<std::thread> pool;
+  for (int w = 1; w < workers; ++w) pool.emplace_back(run, w);
+  run(0);
+  for (auto& t : pool) t.join();
+  if (first_error.load() != (int)cudaSuccess) {
+    (void)cudaGetLastError();
+    return mlf::cuda_fail((cudaError_t)first_error.load(), "pipelined bounce copy");
+  }
   return MLF_OK;
 }
 

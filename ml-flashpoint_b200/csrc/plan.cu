@@ -36,7 +36,7 @@ struct Seg {
   uint32_t kind;
   uint32_t esize;
   uint32_t ndim;
-  uint32_t b;  // ROWS: rows per tile (0 = chunked rows) | TRANSPOSE: tiles along L
+  uint32_t b;  // FLAT: destination address mod 128 | ROWS: rows per tile (0 = chunked rows) | TRANSPOSE: tiles along L
   uint32_t c;  // ROWS: chunks per row                   | TRANSPOSE: index of dimension C
   uint32_t image_aligned;  // 1 if every image element address is a multiple of esize
   int64_t shape[MLF_MAX_DIMS];
@@ -219,8 +219,11 @@ __global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restric
     const uint32_t local = tile - tile_begin[lo];
     switch (g.kind) {
       case kFlat: {
-        const uint64_t off = (uint64_t)local * kTileBytes;
-        const uint64_t len = min(kTileBytes, g.a - off);
+        // tiles are cut on 64 KiB boundaries of the DESTINATION address space, so that only the
+        // first and last tile of a segment have ragged edges
+        const uint64_t lo_edge = (uint64_t)local * kTileBytes;
+        const uint64_t off = lo_edge > g.b ? lo_edge - g.b : 0;
+        const uint64_t len = min(lo_edge + kTileBytes - g.b, g.a) - off;
         uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + off;
         uint8_t* ip = image + g.image_off + off;
         if (DIR == MLF_PACK)
@@ -254,10 +257,13 @@ __global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restric
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
                                                                  const uint8_t* __restrict__ src, uint64_t nbytes) {
-  const uint64_t ntiles = (nbytes + kTileBytes - 1) / kTileBytes;
+  const uint64_t mis = (uint64_t)((uintptr_t)dst & 127u);
+  const uint64_t ntiles = (mis + nbytes + kTileBytes - 1) / kTileBytes;
   for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const uint64_t off = t * kTileBytes;
-    mlf::copy_bytes(dst + off, src + off, min(kTileBytes, nbytes - off), threadIdx.x, blockDim.x);
+    const uint64_t lo_edge = t * kTileBytes;
+    const uint64_t off = lo_edge > mis ? lo_edge - mis : 0;
+    const uint64_t len = min(lo_edge + kTileBytes - mis, nbytes) - off;
+    mlf::copy_bytes(dst + off, src + off, len, threadIdx.x, blockDim.x);
   }
 }
 
@@ -400,7 +406,10 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
     if (c.ndim == 0 || (c.ndim == 1 && inner_contig)) {
       g.kind = kFlat;
       g.a = numel * d.elem_size;
-      ntile = (g.a + kTileBytes - 1) / kTileBytes;
+      // the image base is at least 128-byte aligned in practice (HBM allocations, page-aligned
+      // mappings); if it is not, only the tile edges move, never the bytes
+      g.b = (uint32_t)((direction == MLF_PACK ? d.image_off : d.tensor_ptr) & 127u);
+      ntile = (g.b + g.a + kTileBytes - 1) / kTileBytes;
     } else if (inner_contig) {
       g.kind = kRows;
       g.a = (uint64_t)c.shape[last] * esize;
@@ -520,7 +529,7 @@ int32_t mlf_copy_kernel_launch(void* dst, const void* src, uint64_t nbytes, void
   if (nbytes == 0) return MLF_OK;
   if (!dst || !src) return mlf::fail(MLF_ERR_INVALID, "mlf_copy_kernel_launch: null pointer");
   uint32_t grid = 1;
-  int32_t rc = wave_grid(mlf_flat_copy_kernel, max_ctas, (nbytes + kTileBytes - 1) / kTileBytes, &grid);
+  int32_t rc = wave_grid(mlf_flat_copy_kernel, max_ctas, (nbytes + 127 + kTileBytes - 1) / kTileBytes, &grid);
   if (rc != MLF_OK) return rc;
   mlf_flat_copy_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nbytes);

@@ -83,6 +83,7 @@ _SIGNATURES = {
     "mlf_plan_launch": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_int32]),
     "mlf_plan_status": (c_int32, [c_void_p]),
     "mlf_memcpy_async": (c_int32, [c_void_p, c_void_p, c_uint64, c_int32, c_void_p]),
+    "mlf_bounce_copy": (c_int32, [c_void_p, c_void_p, c_uint64, c_int32, c_int32]),
     "mlf_copy_kernel_launch": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_int32]),
     "mlf_dev_alloc": (c_int32, [c_uint64, POINTER(c_void_p)]),
     "mlf_dev_free": (c_int32, [c_void_p]),

@@ -206,9 +206,10 @@ class PackTicket:
     byte has reached the object mapping. ``wait()`` blocks on the latter and surfaces kernel status.
     """
 
-    def __init__(self, engine: "CudaCopyEngine", cached: _CachedPack, mutate_event, done_event, nbytes: int):
+    def __init__(self, engine: "CudaCopyEngine", cached: _CachedPack, start_event, mutate_event, done_event, nbytes: int):
         self._engine = engine
         self._cached = cached
+        self.start_event = start_event
         self.mutate_event = mutate_event
         self.done_event = done_event
         self.nbytes = nbytes
@@ -216,6 +217,14 @@ class PackTicket:
     def wait(self) -> None:
         self.done_event.synchronize()
         self._cached.plan.status()
+
+    def kernel_ms(self) -> float:
+        """Device time of the pack kernel (valid after ``wait``)."""
+        return self.start_event.elapsed_time(self.mutate_event)
+
+    def total_ms(self) -> float:
+        """Device time from kernel start to the last byte reaching the object mapping."""
+        return self.start_event.elapsed_time(self.done_event)
 
 
 class CudaCopyEngine:
@@ -239,12 +248,16 @@ class CudaCopyEngine:
         if self.mode not in ("staged", "direct"):
             raise ValueError(f"unknown pack mode '{self.mode}' (expected 'staged' or 'direct')")
         self.host_ctas = get_env_val_int("GPU_HOST_CTAS", 32)
+        # CPU threads feeding the bounce ring when host memory is not page-locked (0 = half the cores)
+        self.host_threads = get_env_val_int("GPU_HOST_THREADS", 0)
         self._lock = threading.RLock()
         self._cache: "OrderedDict[tuple, _CachedPack]" = OrderedDict()
         self._cache_size = plan_cache_size
         self._staging: Optional[torch.Tensor] = None
         self._last_mutate: Optional[torch.cuda.Event] = None  # last kernel that read a pinned blob
         self._last_done: Optional[torch.cuda.Event] = None  # last transfer that read the HBM image
+        self.last_ticket: Optional[PackTicket] = None  # most recent save, for timing queries
+        self.last_unpack_ms: Optional[Tuple[float, float]] = None  # (host-to-HBM ms, kernel ms) of the last restore
         self._resident: Optional[tuple] = None  # (object id, image tensor, nbytes, done event) of the last staged save
         with torch.cuda.device(self.device):
             self._bind()
@@ -254,6 +267,11 @@ class CudaCopyEngine:
     # ------------------------------------------------------------------ helpers
     def _bind(self) -> None:
         _native.check(_native.lib().mlf_set_device(self.device.index))
+
+    @staticmethod
+    def _is_registered(buffer_io) -> bool:
+        obj = getattr(buffer_io, "buffer_obj", None)
+        return bool(getattr(obj, "is_cuda_registered", False))
 
     def staging(self, nbytes: int) -> torch.Tensor:
         """HBM image buffer of at least ``nbytes`` (grown geometrically, reused across saves)."""
@@ -331,13 +349,15 @@ class CudaCopyEngine:
             if self._last_done is not None:
                 # the HBM image is reused: the previous drain must have finished reading it
                 self.pack_stream.wait_event(self._last_done)
-            mutate_event = torch.cuda.Event()
-            done_event = torch.cuda.Event()
+            start_event = torch.cuda.Event(enable_timing=True)
+            mutate_event = torch.cuda.Event(enable_timing=True)
+            done_event = torch.cuda.Event(enable_timing=True)
             total = layout.total_bytes
+            start_event.record(self.pack_stream)
             if total == 0:
                 mutate_event.record(self.pack_stream)
                 done_event.record(self.pack_stream)
-                return PackTicket(self, entry, mutate_event, done_event, 0)
+                return PackTicket(self, entry, start_event, mutate_event, done_event, 0)
             if self.mode == "direct":
                 base = buffer_io.device_address(start_pos)
                 entry.plan.launch(base, total, self.pack_stream.cuda_stream, self.host_ctas)
@@ -347,21 +367,38 @@ class CudaCopyEngine:
                 image = self.staging(total)
                 entry.plan.launch(image.data_ptr(), total, self.pack_stream.cuda_stream)
                 mutate_event.record(self.pack_stream)
-                self.copy_stream.wait_event(mutate_event)
-                _native.check(
-                    _native.lib().mlf_memcpy_async(
-                        ctypes.c_void_p(buffer_io.host_address(start_pos)),
-                        ctypes.c_void_p(image.data_ptr()),
-                        total,
-                        _native.MLF_COPY_D2H,
-                        ctypes.c_void_p(self.copy_stream.cuda_stream),
+                if self._is_registered(buffer_io):
+                    # page-locked destination: one asynchronous copy-engine transfer
+                    self.copy_stream.wait_event(mutate_event)
+                    _native.check(
+                        _native.lib().mlf_memcpy_async(
+                            ctypes.c_void_p(buffer_io.host_address(start_pos)),
+                            ctypes.c_void_p(image.data_ptr()),
+                            total,
+                            _native.MLF_COPY_D2H,
+                            ctypes.c_void_p(self.copy_stream.cuda_stream),
+                        )
                     )
-                )
-                done_event.record(self.copy_stream)
+                    done_event.record(self.copy_stream)
+                else:
+                    # pageable destination (a standalone object file): drain through the page-locked
+                    # bounce ring, several CPU threads wide. This part blocks the caller.
+                    mutate_event.synchronize()
+                    _native.check(
+                        _native.lib().mlf_bounce_copy(
+                            ctypes.c_void_p(image.data_ptr()),
+                            ctypes.c_void_p(buffer_io.host_address(start_pos)),
+                            total,
+                            0,
+                            self.host_threads,
+                        )
+                    )
+                    done_event.record(self.pack_stream)
                 if object_id is not None and start_pos == 0:
                     self._resident = (str(object_id), image, total, done_event)
             self._last_mutate, self._last_done = mutate_event, done_event
-            return PackTicket(self, entry, mutate_event, done_event, total)
+            self.last_ticket = PackTicket(self, entry, start_event, mutate_event, done_event, total)
+            return self.last_ticket
 
     def pack(self, layout: ObjectLayout, buffer_io, start_pos: int = 0, object_id: Optional[str] = None) -> None:
         self.pack_async(layout, buffer_io, start_pos, object_id).wait()
@@ -407,15 +444,32 @@ class CudaCopyEngine:
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
             stream.wait_event(ready)
-            _native.check(
-                _native.lib().mlf_memcpy_async(
-                    ctypes.c_void_p(image.data_ptr()),
-                    ctypes.c_void_p(buffer_io.host_address(lo)),
-                    hi - lo,
-                    _native.MLF_COPY_H2D,
-                    ctypes.c_void_p(stream.cuda_stream),
+            t_begin = torch.cuda.Event(enable_timing=True)
+            t_copied = torch.cuda.Event(enable_timing=True)
+            t_begin.record(stream)
+            if self._is_registered(buffer_io):
+                _native.check(
+                    _native.lib().mlf_memcpy_async(
+                        ctypes.c_void_p(image.data_ptr()),
+                        ctypes.c_void_p(buffer_io.host_address(lo)),
+                        hi - lo,
+                        _native.MLF_COPY_H2D,
+                        ctypes.c_void_p(stream.cuda_stream),
+                    )
                 )
-            )
+            else:
+                # read-only object mappings cannot be page-locked: feed HBM through the bounce ring
+                stream.synchronize()
+                _native.check(
+                    _native.lib().mlf_bounce_copy(
+                        ctypes.c_void_p(image.data_ptr()),
+                        ctypes.c_void_p(buffer_io.host_address(lo)),
+                        hi - lo,
+                        1,
+                        self.host_threads,
+                    )
+                )
+            t_copied.record(stream)
             descs = (_native.CopyDesc * len(prepared))()
             host_targets = []
             for k, (target, first, istr) in enumerate(prepared):
@@ -428,10 +482,11 @@ class CudaCopyEngine:
                 fill_desc(descs[k], dev_target.data_ptr(), first - lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
             plan = _Plan(descs, len(prepared), _native.MLF_UNPACK)
             plan.launch(image.data_ptr(), hi - lo, stream.cuda_stream)
-            done = torch.cuda.Event()
+            done = torch.cuda.Event(enable_timing=True)
             done.record(stream)
             done.synchronize()
             plan.status()
+            self.last_unpack_ms = (t_begin.elapsed_time(t_copied), t_copied.elapsed_time(done))
             for target, dev_target in host_targets:
                 target.copy_(dev_target)
             # later work on the caller's stream must see the restored values

@@ -23,3 +23,18 @@ def pytest_configure(config):
 @pytest.fixture
 def golden_dir():
     return GOLDEN_DIR
+
+
+@pytest.fixture
+def shm_path():
+    """Scratch directory on tmpfs: page-locking a file mapping for CUDA only works for memory-backed files."""
+    import pathlib
+    import shutil
+    import tempfile
+
+    root = "/dev/shm" if os.path.isdir("/dev/shm") else None
+    path = tempfile.mkdtemp(prefix="mlf_test_", dir=root)
+    try:
+        yield pathlib.Path(path)
+    finally:
+        shutil.rmtree(path, ignore_errors=True)

@@ -47,10 +47,10 @@ def _save(case, tmp_path, engine, **kw):
 
 @pytest.mark.parametrize("mode", ["staged", "direct"])
 @pytest.mark.parametrize("name", sorted(cases.CASES))
-def test_saved_objects_match_reference_bytes(name, mode, tmp_path, golden_dir, engine, direct_engine):
+def test_saved_objects_match_reference_bytes(name, mode, shm_path, golden_dir, engine, direct_engine):
     gold = load_golden(golden_dir, f"{name}.json")
     case = case_to_device(cases.CASES[name](), "cuda")
-    _, _, ckpt, buckets, results = _save(case, tmp_path, engine if mode == "staged" else direct_engine)
+    _, _, ckpt, buckets, results = _save(case, shm_path, engine if mode == "staged" else direct_engine)
     assert [b.object_name for b in buckets] == [o["name"] for o in gold["objects"]]
     for bucket, g in zip(buckets, gold["objects"]):
         with open(str(bucket.object_id), "rb") as f:
