@@ -115,6 +115,28 @@ uint64_t mlf_plan_num_tiles(const mlf_plan* p);
 int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, void* stream, int32_t max_ctas);
 /* After the stream has been synchronised: 0, or the MLF_ERR_* a kernel recorded. Clears it. */
 int32_t mlf_plan_status(mlf_plan* p);
+/* Gather-pack for callers that cannot obtain device memory: the same kernel as a MLF_PACK plan,
+ * with its tables in a fixed array inside the library instead of freshly allocated memory.
+ * (No counterpart in the reference implementation, which never touches device memory.)
+ *
+ * Who needs it: a save that has to run when the process cannot get another byte of HBM, typically
+ * an emergency checkpoint right after an out-of-memory error, or any trainer whose own caching
+ * allocator has claimed the whole device, so that the cudaMalloc inside mlf_plan_create would
+ * fail. This call allocates nothing: no cudaMalloc, cudaFree or other allocating routine, on
+ * the device or through a framework. The caller passes inputs (descriptors, tensors) and the
+ * output image as for a plan.
+ *
+ * Limit: at most MLF_NOALLOC_MAX_DESCS descriptors per call; more is refused with
+ * MLF_ERR_TOO_LARGE. The array (about 250 KiB) is held by every GPU that loads the library,
+ * until the process exits.
+ *
+ * The first call on a device, with that device current, looks up the array's device address;
+ * make that first call outside any stream capture. All calls on a device share the one array,
+ * and it keeps the last call's tables: two calls whose kernels can overlap on the GPU (different
+ * streams, or several threads) race on it, so finish one (or order them on one stream) before
+ * starting the next. The launch is asynchronous on `stream`, like mlf_plan_launch. */
+#define MLF_NOALLOC_MAX_DESCS 1024
+int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_base, uint64_t image_capacity, void* stream);
 /* Kernel launches issued by this library since load (for launch accounting in benchmarks). */
 uint64_t mlf_launch_count(void);
 

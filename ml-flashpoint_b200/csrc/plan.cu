@@ -13,6 +13,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -311,37 +312,32 @@ Canon canonicalise(uint32_t esize, const int64_t* shape, const int64_t* ts_elems
   return c;
 }
 
-}  // namespace
+// ---- scratch of mlf_pack_noalloc ---------------------------------------------------------
+// Segment table, tile index and a status word for the entry point that may not allocate. The
+// array lives in every device that loads this library, from load until exit.
+constexpr uint32_t kNoAllocMaxSegs = MLF_NOALLOC_MAX_DESCS;
+constexpr size_t kNoAllocSegBytes = sizeof(Seg) * kNoAllocMaxSegs;
+constexpr size_t kNoAllocTileBytes = sizeof(uint32_t) * (kNoAllocMaxSegs + 1);
+constexpr size_t kNoAllocStatusOff = (kNoAllocSegBytes + kNoAllocTileBytes + 255) / 256 * 256;
+constexpr size_t kNoAllocScratchBytes = kNoAllocStatusOff + 256;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocScratchBytes];
 
-struct mlf_plan {
-  int direction = MLF_PACK;
-  int device = 0;
-  uint32_t nseg = 0;
-  uint32_t ntiles = 0;
-  uint64_t extent = 0;
-  uint64_t payload = 0;
-  Seg* d_segs = nullptr;
-  uint32_t* d_tile_begin = nullptr;
-  int32_t* d_status = nullptr;
-};
+// Device address of g_noalloc_scratch per device, resolved on the first call made with that
+// device current. (In host code the array's name is only a handle for the runtime, not an address.)
+constexpr int kMaxDevices = 64;
+uint8_t* g_noalloc_dev_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;  // guards the pointer table and the host staging arrays below
+Seg g_noalloc_host_segs[kNoAllocMaxSegs];
+uint32_t g_noalloc_host_tiles[kNoAllocMaxSegs + 1];
 
-extern "C" {
-
-int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t direction, mlf_plan** out) {
-  if (!out) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: null out");
-  *out = nullptr;
-  if (n > 0 && !descs) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: null descriptors");
-  if (direction != MLF_PACK && direction != MLF_UNPACK)
-    return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: direction must be MLF_PACK or MLF_UNPACK");
-
-  std::vector<Seg> segs;
-  std::vector<uint32_t> tile_begin;
-  segs.reserve(n);
-  tile_begin.reserve(n + 1);
-  uint64_t tiles = 0, extent = 0, payload = 0;
-
-  for (uint64_t i = 0; i < n; ++i) {
-    const mlf_copy_desc& d = descs[i];
+// Turns one descriptor into a segment: validation, canonical form, kind and tile count.
+// On success *ntile_out is 0 if the descriptor moves nothing (the segment is then unused).
+int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg* seg_out, uint64_t* ntile_out,
+                     uint64_t* payload_out, uint64_t* extent_out) {
+  *ntile_out = 0;
+  *payload_out = 0;
+  *extent_out = 0;
+  {
     const std::string where = "descriptor " + std::to_string(i);
     if (d.ndim > MLF_MAX_DIMS) return mlf::fail(MLF_ERR_INVALID, where + ": ndim exceeds MLF_MAX_DIMS");
     if (d.elem_size != 1 && d.elem_size != 2 && d.elem_size != 4 && d.elem_size != 8 && d.elem_size != 16)
@@ -354,10 +350,10 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
       numel *= (uint64_t)d.shape[k];
       if (d.shape[k] > 0) span += (uint64_t)(d.shape[k] - 1) * (uint64_t)d.image_stride[k];
     }
-    if (numel == 0) continue;  // nothing to move; the format stores no payload for it either
+    if (numel == 0) return MLF_OK;  // nothing to move; the format stores no payload for it either
     if (d.tensor_ptr == 0) return mlf::fail(MLF_ERR_INVALID, where + ": null tensor pointer");
-    payload += numel * d.elem_size;
-    extent = std::max(extent, d.image_off + (span + 1) * d.elem_size);
+    *payload_out = numel * d.elem_size;
+    *extent_out = d.image_off + (span + 1) * d.elem_size;
 
     // 16-byte elements are moved as pairs of 8-byte halves (an extra innermost dimension of 2)
     int64_t shp[MLF_MAX_DIMS + 1], ts[MLF_MAX_DIMS + 1], is[MLF_MAX_DIMS + 1];
@@ -383,7 +379,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
     if (c.ndim > MLF_MAX_DIMS)
       return mlf::fail(MLF_ERR_INVALID, where + ": too many dimensions after splitting 16-byte elements");
 
-    Seg g;
+    Seg& g = *seg_out;
     memset(&g, 0, sizeof(g));
     g.tensor = d.tensor_ptr;
     g.image_off = d.image_off;
@@ -446,6 +442,48 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
         ntile = (g.a + kGenericTile - 1) / kGenericTile;
       }
     }
+    *ntile_out = ntile;
+  }
+  return MLF_OK;
+}
+
+}  // namespace
+
+struct mlf_plan {
+  int direction = MLF_PACK;
+  int device = 0;
+  uint32_t nseg = 0;
+  uint32_t ntiles = 0;
+  uint64_t extent = 0;
+  uint64_t payload = 0;
+  Seg* d_segs = nullptr;
+  uint32_t* d_tile_begin = nullptr;
+  int32_t* d_status = nullptr;
+};
+
+extern "C" {
+
+int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t direction, mlf_plan** out) {
+  if (!out) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: null out");
+  *out = nullptr;
+  if (n > 0 && !descs) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: null descriptors");
+  if (direction != MLF_PACK && direction != MLF_UNPACK)
+    return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: direction must be MLF_PACK or MLF_UNPACK");
+
+  std::vector<Seg> segs;
+  std::vector<uint32_t> tile_begin;
+  segs.reserve(n);
+  tile_begin.reserve(n + 1);
+  uint64_t tiles = 0, extent = 0, payload = 0;
+
+  for (uint64_t i = 0; i < n; ++i) {
+    Seg g;
+    uint64_t ntile = 0, seg_payload = 0, seg_extent = 0;
+    const int32_t rc = plan_segment(descs[i], i, direction, &g, &ntile, &seg_payload, &seg_extent);
+    if (rc != MLF_OK) return rc;
+    if (ntile == 0) continue;
+    payload += seg_payload;
+    extent = std::max(extent, seg_extent);
     if (tiles + ntile > 0xfffffff0ull) return mlf::fail(MLF_ERR_TOO_LARGE, "plan has too many tiles");
     tile_begin.push_back((uint32_t)tiles);
     segs.push_back(g);
@@ -522,6 +560,64 @@ int32_t mlf_plan_status(mlf_plan* p) {
     MLF_CUDA(cudaMemset(p->d_status, 0, sizeof(v)));
     return mlf::fail(v, "a plan kernel recorded status " + std::to_string(v));
   }
+  return MLF_OK;
+}
+
+int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_base, uint64_t image_capacity, void* stream) {
+  if (n > 0 && !descs) return mlf::fail(MLF_ERR_INVALID, "mlf_pack_noalloc: null descriptors");
+  if (n > kNoAllocMaxSegs)
+    return mlf::fail(MLF_ERR_TOO_LARGE, "mlf_pack_noalloc takes at most " + std::to_string(kNoAllocMaxSegs) +
+                                            " descriptors per call, got " + std::to_string(n) +
+                                            "; split the object or use mlf_plan_create");
+  int dev = 0;
+  MLF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return mlf::fail(MLF_ERR_INVALID, "mlf_pack_noalloc: device index out of range");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  std::lock_guard<std::mutex> hold(g_noalloc_mu);
+  if (!g_noalloc_dev_ptr[dev]) {
+    // one-time set-up for this device: ask the runtime where the static array lives here
+    uint8_t* where = nullptr;
+    MLF_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&where), g_noalloc_scratch));
+    g_noalloc_dev_ptr[dev] = where;
+  }
+  uint8_t* scratch = g_noalloc_dev_ptr[dev];
+
+  uint32_t nseg = 0;
+  uint64_t tiles = 0, extent = 0;
+  for (uint64_t i = 0; i < n; ++i) {
+    uint64_t ntile = 0, seg_payload = 0, seg_extent = 0;
+    const int32_t rc = plan_segment(descs[i], i, MLF_PACK, &g_noalloc_host_segs[nseg], &ntile, &seg_payload, &seg_extent);
+    if (rc != MLF_OK) return rc;
+    if (ntile == 0) continue;
+    extent = std::max(extent, seg_extent);
+    if (tiles + ntile > 0xfffffff0ull) return mlf::fail(MLF_ERR_TOO_LARGE, "mlf_pack_noalloc: too many tiles");
+    g_noalloc_host_tiles[nseg] = (uint32_t)tiles;
+    tiles += ntile;
+    ++nseg;
+  }
+  g_noalloc_host_tiles[nseg] = (uint32_t)tiles;
+  if (extent > image_capacity)
+    return mlf::fail(MLF_ERR_BOUNDS, "descriptors touch " + std::to_string(extent) + " image bytes but only " +
+                                         std::to_string(image_capacity) + " are available");
+  if (tiles == 0) return MLF_OK;
+  if (!image_base) return mlf::fail(MLF_ERR_INVALID, "mlf_pack_noalloc: null image");
+
+  // The array still holds the previous call's tables. Everything the kernel reads, entries
+  // [0, nseg) and [0, nseg], is overwritten here; the status word is the one thing that must
+  // start at zero. The uploads are ordered on `stream`, ahead of the kernel, and have left the
+  // host staging arrays by the time cudaMemcpyAsync returns (pageable source).
+  Seg* d_segs = reinterpret_cast<Seg*>(scratch);
+  uint32_t* d_tiles = reinterpret_cast<uint32_t*>(scratch + kNoAllocSegBytes);
+  MLF_CUDA(cudaMemsetAsync(scratch + kNoAllocStatusOff, 0, 256, s));
+  MLF_CUDA(cudaMemcpyAsync(d_segs, g_noalloc_host_segs, sizeof(Seg) * nseg, cudaMemcpyHostToDevice, s));
+  MLF_CUDA(cudaMemcpyAsync(d_tiles, g_noalloc_host_tiles, sizeof(uint32_t) * (nseg + 1), cudaMemcpyHostToDevice, s));
+  uint32_t grid = 1;
+  const int32_t rc = wave_grid(mlf_plan_kernel<MLF_PACK>, 0, tiles, &grid);
+  if (rc != MLF_OK) return rc;
+  mlf_plan_kernel<MLF_PACK><<<grid, kThreads, 0, s>>>(d_segs, d_tiles, nseg, (uint32_t)tiles, static_cast<uint8_t*>(image_base));
+  MLF_CUDA(cudaGetLastError());
+  mlf::g_launches.fetch_add(1);
   return MLF_OK;
 }
 

@@ -29,6 +29,7 @@ MLF_COPY_D2H = 0
 MLF_COPY_H2D = 1
 MLF_COPY_D2D = 2
 MLF_IPC_HANDLE_BYTES = 64
+MLF_NOALLOC_MAX_DESCS = 1024
 
 LIB_NAME = "libmlf_b200.so"
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
@@ -82,6 +83,7 @@ _SIGNATURES = {
     "mlf_plan_num_tiles": (c_uint64, [c_void_p]),
     "mlf_plan_launch": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_int32]),
     "mlf_plan_status": (c_int32, [c_void_p]),
+    "mlf_pack_noalloc": (c_int32, [POINTER(CopyDesc), c_uint64, c_void_p, c_uint64, c_void_p]),
     "mlf_memcpy_async": (c_int32, [c_void_p, c_void_p, c_uint64, c_int32, c_void_p]),
     "mlf_bounce_copy": (c_int32, [c_void_p, c_void_p, c_uint64, c_int32, c_int32]),
     "mlf_copy_kernel_launch": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_int32]),
