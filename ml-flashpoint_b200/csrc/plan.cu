@@ -10,6 +10,7 @@
 //              shared memory so both sides are touched along their contiguous direction
 //   GENERIC    anything else (stepped slices, expands): one element per thread
 // The image side has byte alignment only, because the object format is unpadded.
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -17,6 +18,7 @@
 #include <string>
 #include <vector>
 
+#include "bulk_pipeline.cuh"
 #include "common.h"
 #include "copy_device.cuh"
 
@@ -256,6 +258,181 @@ __global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restric
   }
 }
 
+// ---- bulk-copy staged variant -------------------------------------------------------------
+// Same tiles, same bytes. Linear tiles (FLAT, and chunks of long ROWS) stream through the
+// shared-memory ring of bulk_pipeline.cuh; the other kinds run exactly as in mlf_plan_kernel.
+
+struct LinearTile {
+  const uint8_t* src;
+  uint8_t* dst;
+  uint64_t len;
+  uint32_t nstage;
+};
+
+// Span of tile `local` of segment g if the tile is one contiguous run on both sides.
+template <int DIR>
+__device__ __forceinline__ bool linear_span(const Seg& g, uint32_t local, uint8_t* image, LinearTile* out) {
+  uint64_t toff, ioff, len;
+  if (g.kind == kFlat) {
+    const uint64_t lo_edge = (uint64_t)local * kTileBytes;
+    const uint64_t off = lo_edge > g.b ? lo_edge - g.b : 0;
+    len = min(lo_edge + kTileBytes - g.b, g.a) - off;
+    toff = off;
+    ioff = off;
+  } else if (g.kind == kRows && g.b == 0) {
+    uint64_t row = local / g.c;
+    const uint64_t chunk = local % g.c;
+    int64_t t = 0, i = 0;
+    for (int d = (int)g.ndim - 2; d >= 0; --d) {
+      const int64_t idx = (int64_t)(row % (uint64_t)g.shape[d]);
+      row /= (uint64_t)g.shape[d];
+      t += idx * g.tstride[d];
+      i += idx * g.istride[d];
+    }
+    const uint64_t off = chunk * kTileBytes;
+    len = min(kTileBytes, g.a - off);
+    toff = (uint64_t)t + off;
+    ioff = (uint64_t)i + off;
+  } else {
+    return false;
+  }
+  uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + toff;
+  uint8_t* ip = image + g.image_off + ioff;
+  out->src = DIR == MLF_PACK ? tp : ip;
+  out->dst = DIR == MLF_PACK ? ip : tp;
+  out->len = len;
+  out->nstage = (uint32_t)((len + mlf::kStageBytes - 1) / mlf::kStageBytes);
+  return true;
+}
+
+__device__ __forceinline__ uint32_t find_segment(const uint32_t* __restrict__ tile_begin, uint32_t nseg, uint32_t tile) {
+  uint32_t lo = 0, hi = nseg;
+  while (hi - lo > 1) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (tile_begin[mid] <= tile)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  return lo;
+}
+
+template <int DIR>
+__global__ void __launch_bounds__(kThreads) mlf_plan_kernel_bulk(const Seg* __restrict__ segs,
+                                                                 const uint32_t* __restrict__ tile_begin, uint32_t nseg,
+                                                                 uint32_t ntiles, uint8_t* __restrict__ image,
+                                                                 int32_t* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
+  __shared__ __align__(8) uint64_t full[mlf::kStages];
+  __shared__ __align__(16) uint8_t tsmem[32 * 33 * 8];
+  __shared__ Seg g;
+  __shared__ int abort_flag;
+  const unsigned tid = threadIdx.x;
+
+  if (tid == 0) {
+    for (uint32_t k = 0; k < mlf::kStages; ++k) mlf::mbar_init(&full[k], 1);
+    mlf::mbar_init_fence();
+    abort_flag = 0;
+  }
+  __syncthreads();
+
+  // producer cursor (thread 0): the next stage to load, always ahead of the consumers
+  uint32_t p_tile = blockIdx.x, p_stage = 0, issued = 0;
+  LinearTile p_lt;
+  p_lt.nstage = 0;
+  auto seek = [&]() {  // moves p_tile to the next linear tile of this CTA's sequence
+    while (p_tile < ntiles) {
+      const uint32_t sg = find_segment(tile_begin, nseg, p_tile);
+      if (linear_span<DIR>(segs[sg], p_tile - tile_begin[sg], image, &p_lt)) return;
+      p_tile += gridDim.x;
+    }
+  };
+  if (tid == 0) seek();
+
+  uint32_t consumed = 0;
+  uint32_t cached = 0xffffffffu;
+  bool aborted = false;
+  for (uint32_t tile = blockIdx.x; tile < ntiles && !aborted; tile += gridDim.x) {
+    const uint32_t sg = find_segment(tile_begin, nseg, tile);
+    const uint32_t local = tile - tile_begin[sg];
+    LinearTile lt;
+    if (linear_span<DIR>(segs[sg], local, image, &lt)) {
+      for (uint32_t st = 0; st < lt.nstage; ++st) {
+        if (tid == 0) {
+          // keep the ring full: slot (issued % kStages) was released by the barrier that ended
+          // stage (issued - kStages)
+          while (issued < consumed + mlf::kStages && p_tile < ntiles) {
+            const uint64_t off = (uint64_t)p_stage * mlf::kStageBytes;
+            const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, p_lt.len - off);
+            const uint8_t* src = p_lt.src + off;
+            const uint32_t shift = (uint32_t)((uintptr_t)src & 15u);
+            const uint32_t bytes = (shift + slen + 15u) & ~15u;
+            const uint32_t slot = issued % mlf::kStages;
+            mlf::mbar_expect_tx(&full[slot], bytes);
+            mlf::bulk_load(ring + (size_t)slot * mlf::kSlotBytes, src - shift, bytes, &full[slot]);
+            ++issued;
+            if (++p_stage == p_lt.nstage) {
+              p_stage = 0;
+              p_tile += gridDim.x;
+              seek();
+            }
+          }
+        }
+        const uint32_t slot = consumed % mlf::kStages;
+        const bool ok = mlf::mbar_wait_bounded(&full[slot], (consumed / mlf::kStages) & 1u);
+        if (ok) {
+          const uint64_t off = (uint64_t)st * mlf::kStageBytes;
+          const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, lt.len - off);
+          const uint32_t shift = (uint32_t)((uintptr_t)(lt.src + off) & 15u);
+          mlf::drain_slot(lt.dst + off, ring + (size_t)slot * mlf::kSlotBytes, shift, slen, tid, blockDim.x);
+        } else {
+          abort_flag = 1;
+        }
+        __syncthreads();  // slot is free again; also publishes abort_flag
+        ++consumed;
+        if (abort_flag) {
+          aborted = true;
+          break;
+        }
+      }
+      continue;
+    }
+    if (sg != cached) {
+      __syncthreads();
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + sg);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
+      for (uint32_t w = tid; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
+      __syncthreads();
+      cached = sg;
+    }
+    if (g.kind == kRows) {
+      rows_tile<DIR>(g, local, image);
+    } else if (g.kind == kTranspose) {
+      switch (g.esize) {
+        case 1: transpose_tile<uint8_t, DIR>(g, local, image, tsmem); break;
+        case 2: transpose_tile<uint16_t, DIR>(g, local, image, tsmem); break;
+        case 4: transpose_tile<uint32_t, DIR>(g, local, image, tsmem); break;
+        default: transpose_tile<uint64_t, DIR>(g, local, image, tsmem); break;
+      }
+    } else {
+      switch (g.esize) {
+        case 1: generic_tile<uint8_t, DIR>(g, local, image); break;
+        case 2: generic_tile<uint16_t, DIR>(g, local, image); break;
+        case 4: generic_tile<uint32_t, DIR>(g, local, image); break;
+        default: generic_tile<uint64_t, DIR>(g, local, image); break;
+      }
+    }
+  }
+  if (aborted && tid == 0) {
+    atomicCAS(status, 0, MLF_ERR_TIMEOUT);
+    // the CTA may not exit while bulk copies still target its shared memory: wait for them too,
+    // again with a budget
+    for (uint32_t n = consumed; n < issued; ++n) (void)mlf::mbar_wait_bounded(&full[n % mlf::kStages], (n / mlf::kStages) & 1u);
+  }
+}
+
+constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
+
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
                                                                  const uint8_t* __restrict__ src, uint64_t nbytes) {
   const uint64_t mis = (uint64_t)((uintptr_t)dst & 127u);
@@ -273,11 +450,11 @@ __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __rest
 // Grid for a persistent launch of `kernel`: one full wave (SMs x resident CTAs per SM), capped by
 // the tile count and by the caller's limit.
 template <typename K>
-int32_t wave_grid(K kernel, int32_t max_ctas, uint64_t ntiles, uint32_t* grid) {
+int32_t wave_grid(K kernel, int32_t max_ctas, uint64_t ntiles, uint32_t* grid, size_t dyn_smem = 0) {
   int dev = 0, sms = 0, per_sm = 0;
   MLF_CUDA(cudaGetDevice(&dev));
   MLF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  MLF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int)kThreads, 0));
+  MLF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int)kThreads, dyn_smem));
   uint64_t g = (uint64_t)sms * (uint64_t)std::max(per_sm, 1);
   if (max_ctas > 0) g = std::min<uint64_t>(g, (uint64_t)max_ctas);
   g = std::max<uint64_t>(1, std::min<uint64_t>(g, ntiles));
@@ -310,6 +487,16 @@ Canon canonicalise(uint32_t esize, const int64_t* shape, const int64_t* ts_elems
     }
   }
   return c;
+}
+
+// Kernel variant for plan launches: the bulk-copy staged kernel unless MLF_PLAN_KERNEL=ldg asks for
+// the register-staged one (kept for comparison and for mlf_pack_noalloc).
+bool use_bulk_kernel() {
+  static const bool bulk = []() {
+    const char* v = getenv("MLF_PLAN_KERNEL");
+    return !(v && std::string(v) == "ldg");
+  }();
+  return bulk;
 }
 
 // ---- scratch of mlf_pack_noalloc ---------------------------------------------------------
@@ -536,16 +723,35 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
   if (p->ntiles == 0) return MLF_OK;
   if (!image_base) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_launch: null image");
   uint32_t grid = 1;
-  int32_t rc = p->direction == MLF_PACK ? wave_grid(mlf_plan_kernel<MLF_PACK>, max_ctas, p->ntiles, &grid)
-                                        : wave_grid(mlf_plan_kernel<MLF_UNPACK>, max_ctas, p->ntiles, &grid);
-  if (rc != MLF_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (p->direction == MLF_PACK)
-    mlf_plan_kernel<MLF_PACK><<<grid, kThreads, 0, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles,
-                                                        static_cast<uint8_t*>(image_base));
-  else
-    mlf_plan_kernel<MLF_UNPACK><<<grid, kThreads, 0, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles,
-                                                          static_cast<uint8_t*>(image_base));
+  uint8_t* image = static_cast<uint8_t*>(image_base);
+  if (use_bulk_kernel()) {
+    auto pack = mlf_plan_kernel_bulk<MLF_PACK>;
+    auto unpack = mlf_plan_kernel_bulk<MLF_UNPACK>;
+    static std::once_flag opted_in;
+    static cudaError_t opt_status = cudaSuccess;
+    std::call_once(opted_in, [&]() {
+      opt_status = cudaFuncSetAttribute(pack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
+      if (opt_status == cudaSuccess)
+        opt_status = cudaFuncSetAttribute(unpack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
+    });
+    MLF_CUDA(opt_status);
+    int32_t rc = p->direction == MLF_PACK ? wave_grid(pack, max_ctas, p->ntiles, &grid, kBulkDynSmem)
+                                          : wave_grid(unpack, max_ctas, p->ntiles, &grid, kBulkDynSmem);
+    if (rc != MLF_OK) return rc;
+    if (p->direction == MLF_PACK)
+      pack<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image, p->d_status);
+    else
+      unpack<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image, p->d_status);
+  } else {
+    int32_t rc = p->direction == MLF_PACK ? wave_grid(mlf_plan_kernel<MLF_PACK>, max_ctas, p->ntiles, &grid)
+                                          : wave_grid(mlf_plan_kernel<MLF_UNPACK>, max_ctas, p->ntiles, &grid);
+    if (rc != MLF_OK) return rc;
+    if (p->direction == MLF_PACK)
+      mlf_plan_kernel<MLF_PACK><<<grid, kThreads, 0, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image);
+    else
+      mlf_plan_kernel<MLF_UNPACK><<<grid, kThreads, 0, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image);
+  }
   MLF_CUDA(cudaGetLastError());
   mlf::g_launches.fetch_add(1);
   return MLF_OK;

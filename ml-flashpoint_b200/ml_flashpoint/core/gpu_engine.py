@@ -74,6 +74,20 @@ class ObjectLayout:
         return sum(len(c.data) for c in self.host_chunks)
 
 
+_HEADER_CACHE: dict = {}
+
+
+def _header_bytes(dtype: torch.dtype, shape: torch.Size) -> bytes:
+    """Pickled header for (dtype, shape); identical inputs pickle to identical bytes, so cache them."""
+    key = (dtype, tuple(shape))
+    cached = _HEADER_CACHE.get(key)
+    if cached is None:
+        if len(_HEADER_CACHE) > 65536:
+            _HEADER_CACHE.clear()
+        cached = _HEADER_CACHE[key] = TensorHeader(dtype=dtype, shape=shape).to_bytes()
+    return cached
+
+
 def plan_object_layout(
     tensor_items: Sequence[Tuple[Any, torch.Tensor]],
     bytes_items: Sequence[Tuple[Any, Any]],
@@ -91,7 +105,7 @@ def plan_object_layout(
     payload_total = 0
     for item, tensor in tensor_items:
         begin = pos
-        header = TensorHeader(dtype=tensor.dtype, shape=tensor.shape).to_bytes()
+        header = _header_bytes(tensor.dtype, tensor.shape)
         chunks.append(HostChunk(pos, header))
         pos += len(header)
         nbytes = tensor.numel() * tensor.element_size()
@@ -154,10 +168,8 @@ class _PinnedBlob:
         self.ptr = int(ptr.value)
 
     def fill(self, chunks: Sequence[HostChunk]) -> None:
-        at = self.ptr
-        for c in chunks:
-            ctypes.memmove(at, c.data, len(c.data))
-            at += len(c.data)
+        packed = b"".join(c.data for c in chunks)
+        ctypes.memmove(self.ptr, packed, len(packed))
 
     def __del__(self):
         try:
@@ -481,12 +493,14 @@ class CudaCopyEngine:
                     raise ValueError(f"target lives on {target.device}, engine on {self.device}")
                 fill_desc(descs[k], dev_target.data_ptr(), first - lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
             plan = _Plan(descs, len(prepared), _native.MLF_UNPACK)
+            t_launch = torch.cuda.Event(enable_timing=True)
+            t_launch.record(stream)
             plan.launch(image.data_ptr(), hi - lo, stream.cuda_stream)
             done = torch.cuda.Event(enable_timing=True)
             done.record(stream)
             done.synchronize()
             plan.status()
-            self.last_unpack_ms = (t_begin.elapsed_time(t_copied), t_copied.elapsed_time(done))
+            self.last_unpack_ms = (t_begin.elapsed_time(t_copied), t_launch.elapsed_time(done))
             for target, dev_target in host_targets:
                 target.copy_(dev_target)
             # later work on the caller's stream must see the restored values
