@@ -185,10 +185,14 @@ def world():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
+def _collective_device(device):
+    return torch.device("cpu") if dist.get_backend() == "gloo" else device
+
+
 def all_max(value: float, device) -> float:
     if not dist.is_initialized():
         return value
-    t = torch.tensor([value], dtype=torch.float64, device=device)
+    t = torch.tensor([value], dtype=torch.float64, device=_collective_device(device))
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
@@ -196,7 +200,7 @@ def all_max(value: float, device) -> float:
 def all_sum(value: float, device) -> float:
     if not dist.is_initialized():
         return value
-    t = torch.tensor([value], dtype=torch.float64, device=device)
+    t = torch.tensor([value], dtype=torch.float64, device=_collective_device(device))
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t.item())
 
@@ -268,8 +272,10 @@ def main() -> None:
     ap.add_argument("--mode", default=None, choices=[None, "staged", "direct"], help="pack destination (default: staged)")
     ap.add_argument("--no-restore", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-replication", action="store_true")
     ap.add_argument("--cpu-sample-gb", type=float, default=2.0)
     ap.add_argument("--workdir", default=None)
+    ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "mlf_b200" and args.layers == 32:
         args.warmup = max(args.warmup, 1)
@@ -278,9 +284,17 @@ def main() -> None:
     if world_size > 1:
         if args.impl == "reference" and rank != 0:
             return  # the CPU arm runs on rank 0 alone
-        if args.impl != "reference":
+        if args.impl != "reference" and args.share_gpu:
+            local_rank = 0
+            dist.init_process_group("gloo")
+        elif args.impl != "reference":
             torch.cuda.set_device(local_rank)
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            import datetime
+
+            # a rank that fails must not leave the others waiting for the default 10 minutes
+            dist.init_process_group(
+                "nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=240)
+            )
     device = torch.device("cuda", local_rank if torch.cuda.is_available() else 0)
     if torch.cuda.is_available():
         torch.cuda.set_device(device)
@@ -294,10 +308,19 @@ def main() -> None:
             run_reference_arm(args, device, workdir)
         else:
             run_native_arm(args, rank, world_size, device, workdir)
-    finally:
+    except BaseException:
+        # a failed rank must exit at once so that the launcher stops the others instead of letting
+        # them wait in a collective
+        import traceback
+
+        traceback.print_exc()
         shutil.rmtree(workdir, ignore_errors=True)
-        if dist.is_initialized():
-            dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(1)
+    shutil.rmtree(workdir, ignore_errors=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
 
 
 def run_reference_arm(args, device, workdir: str) -> None:
@@ -360,6 +383,99 @@ def workload_config(args, payload_bytes: int) -> dict:
     }
 
 
+def run_replication(args, rank, world_size, device, workdir, com, saver, engine, items, resolver, shard, one_save, state):
+    """Replicates the last saved object of every rank to rank (r + 1) mod N, all ranks at once.
+
+    Uses the full object when /dev/shm can hold a second copy per rank, otherwise a prefix of the
+    shard saved as an object of its own (and says so). Returns throughput of the whole replication
+    (object in the partner's file) and of the GPU-to-GPU hop alone (NVLink roofline)."""
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+    from ml_flashpoint.replication import replication_manager as rm
+    from ml_flashpoint.replication.transfer_service.transfer_service_ext import TransferService
+
+    replica_root = os.path.join(workdir, "replicas")
+
+    def mapper(object_id, source_rank):
+        return os.path.join(replica_root, f"src{source_rank}", object_id.lstrip("/"))
+
+    service = TransferService(replica_path_mapper=mapper)
+    if service.initialize(0, threads=4, global_rank=rank) <= 0:
+        raise RuntimeError("transfer service failed to start")
+    addresses = [None] * world_size
+    dist.all_gather_object(addresses, service.address)
+    manager = rm.ReplicationManager()
+    manager.initialize(com, replication_transfer_service=service, repl_strategy=rm.RingReplicationStrategy(addresses))
+
+    # how much may be replicated: every rank lands one more copy in the shared tmpfs
+    stat = os.statvfs(workdir)
+    free = stat.f_bavail * stat.f_frsize
+    full = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
+    budget = int(0.8 * free / world_size)
+    note = "full object"
+    sub_items = items
+    if full > budget:
+        picked, total = [], 0
+        for wi in items:
+            t = resolver.resolve_data(wi)
+            n = t.numel() * t.element_size()
+            if total + n > budget and picked:
+                break
+            picked.append(wi)
+            total += n
+        sub_items = picked
+        note = f"prefix of the shard ({total / 1e9:.2f} of {full / 1e9:.2f} GB): tmpfs cannot hold a second full copy per rank"
+    times, hops = [], []
+    error = None
+    for i in range(3):
+        if state["prev"] is not None:
+            com.delete_container(state["prev"])
+        ckpt = CheckpointContainerId(os.path.join(workdir, "ckpt", f"step-{state['step']}_ckpt"))
+        state["step"] += 1
+        state["prev"] = ckpt
+        saver.initialize_checkpoint(ckpt)
+        buckets = saver.prepare_write_data(ckpt, sub_items, resolver, f"__{rank}_", bucket_count=1)
+        saver.write_data(ckpt, buckets, replicate_after_write=False, thread_count=1)
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        try:
+            futures = manager.async_replicate(com.get_buffer(buckets[0].object_id))
+            for f in futures:
+                f.result(timeout=200)
+        except Exception as e:  # keep the collectives below symmetric; report instead of dying
+            error = f"{type(e).__name__}: {e}"
+        dt = time.perf_counter() - t0
+        barrier()
+        if i and error is None:  # first round opens IPC handles and allocates landing buffers
+            times.append(dt)
+            hops.append(service.last_put_stats)
+        shutil.rmtree(replica_root, ignore_errors=True)  # the partner's copy of the previous round
+        barrier()
+    object_bytes = os.path.getsize(str(buckets[0].object_id))
+    failed = all_max(0.0 if error is None else 1.0, device)
+    service.release_peers()  # importers close first ...
+    barrier()
+    manager.shutdown()  # ... then exporters free their landing buffers
+    if failed:
+        return {"error": error or "a peer rank failed", "what": note}
+    slow = all_max(statistics.mean(times), device)
+    hop_ms = all_max(statistics.mean(h["hop_ms"] for h in hops), device)
+    total_bytes = all_sum(object_bytes, device)
+    return {
+        "e2e_value": total_bytes / 1e9 / slow,
+        "unit": UNIT,
+        "ms": slow * 1e3,
+        "object_bytes_per_rank": object_bytes,
+        "what": note,
+        "nvlink_hop_ms": hop_ms,
+        "nvlink_hop_gbs_per_gpu": object_bytes / 1e9 / (hop_ms / 1e3),
+        "nvlink_frac_of_900": object_bytes / 1e9 / (hop_ms / 1e3) / 900.0,
+        "nvlink_frac_of_measured_770": object_bytes / 1e9 / (hop_ms / 1e3) / 770.0,
+        "source": "HBM image of the save" if hops[-1]["from_hbm_image"] else "host mapping via bounce ring",
+        "partner": "(rank + 1) mod N",
+    }
+
+
 def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> None:
     import ctypes
 
@@ -378,6 +494,7 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
     payload = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
     items, resolver = write_items_for(shard)
     engine = gpu_engine.CudaCopyEngine(device=device, mode=args.mode)
+    gpu_engine.set_default_engine(engine)  # replication looks the HBM image up through the process-wide engine
 
     # size the pool buffer exactly: header sizes are known without touching the GPU
     layout = gpu_engine.plan_object_layout([(None, t) for _, t, _, _ in shard], [])
@@ -502,6 +619,11 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
         # the oracle's metadata block carries the sample's length; compare the data section prefix
         parity = got[METADATA_SIZE:] == want[METADATA_SIZE:]
 
+    # ---- replication to the ring partner (only where there is a partner)
+    replication = None
+    if world_size > 1 and not args.no_replication:
+        replication = run_replication(args, rank, world_size, device, workdir, com, saver, engine, items, resolver, shard, one_save, state)
+
     total_payload = all_sum(payload, device)
     slow_device_s = all_max(sum(device_ms) / 1e3, device)
     slow_region_s = all_max(region_s, device)
@@ -545,6 +667,7 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
             "api": "DefaultMLFlashpointCheckpointSaver.write_data (object closed on return)",
         },
         "restore": restore,
+        "replication": replication,
         "roofline": {
             "kernel": "mlf_plan_kernel<PACK>",
             "bound": "hbm",

@@ -539,6 +539,13 @@ def default_engine() -> CudaCopyEngine:
         return _default_engine
 
 
+def set_default_engine(engine: Optional[CudaCopyEngine]) -> None:
+    """Makes ``engine`` the process-wide engine (for callers that configure their own)."""
+    global _default_engine
+    with _default_engine_lock:
+        _default_engine = engine
+
+
 def resident_image(object_id: str, nbytes: int) -> Optional[_ResidentLease]:
     """``CudaCopyEngine.resident_image`` of the process-wide engine, or None if there is no engine yet."""
     engine = _default_engine

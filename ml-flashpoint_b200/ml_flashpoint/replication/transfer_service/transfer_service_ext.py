@@ -123,6 +123,8 @@ class TransferService:
         self._opened_ipc: Dict[str, int] = {}
         self._bounce: Optional[_DeviceBuffer] = None
         self._stream = ctypes.c_void_p()
+        # device timing of the most recent outgoing transfer: {"bytes", "hop_ms", "from_hbm_image"}
+        self.last_put_stats: Optional[dict] = None
 
     # ------------------------------------------------------------------ lifecycle
     def initialize(self, listen_port: int = 0, threads: int = 16, conn_pool_per_peer: int = 16, global_rank: int = -1) -> int:
@@ -158,6 +160,17 @@ class TransferService:
     @property
     def address(self) -> str:
         return f"{self._host}:{self._port}"
+
+    def release_peers(self) -> None:
+        """Closes the landing buffers of other processes that this service has opened.
+
+        An exporter may free a buffer only after every importer has closed it, so ranks that shut
+        down together call this first, synchronise, and then ``shutdown``."""
+        _native.lib().mlf_set_device(self._device)
+        with self._lock:
+            opened, self._opened_ipc = self._opened_ipc, {}
+        for ptr in opened.values():
+            _native.lib().mlf_ipc_close(ctypes.c_void_p(ptr))
 
     def shutdown(self) -> None:
         """Stops accepting, fails every pending future, releases device buffers."""
@@ -234,7 +247,9 @@ class TransferService:
         last = None
         for _ in range(5):  # the reference retries connects 5 times, 100 ms apart
             try:
-                return socket.create_connection((host, port), timeout=30.0)
+                conn = socket.create_connection((host, port), timeout=30.0)
+                conn.settimeout(300.0)  # the peer answers only after draining the whole object to its file
+                return conn
             except OSError as e:
                 last = e
                 threading.Event().wait(0.1)
@@ -268,22 +283,36 @@ class TransferService:
             peer = self._peer_pointer(reply)
             stream = self._stream
             twin = None if exact_path else gpu_engine.resident_image(dest_object_id, data_size - METADATA_SIZE)
-            if twin is not None:
-                # metadata block from the host mapping, data section from the HBM image of the save
-                with twin as image_ptr:
-                    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(peer), ctypes.c_void_p(data_ptr), METADATA_SIZE, _native.MLF_COPY_H2D, stream))
-                    _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer + METADATA_SIZE), ctypes.c_void_p(image_ptr), data_size - METADATA_SIZE, stream, 0))
+            t0, t1 = ctypes.c_void_p(), ctypes.c_void_p()
+            _native.check(lib.mlf_event_create(ctypes.byref(t0)))
+            _native.check(lib.mlf_event_create(ctypes.byref(t1)))
+            try:
+                if twin is not None:
+                    # metadata block from the host mapping, data section from the HBM image of the save
+                    with twin as image_ptr:
+                        _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(peer), ctypes.c_void_p(data_ptr), METADATA_SIZE, _native.MLF_COPY_H2D, stream))
+                        _native.check(lib.mlf_event_record(t0, stream))
+                        _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer + METADATA_SIZE), ctypes.c_void_p(image_ptr), data_size - METADATA_SIZE, stream, 0))
+                        _native.check(lib.mlf_event_record(t1, stream))
+                        _native.check(lib.mlf_stream_sync(stream))
+                else:
+                    with self._lock:
+                        if self._bounce is None or self._bounce.nbytes < data_size:
+                            if self._bounce:
+                                self._bounce.free()
+                            self._bounce = _DeviceBuffer(data_size)
+                        bounce = self._bounce
+                    _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(bounce.ptr), ctypes.c_void_p(data_ptr), data_size, 1, 0))
+                    _native.check(lib.mlf_event_record(t0, stream))
+                    _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer), ctypes.c_void_p(bounce.ptr), data_size, stream, 0))
+                    _native.check(lib.mlf_event_record(t1, stream))
                     _native.check(lib.mlf_stream_sync(stream))
-            else:
-                with self._lock:
-                    if self._bounce is None or self._bounce.nbytes < data_size:
-                        if self._bounce:
-                            self._bounce.free()
-                        self._bounce = _DeviceBuffer(data_size)
-                    bounce = self._bounce
-                _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(bounce.ptr), ctypes.c_void_p(data_ptr), data_size, _native.MLF_COPY_H2D, stream))
-                _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer), ctypes.c_void_p(bounce.ptr), data_size, stream, 0))
-                _native.check(lib.mlf_stream_sync(stream))
+                ms = ctypes.c_float()
+                _native.check(lib.mlf_event_elapsed_ms(t0, t1, ctypes.byref(ms)))
+                self.last_put_stats = {"bytes": data_size, "hop_ms": float(ms.value), "from_hbm_image": twin is not None}
+            finally:
+                lib.mlf_event_destroy(t0)
+                lib.mlf_event_destroy(t1)
             _send_msg(sock, {"op": "put_commit", "token": reply["token"]})
             final = _recv_msg(sock)
             if not final.get("ok"):
@@ -305,7 +334,7 @@ class TransferService:
                 continue
             except OSError:
                 return
-            conn.settimeout(60.0)
+            conn.settimeout(300.0)
             try:
                 self._workers.submit(self._serve, conn)
             except RuntimeError:
@@ -354,13 +383,9 @@ class TransferService:
             tmp_path = final_path + ".tmp"
             target = BufferObject(tmp_path, size, overwrite=True)
             try:
-                stream = ctypes.c_void_p()
-                _native.check(lib.mlf_stream_create(ctypes.byref(stream)))
-                try:
-                    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(target.get_data_ptr()), ctypes.c_void_p(landing.ptr), size, _native.MLF_COPY_D2H, stream))
-                    _native.check(lib.mlf_stream_sync(stream))
-                finally:
-                    lib.mlf_stream_destroy(stream)
+                # the fresh file is pageable: drain through the bounce ring, whose CPU threads also
+                # fault the new tmpfs pages in parallel
+                _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(landing.ptr), ctypes.c_void_p(target.get_data_ptr()), size, 0, 0))
             finally:
                 target.close()
             os.rename(tmp_path, final_path)
