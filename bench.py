@@ -38,6 +38,10 @@ import torch.distributed as dist  # noqa: E402
 METRIC = "checkpoint_save_throughput"
 UNIT = "GB/s"
 FSDP_WORLD = 8  # the named configuration shards the model 8 ways whatever --gpus is
+# DRAM bytes (read + write) per payload byte of the pack kernel, from the ncu capture summarised in
+# profiles/mlf_plan_kernel_bulk__llama3_8b_shard_2layers.md (5.154 GB for 2.602 GB of payload);
+# traffic grows in proportion to the payload, so a full launch is this ratio times its payload.
+NCU_DRAM_BYTES_PER_PAYLOAD_BYTE = 1.981
 
 
 # --------------------------------------------------------------------------------------
@@ -678,7 +682,8 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
             "peak_source": peak_src,
             "algorithmic_bytes_per_launch": 2 * payload,
             "kernel_ms": statistics.mean(kernel_ms),
-            "traffic": None,
+            "traffic": NCU_DRAM_BYTES_PER_PAYLOAD_BYTE * payload,
+            "traffic_source": "ncu capture of a 2.6 GB case scaled by payload bytes",
         },
         "host_link": {
             "d2h_gbs": (
