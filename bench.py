@@ -402,7 +402,16 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
     def mapper(object_id, source_rank):
         return os.path.join(replica_root, f"src{source_rank}", object_id.lstrip("/"))
 
-    service = TransferService(replica_path_mapper=mapper)
+    # how much may be replicated: every rank lands one more copy in the shared tmpfs
+    stat = os.statvfs(workdir)
+    free = stat.f_bavail * stat.f_frsize
+    full = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
+    budget = int(0.8 * free / world_size)
+    from ml_flashpoint.core.buffer_pool import BufferPool
+
+    # replicas land in a page-locked pool file of their own, like primaries do
+    landing_pool = BufferPool(os.path.join(workdir, "replica_pool"), rank, 1, min(full, budget) + (1 << 20), register_cuda=True)
+    service = TransferService(replica_path_mapper=mapper, landing_pool=landing_pool)
     if service.initialize(0, threads=4, global_rank=rank) <= 0:
         raise RuntimeError("transfer service failed to start")
     addresses = [None] * world_size
@@ -410,11 +419,6 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
     manager = rm.ReplicationManager()
     manager.initialize(com, replication_transfer_service=service, repl_strategy=rm.RingReplicationStrategy(addresses))
 
-    # how much may be replicated: every rank lands one more copy in the shared tmpfs
-    stat = os.statvfs(workdir)
-    free = stat.f_bavail * stat.f_frsize
-    full = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
-    budget = int(0.8 * free / world_size)
     note = "full object"
     sub_items = items
     if full > budget:
@@ -460,6 +464,7 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
     service.release_peers()  # importers close first ...
     barrier()
     manager.shutdown()  # ... then exporters free their landing buffers
+    landing_pool.teardown()
     if failed:
         return {"error": error or "a peer rank failed", "what": note}
     slow = all_max(statistics.mean(times), device)

@@ -156,6 +156,17 @@ class BufferPool:
                 self.free_buffers.append(candidate)
                 raise
 
+    def relink(self, buffer_io, old_symlink: str, new_symlink: str) -> None:
+        """Renames the link that keeps ``buffer_io`` in use and records the new name, atomically with
+        respect to garbage collection (objects received from a peer are written under a temporary
+        name and renamed when complete)."""
+        inner = getattr(buffer_io, "_buffer_io", buffer_io)
+        path = inner.buffer_obj.get_id()
+        with self._lock:
+            os.rename(old_symlink, new_symlink)
+            if path in self.active_buffers:
+                self.active_buffers[path] = (inner, new_symlink)
+
     def _gc(self) -> None:
         """Frees every active buffer whose symlink is gone or dangling."""
         # exists(), not lexists(): a link whose target vanished counts as gone too

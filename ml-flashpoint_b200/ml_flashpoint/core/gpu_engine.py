@@ -155,6 +155,14 @@ def fill_desc(
         desc.image_stride[d] = int(image_stride[d])
 
 
+def default_host_threads() -> int:
+    """CPU threads for the bounce ring: half the cores, shared between the ranks on this host."""
+    import os
+
+    local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))
+    return max(2, (os.cpu_count() or 2) // 2 // local_world)
+
+
 # ======================================================================================
 # CUDA engine
 # ======================================================================================
@@ -261,7 +269,7 @@ class CudaCopyEngine:
             raise ValueError(f"unknown pack mode '{self.mode}' (expected 'staged' or 'direct')")
         self.host_ctas = get_env_val_int("GPU_HOST_CTAS", 32)
         # CPU threads feeding the bounce ring when host memory is not page-locked (0 = half the cores)
-        self.host_threads = get_env_val_int("GPU_HOST_THREADS", 0)
+        self.host_threads = get_env_val_int("GPU_HOST_THREADS", default_host_threads())
         self._lock = threading.RLock()
         self._cache: "OrderedDict[tuple, _CachedPack]" = OrderedDict()
         self._cache_size = plan_cache_size

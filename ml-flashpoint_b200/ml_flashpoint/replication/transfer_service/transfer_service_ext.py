@@ -102,12 +102,17 @@ class _DeviceBuffer:
 
 
 class TransferService:
-    def __init__(self, replica_path_mapper: Optional[Callable[[str, int], str]] = None):
+    def __init__(self, replica_path_mapper: Optional[Callable[[str, int], str]] = None, landing_pool=None):
         """``replica_path_mapper(object_id, source_rank) -> path`` decides where a received object is
         stored. The default keeps the sender's path, which is right when peers have separate
         filesystems; ranks that share one must map replicas elsewhere or they would overwrite the
-        primary copy."""
+        primary copy.
+
+        ``landing_pool`` is an optional ``BufferPool`` of page-locked files: received objects are then
+        drained into a pool file by one copy-engine transfer (and appear as a symlink to it, like
+        objects saved through the pool) instead of into a fresh pageable file."""
         self._map_path = replica_path_mapper or (lambda object_id, source_rank: object_id)
+        self._landing_pool = landing_pool
         self._listener: Optional[socket.socket] = None
         self._accept_thread: Optional[threading.Thread] = None
         self._workers: Optional[concurrent.futures.ThreadPoolExecutor] = None
@@ -381,14 +386,40 @@ class TransferService:
                 raise RuntimeError("put was not committed by the sender")
             final_path = request["obj"] if request.get("exact_path") else self._map_path(request["obj"], source)
             tmp_path = final_path + ".tmp"
-            target = BufferObject(tmp_path, size, overwrite=True)
-            try:
-                # the fresh file is pageable: drain through the bounce ring, whose CPU threads also
-                # fault the new tmpfs pages in parallel
-                _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(landing.ptr), ctypes.c_void_p(target.get_data_ptr()), size, 0, 0))
-            finally:
-                target.close()
-            os.rename(tmp_path, final_path)
+            os.makedirs(os.path.dirname(final_path), exist_ok=True)
+            for stale in (tmp_path, final_path):
+                if os.path.lexists(stale):
+                    os.remove(stale)
+            pooled = None
+            if self._landing_pool is not None:
+                try:
+                    pooled = self._landing_pool.acquire(associated_symlink=tmp_path)
+                except RuntimeError:
+                    pooled = None  # pool exhausted: fall back to a plain file
+            if pooled is not None:
+                pooled.ensure_total_size(size)
+                inner = pooled._buffer_io
+                stream = ctypes.c_void_p()
+                _native.check(lib.mlf_stream_create(ctypes.byref(stream)))
+                try:
+                    host = inner.buffer_obj.get_data_ptr()
+                    if inner.buffer_obj.is_cuda_registered:
+                        _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(host), ctypes.c_void_p(landing.ptr), size, _native.MLF_COPY_D2H, stream))
+                        _native.check(lib.mlf_stream_sync(stream))
+                    else:
+                        _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(landing.ptr), ctypes.c_void_p(host), size, 0, 0))
+                finally:
+                    lib.mlf_stream_destroy(stream)
+                self._landing_pool.relink(pooled, tmp_path, final_path)
+            else:
+                target = BufferObject(tmp_path, size, overwrite=True)
+                try:
+                    # the fresh file is pageable: drain through the bounce ring, whose CPU threads also
+                    # fault the new tmpfs pages in parallel
+                    _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(landing.ptr), ctypes.c_void_p(target.get_data_ptr()), size, 0, 0))
+                finally:
+                    target.close()
+                os.rename(tmp_path, final_path)
         _send_msg(conn, {"ok": True})
 
     def _serve_get(self, conn: socket.socket, request: dict) -> None:

@@ -1,0 +1,133 @@
+"""The benchmark's other configurations as parity cases on the GPU.
+
+Small variants are compared byte for byte with the CPU oracle; the full-size packing microbench
+(1 024 tensors, up to 8 GiB) is checked through size-independent properties: record arithmetic,
+bit-exact save -> restore round trip, and oracle bytes for a random sample of its tensors."""
+
+import os
+import random
+
+import pytest
+import torch
+from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+import cases
+import mlf_oracle as oracle
+import workloads
+from helpers import make_loader, make_saver, tensor_bytes
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def engine():
+    from ml_flashpoint.core.gpu_engine import CudaCopyEngine
+
+    return CudaCopyEngine(mode="staged")
+
+
+def _save(case, root, engine, pool_bytes=None):
+    from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
+    from ml_flashpoint.core.buffer_pool import BufferPoolConfig
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+
+    CheckpointObjectManager._worker_pool = None
+    cfg = BufferPoolConfig(str(root / "pool"), 0, 1, pool_bytes, register_cuda=True) if pool_bytes else None
+    saver, com = make_saver(copy_engine=engine, pool_config=cfg, initial_buffer_size_bytes=64 << 20)
+    ckpt = CheckpointContainerId(str(root / "step-1_ckpt"))
+    saver.initialize_checkpoint(ckpt)
+    items, resolver = cases.write_items_and_resolver(case)
+    buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=1)
+    results = saver.write_data(ckpt, buckets, replicate_after_write=False)
+    return com, buckets, results
+
+
+def _restore_all(com, engine, buckets, results, case):
+    loader = make_loader(com, copy_engine=engine)
+    storage = {r.index: r.storage_data for r in results}
+    by_fqn = {r.index.fqn: r.index for r in results}
+    targets = {}
+    reqs = []
+    for fqn, t in case["tensors"].items():
+        if t.numel() == 0:
+            continue
+        targets[fqn] = torch.zeros(t.shape, dtype=t.dtype, device=t.device)
+        idx = by_fqn[fqn]
+        reqs.append(ReadItem(LoadItemType.TENSOR, idx, torch.Size([0] * t.dim()), idx, torch.Size([0] * t.dim()), torch.Size(t.shape)))
+
+    class _Planner:
+        def resolve_tensor(self, req):
+            return targets[req.dest_index.fqn]
+
+        def commit_tensor(self, req, tensor):
+            pass
+
+    loader.read_data(buckets[0].object_id, reqs, _Planner(), storage)
+    torch.cuda.synchronize()
+    return targets
+
+
+def _oracle_bytes(case):
+    cpu = {"tensors": {k: v.cpu() for k, v in case["tensors"].items()}, "blobs": case["blobs"], "bucket_count": 1}
+    ((_, data, _),) = oracle.save_case(cpu)
+    return data
+
+
+@pytest.mark.parametrize("make", [
+    lambda: workloads.moe_expert_parallel_rank("cuda", rank=3),
+    lambda: workloads.tensor_parallel_rank("cuda", rank=5, as_views=True),
+    lambda: workloads.tensor_parallel_rank("cuda", rank=2, as_views=False),
+    lambda: {"tensors": workloads.packing_microbench("cuda", count=96, max_bytes=1 << 20, cap_bytes=48 << 20), "blobs": {}, "bucket_count": 1},
+], ids=["moe_ep_rank_small_objects", "megatron_tp_views", "megatron_tp_contiguous", "packing_microbench_scaled"])
+def test_configuration_objects_match_oracle(make, shm_path, engine):
+    case = make()
+    com, buckets, results = _save(case, shm_path, engine)
+    with open(str(buckets[0].object_id), "rb") as f:
+        got = f.read()
+    want = _oracle_bytes(case)
+    if got != want:
+        first = next(i for i in range(min(len(got), len(want))) if got[i] != want[i])
+        pytest.fail(f"object differs from oracle at byte {first} (sizes {len(got)} vs {len(want)})")
+    restored = _restore_all(com, engine, buckets, results, case)
+    for fqn, t in restored.items():
+        assert tensor_bytes(t) == tensor_bytes(case["tensors"][fqn]), fqn
+
+
+def test_packing_microbench_full_size_properties(shm_path, engine):
+    free = os.statvfs(str(shm_path)).f_bavail * os.statvfs(str(shm_path)).f_frsize
+    cap = 8 << 30
+    if free < cap + (1 << 30) or torch.cuda.mem_get_info()[0] < 3 * cap + (4 << 30):
+        cap = 1 << 30  # smaller box: same generator, smaller cap
+    tensors = workloads.packing_microbench("cuda", cap_bytes=cap)
+    case = {"tensors": tensors, "blobs": {}, "bucket_count": 1}
+    payload = sum(t.numel() * t.element_size() for t in tensors.values())
+    header_total = sum(len(oracle.header_bytes(str(t.dtype).split(".")[-1], tuple(t.shape))) for t in tensors.values())
+    assert any(not t.is_contiguous() for t in tensors.values())
+    com, buckets, results = _save(case, shm_path, engine, pool_bytes=4096 + payload + header_total)
+    path = str(buckets[0].object_id)
+    # records: back to back in plan order, no padding, file is exactly metadata + data
+    assert os.path.getsize(path) == 4096 + payload + header_total
+    pos = 0
+    by_fqn = {}
+    for r, (fqn, t) in zip(results, tensors.items()):
+        assert r.index.fqn == fqn and r.storage_data.offset == pos
+        pos += r.storage_data.length
+        by_fqn[fqn] = r.storage_data
+    assert pos == payload + header_total
+    # oracle bytes for a sample, transposed views included
+    rng = random.Random(5)
+    names = list(tensors)
+    sample = rng.sample(names, 24) + [n for n in names if not tensors[n].is_contiguous()][:8]
+    with open(path, "rb") as f:
+        for fqn in sample:
+            t = tensors[fqn]
+            info = by_fqn[fqn]
+            f.seek(4096 + info.offset)
+            got = f.read(info.length)
+            want = oracle.header_bytes(str(t.dtype).split(".")[-1], tuple(t.shape)) + oracle.tensor_payload(t.cpu())
+            assert got == want, fqn
+    # round trip
+    restored = _restore_all(com, engine, buckets, results, case)
+    for fqn, t in tensors.items():
+        assert torch.equal(restored[fqn], t), fqn
+    com.teardown_pool()

@@ -76,6 +76,34 @@ def test_put_then_get_round_trip(shm_path, services, resident):
     buf.close()
 
 
+def test_replica_lands_in_a_page_locked_pool_file(shm_path):
+    """With a landing pool the receiver drains by one copy-engine transfer into a pool file; the
+    replica is a symlink to it and frees the pool buffer when it is deleted."""
+    from ml_flashpoint.core import gpu_engine
+    from ml_flashpoint.core.buffer_pool import BufferPool
+    from ml_flashpoint.replication.transfer_service.transfer_service_ext import TransferService
+
+    pool = BufferPool(str(shm_path / "replica_pool"), rank=1, num_buffers=1, buffer_size=1 << 20, register_cuda=True)
+    replica = str(shm_path / "replicas" / "obj.distcp")
+    a, b = TransferService(), TransferService(replica_path_mapper=lambda obj, src: replica, landing_pool=pool)
+    a.initialize(0, threads=2, global_rank=0)
+    b.initialize(0, threads=2, global_rank=1)
+    try:
+        com, oid = _save_object(shm_path, gpu_engine.default_engine(), name="mixed")
+        primary = open(str(oid), "rb").read()
+        for _ in range(2):  # the second round reuses the pool buffer freed by deleting the replica
+            buf = com.get_buffer(oid)
+            assert a.async_put(buf.buffer_obj.get_data_ptr(), buf.buffer_obj.get_capacity(), b.address, str(oid)).result(timeout=60).success
+            buf.close()
+            assert os.path.islink(replica) and os.path.dirname(os.path.realpath(replica)) == os.path.realpath(pool.pool_dir)
+            assert open(replica, "rb").read() == primary
+            os.remove(replica)
+    finally:
+        a.shutdown()
+        b.shutdown()
+        pool.teardown()
+
+
 def test_failures_surface_on_the_future(shm_path, services):
     a, b, _ = services
     with socket.socket() as s:
