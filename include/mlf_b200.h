@@ -68,6 +68,12 @@ int32_t mlf_buf_is_readonly(const mlf_buf* b);
 int32_t mlf_buf_register(mlf_buf* b);
 int32_t mlf_buf_unregister(mlf_buf* b);
 int32_t mlf_buf_is_registered(const mlf_buf* b);
+/* Blocking read of object bytes [offset, offset + nbytes) into device memory, for mappings that are
+ * not page-locked (an object opened read-only after a restart cannot be): CPU threads pread() the
+ * file into a ring of page-locked slots while copy engines carry the previous chunks. Reading
+ * through the descriptor avoids faulting the whole object into the mapping. `nthreads` 0 = half
+ * the cores. */
+int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads);
 /* Device-visible address of byte 0 of the mapping (requires registration). */
 int32_t mlf_buf_dev_ptr(const mlf_buf* b, void** out);
 

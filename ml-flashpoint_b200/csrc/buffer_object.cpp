@@ -277,6 +277,19 @@ int32_t mlf_buf_unregister(mlf_buf* b) {
   return drop_registration(b);
 }
 
+int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads) {
+  if (!b) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_read_to_device: null buffer");
+  if (b->closed) return mlf::fail(MLF_ERR_CLOSED, "buffer is closed: " + b->id);
+  if (offset > b->capacity || nbytes > b->capacity - offset)
+    return mlf::fail(MLF_ERR_BOUNDS, "read of " + std::to_string(nbytes) + " bytes at " + std::to_string(offset) +
+                                         " leaves the object " + b->id);
+  if (b->registered) {  // page-locked already: one copy-engine transfer, no CPU copy
+    MLF_CUDA(cudaMemcpy(dev_ptr, static_cast<char*>(b->ptr) + offset, nbytes, cudaMemcpyHostToDevice));
+    return MLF_OK;
+  }
+  return mlf::bounce_transfer(dev_ptr, nullptr, b->fd, offset, nbytes, 1, nthreads);
+}
+
 int32_t mlf_buf_dev_ptr(const mlf_buf* b, void** out) {
   if (!b || !out) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_dev_ptr: null argument");
   *out = nullptr;

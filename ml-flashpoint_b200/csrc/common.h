@@ -20,6 +20,9 @@ void clear_error();
 
 extern std::atomic<uint64_t> g_launches;
 
+int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off, uint64_t nbytes, int32_t to_device,
+                        int32_t nthreads);
+
 inline int32_t cuda_fail(cudaError_t e, const char* what) {
   return fail(MLF_ERR_CUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 }

@@ -2,6 +2,7 @@
 // IPC handles for peer replication, streams and events. Kept free of any policy so that the
 // Python host code decides what overlaps with what.
 #include <string.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <atomic>
@@ -55,9 +56,17 @@ int32_t mlf_memcpy_async(void* dst, const void* src, uint64_t nbytes, int32_t ki
   return MLF_OK;
 }
 
-int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t to_device, int32_t nthreads) {
+}  // extern "C"
+
+namespace mlf {
+// Shared body of mlf_bounce_copy and mlf_buf_read_to_device. The host side is either a mapped
+// address (`host_ptr`) or, for host -> device only, a file descriptor read with pread() at
+// `file_off`: reading through the descriptor copies straight from the page cache into the
+// page-locked slot and never builds (or tears down) page tables for the object.
+int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off, uint64_t nbytes, int32_t to_device,
+                        int32_t nthreads) {
   if (nbytes == 0) return MLF_OK;
-  if (!dev_ptr || !host_ptr) return mlf::fail(MLF_ERR_INVALID, "mlf_bounce_copy: null pointer");
+  if (!dev_ptr || (!host_ptr && fd < 0)) return mlf::fail(MLF_ERR_INVALID, "bounce transfer: null pointer");
   int workers = nthreads > 0 ? nthreads : (int)std::max(1u, std::thread::hardware_concurrency() / 2);
   workers = std::min(workers, kMaxWorkers);
   const uint64_t nchunks = (nbytes + kSlotBytes - 1) / kSlotBytes;
@@ -68,6 +77,7 @@ int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t 
   MLF_CUDA(ensure_slots(workers));
 
   std::atomic<int> first_error{(int)cudaSuccess};
+  std::atomic<bool> io_failed{false};
   auto run = [&](int w) {
     cudaError_t e = cudaSetDevice(dev);
     cudaStream_t stream = nullptr;
@@ -87,7 +97,20 @@ int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t 
         if (!to_device) memcpy(static_cast<char*>(host_ptr) + pending_off[turn], slot, pending_len[turn]);
       }
       if (to_device) {
-        memcpy(slot, static_cast<const char*>(host_ptr) + off, len);
+        if (fd >= 0) {
+          uint64_t got = 0;
+          while (got < len) {
+            const ssize_t n = pread(fd, slot + got, len - got, (off_t)(file_off + off + got));
+            if (n <= 0) {
+              io_failed.store(true);
+              break;
+            }
+            got += (uint64_t)n;
+          }
+          if (io_failed.load()) break;
+        } else {
+          memcpy(slot, static_cast<const char*>(host_ptr) + off, len);
+        }
         e = cudaMemcpyAsync(static_cast<char*>(dev_ptr) + off, slot, len, cudaMemcpyHostToDevice, stream);
       } else {
         e = cudaMemcpyAsync(slot, static_cast<const char*>(dev_ptr) + off, len, cudaMemcpyDeviceToHost, stream);
@@ -124,7 +147,16 @@ int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t 
     (void)cudaGetLastError();
     return mlf::cuda_fail((cudaError_t)first_error.load(), "pipelined bounce copy");
   }
+  if (io_failed.load()) return mlf::fail_errno(MLF_ERR_IO, "pread() failed or hit end of file during a bounce transfer");
   return MLF_OK;
+}
+}  // namespace mlf
+
+extern "C" {
+
+int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t to_device, int32_t nthreads) {
+  if (nbytes > 0 && !host_ptr) return mlf::fail(MLF_ERR_INVALID, "mlf_bounce_copy: null pointer");
+  return mlf::bounce_transfer(dev_ptr, host_ptr, -1, 0, nbytes, to_device, nthreads);
 }
 
 int32_t mlf_dev_alloc(uint64_t nbytes, void** out) {

@@ -90,6 +90,13 @@ class BufferObject:
         _native.check(_native.lib().mlf_buf_dev_ptr(self._handle, ctypes.byref(out)))
         return int(out.value or 0)
 
+    def read_to_device(self, offset: int, device_ptr: int, nbytes: int, threads: int = 0) -> None:
+        """Blocking copy of object bytes ``[offset, offset + nbytes)`` into device memory through the
+        page-locked bounce ring, reading the file descriptor rather than the mapping."""
+        _native.check(
+            _native.lib().mlf_buf_read_to_device(self._handle, int(offset), ctypes.c_void_p(device_ptr), int(nbytes), int(threads))
+        )
+
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None
         if handle:

@@ -478,17 +478,24 @@ class CudaCopyEngine:
                     )
                 )
             else:
-                # read-only object mappings cannot be page-locked: feed HBM through the bounce ring
+                # read-only object mappings cannot be page-locked: feed HBM through the bounce ring,
+                # reading the file descriptor so that the mapping's pages are never faulted in
                 stream.synchronize()
-                _native.check(
-                    _native.lib().mlf_bounce_copy(
-                        ctypes.c_void_p(image.data_ptr()),
-                        ctypes.c_void_p(buffer_io.host_address(lo)),
-                        hi - lo,
-                        1,
-                        self.host_threads,
+                reader = getattr(getattr(buffer_io, "buffer_obj", None), "read_to_device", None)
+                if reader is not None:
+                    from ml_flashpoint.checkpoint_object_manager.buffer_metadata import METADATA_SIZE
+
+                    reader(METADATA_SIZE + lo, image.data_ptr(), hi - lo, self.host_threads)
+                else:
+                    _native.check(
+                        _native.lib().mlf_bounce_copy(
+                            ctypes.c_void_p(image.data_ptr()),
+                            ctypes.c_void_p(buffer_io.host_address(lo)),
+                            hi - lo,
+                            1,
+                            self.host_threads,
+                        )
                     )
-                )
             t_copied.record(stream)
             descs = (_native.CopyDesc * len(prepared))()
             host_targets = []
