@@ -6,8 +6,8 @@
 // over the tile prefix, and move that tile. Four segment kinds exist:
 //   FLAT       both sides contiguous: 64 KiB byte runs, destination-aligned 16-byte vectors
 //   ROWS       innermost dimension contiguous on both sides: runs per row (or per row chunk)
-//   TRANSPOSE  the tensor's unit-stride dimension is not the image's: 64x64 element tiles through
-//              shared memory so both sides are touched along their contiguous direction
+//   TRANSPOSE  the tensor's unit-stride dimension is not the image's: tiles of 32 elements by 256
+//              bytes through shared memory so both sides are touched along their contiguous direction
 //   GENERIC    anything else (stepped slices, expands): one element per thread
 // The image side has byte alignment only, because the object format is unpadded.
 #include <stdlib.h>
@@ -27,7 +27,10 @@ namespace {
 constexpr uint32_t kThreads = 256;
 constexpr uint64_t kTileBytes = 64 * 1024;    // FLAT tile and ROWS chunk
 constexpr uint64_t kRowSplitBytes = 16 * 1024;  // rows at least this long are cut into chunks
-constexpr int kTransTile = 64;                // TRANSPOSE tile edge, in elements
+constexpr int kTransCols = 32;                // TRANSPOSE tile: elements along the tensor-contiguous dim
+constexpr int kTransRowBytes = 256;           // TRANSPOSE tile: bytes along the image-contiguous dim
+constexpr int kTransSmemBytes = 32 * 264 + 16;  // 32 rows at the widest pitch + slack for vector reads
+constexpr int kTransNarrowBytes = 8192;       // staging bytes of a tile made of whole short rows
 constexpr uint64_t kGenericTile = 4096;       // GENERIC elements per tile
 
 enum SegKind : uint32_t { kFlat = 0, kRows = 1, kTranspose = 2, kGeneric = 3 };
@@ -42,6 +45,8 @@ struct Seg {
   uint32_t b;  // FLAT: destination address mod 128 | ROWS: rows per tile (0 = chunked rows) | TRANSPOSE: tiles along L
   uint32_t c;  // ROWS: chunks per row                   | TRANSPOSE: index of dimension C
   uint32_t image_aligned;  // 1 if every image element address is a multiple of esize
+  uint32_t d;  // TRANSPOSE: elements along C per tile when the tile spans whole image rows (0 = 32 x 256 B tiles)
+  uint32_t reserved;
   int64_t shape[MLF_MAX_DIMS];
   int64_t tstride[MLF_MAX_DIMS];  // bytes
   int64_t istride[MLF_MAX_DIMS];  // bytes
@@ -69,18 +74,40 @@ __device__ __forceinline__ void store_elem(uint8_t* p, T v, bool aligned) {
   for (int k = 0; k < (int)sizeof(T); ++k) p[k] = b[k];
 }
 
-// One 64x64 element tile of a TRANSPOSE segment, as four 32x32 blocks through shared memory.
-// Dimension C is contiguous in the tensor, dimension L (the last) is contiguous in the image.
+// Copies `len` bytes from global memory at any alignment into a 4-byte aligned shared-memory
+// row with a group of `nthr` threads (a warp by default): aligned 32-bit loads, funnel-shifted into place.
+__device__ __forceinline__ void load_row_to_smem(uint8_t* __restrict__ row, const uint8_t* __restrict__ gsrc, uint32_t len,
+                                                 unsigned lane, unsigned nthr = 32) {
+  const uint32_t m = (uint32_t)((uintptr_t)gsrc & 3u);
+  const uint32_t* __restrict__ a = reinterpret_cast<const uint32_t*>(gsrc - m);
+  const uint32_t nwords = len >> 2;
+  uint32_t* __restrict__ out = reinterpret_cast<uint32_t*>(row);
+  for (uint32_t i = lane; i < nwords; i += nthr) {
+    const uint32_t lo = a[i];
+    const uint32_t hi = m ? a[i + 1] : 0u;
+    out[i] = __funnelshift_r(lo, hi, 8u * m);
+  }
+  const uint32_t tail = len & 3u;
+  if (lane < tail) row[(nwords << 2) + lane] = gsrc[(nwords << 2) + lane];
+}
+
+// One tile of a TRANSPOSE segment: 32 elements along C (contiguous in the tensor) by 256 bytes
+// along L (contiguous in the image), staged in shared memory as 32 image rows. The tensor side is
+// touched with naturally aligned element accesses coalesced along C; the image side, which has
+// byte alignment only, is moved a row at a time by a warp with 16-byte vectors (drain_slot) or
+// aligned words (load_row_to_smem).
 template <typename T, int DIR>
-__device__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem_raw) {
-  T(*tile)[33] = reinterpret_cast<T(*)[33]>(smem_raw);
+__device__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
+  constexpr int E = (int)sizeof(T);
+  constexpr int TL = kTransRowBytes / E;
+  constexpr int ROW = E == 8 ? 264 : 260;  // row pitch: odd word count keeps column accesses off one bank
   const int L = (int)g.ndim - 1;
   const int C = (int)g.c;
   const uint32_t tiles_per_batch = (uint32_t)g.a;
   uint64_t batch = local / tiles_per_batch;
   const uint32_t in_batch = local % tiles_per_batch;
-  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransTile;
-  const int64_t l0 = (int64_t)(in_batch % g.b) * kTransTile;
+  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransCols;
+  const int64_t l0 = (int64_t)(in_batch % g.b) * TL;
   int64_t toff = 0, ioff = 0;
   for (int d = L - 1; d >= 0; --d) {
     if (d == C) continue;
@@ -89,39 +116,58 @@ __device__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uin
     toff += idx * g.tstride[d];
     ioff += idx * g.istride[d];
   }
-  const uint8_t* tbase_c = reinterpret_cast<const uint8_t*>(g.tensor) + toff;
   uint8_t* tbase = reinterpret_cast<uint8_t*>(g.tensor) + toff;
   uint8_t* ibase = image + g.image_off + ioff;
   const int64_t nC = g.shape[C], nL = g.shape[L];
   const int64_t tsL = g.tstride[L], isC = g.istride[C];
-  const bool ial = g.image_aligned != 0;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-  for (int sub = 0; sub < 4; ++sub) {
-    const int64_t cb = c0 + (sub >> 1) * 32, lb = l0 + (sub & 1) * 32;
-    if (cb >= nC || lb >= nL) continue;  // uniform across the CTA
+  if (g.d != 0) {
+    // Narrow image rows (shorter than 256 bytes) that follow one another without a gap: the tile
+    // takes g.d consecutive rows whole, which is ONE contiguous run in the image.
+    const int64_t cn0 = (int64_t)in_batch * g.d;
+    const int ncn = (int)min((int64_t)g.d, nC - cn0);
+    const int nln = (int)nL;
+    const uint32_t run = (uint32_t)ncn * (uint32_t)nln * E;
+    uint8_t* irun = ibase + cn0 * isC;
+    uint8_t* trun = tbase + cn0 * (int64_t)E;
     if (DIR == MLF_PACK) {
-      for (int j = ty; j < 32; j += 8) {
-        const int64_t l = lb + j, c = cb + tx;
-        if (l < nL && c < nC) tile[j][tx] = *reinterpret_cast<const T*>(tbase_c + c * (int64_t)sizeof(T) + l * tsL);
-      }
+      for (int l = 0; l < nln; ++l)
+        for (int c = (int)threadIdx.x; c < ncn; c += (int)blockDim.x)
+          *reinterpret_cast<T*>(smem + ((size_t)c * nln + l) * E) = *reinterpret_cast<const T*>(trun + c * (int64_t)E + l * tsL);
       __syncthreads();
-      for (int j = ty; j < 32; j += 8) {
-        const int64_t c = cb + j, l = lb + tx;
-        if (l < nL && c < nC) store_elem<T>(ibase + c * isC + l * (int64_t)sizeof(T), tile[tx][j], ial);
-      }
+      mlf::drain_slot(irun, smem, 0, run, threadIdx.x, blockDim.x);
     } else {
-      for (int j = ty; j < 32; j += 8) {
-        const int64_t c = cb + j, l = lb + tx;
-        if (l < nL && c < nC) tile[tx][j] = load_elem<T>(ibase + c * isC + l * (int64_t)sizeof(T), ial);
-      }
+      load_row_to_smem(smem, irun, run, threadIdx.x, blockDim.x);
       __syncthreads();
-      for (int j = ty; j < 32; j += 8) {
-        const int64_t l = lb + j, c = cb + tx;
-        if (l < nL && c < nC) *reinterpret_cast<T*>(tbase + c * (int64_t)sizeof(T) + l * tsL) = tile[j][tx];
-      }
+      for (int l = 0; l < nln; ++l)
+        for (int c = (int)threadIdx.x; c < ncn; c += (int)blockDim.x)
+          *reinterpret_cast<T*>(trun + c * (int64_t)E + l * tsL) = *reinterpret_cast<const T*>(smem + ((size_t)c * nln + l) * E);
     }
     __syncthreads();
+    return;
   }
+  const int nc = (int)min((int64_t)kTransCols, nC - c0);  // rows of this tile
+  const int nl = (int)min((int64_t)TL, nL - l0);          // elements per row
+  const unsigned tx = threadIdx.x & 31u, ty = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  if (DIR == MLF_PACK) {
+    if ((int)tx < nc)
+      for (int l = (int)ty; l < nl; l += (int)nwarp)
+        *reinterpret_cast<T*>(smem + tx * ROW + l * E) =
+            *reinterpret_cast<const T*>(tbase + (c0 + tx) * (int64_t)E + (l0 + l) * tsL);
+    __syncthreads();
+    for (int r = (int)ty; r < nc; r += (int)nwarp) {
+      const uint32_t at = (uint32_t)r * ROW;
+      mlf::drain_slot(ibase + (c0 + r) * isC + l0 * (int64_t)E, smem + (at & ~15u), at & 15u, (uint32_t)nl * E, tx, 32);
+    }
+  } else {
+    for (int r = (int)ty; r < nc; r += (int)nwarp)
+      load_row_to_smem(smem + (uint32_t)r * ROW, ibase + (c0 + r) * isC + l0 * (int64_t)E, (uint32_t)nl * E, tx);
+    __syncthreads();
+    if ((int)tx < nc)
+      for (int l = (int)ty; l < nl; l += (int)nwarp)
+        *reinterpret_cast<T*>(tbase + (c0 + tx) * (int64_t)E + (l0 + l) * tsL) =
+            *reinterpret_cast<const T*>(smem + tx * ROW + l * E);
+  }
+  __syncthreads();
 }
 
 template <typename T, int DIR>
@@ -199,7 +245,7 @@ template <int DIR>
 __global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restrict__ segs,
                                                             const uint32_t* __restrict__ tile_begin, uint32_t nseg,
                                                             uint32_t ntiles, uint8_t* __restrict__ image) {
-  __shared__ __align__(16) uint8_t smem[32 * 33 * 8];
+  __shared__ __align__(16) uint8_t smem[kTransSmemBytes];
   __shared__ Seg g;
   uint32_t cached = 0xffffffffu;
   for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
@@ -318,13 +364,13 @@ __device__ __forceinline__ uint32_t find_segment(const uint32_t* __restrict__ ti
 }
 
 template <int DIR>
-__global__ void __launch_bounds__(kThreads) mlf_plan_kernel_bulk(const Seg* __restrict__ segs,
+__global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* __restrict__ segs,
                                                                  const uint32_t* __restrict__ tile_begin, uint32_t nseg,
                                                                  uint32_t ntiles, uint8_t* __restrict__ image,
                                                                  int32_t* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
   __shared__ __align__(8) uint64_t full[mlf::kStages];
-  __shared__ __align__(16) uint8_t tsmem[32 * 33 * 8];
+  __shared__ __align__(16) uint8_t tsmem[kTransSmemBytes];
   __shared__ Seg g;
   __shared__ int abort_flag;
   const unsigned tid = threadIdx.x;
@@ -614,8 +660,18 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg*
       if (cdim >= 0) {
         g.kind = kTranspose;
         g.c = (uint32_t)cdim;
-        const uint64_t tc = ((uint64_t)c.shape[cdim] + kTransTile - 1) / kTransTile;
-        const uint64_t tl = ((uint64_t)c.shape[last] + kTransTile - 1) / kTransTile;
+        const uint64_t per_row = (uint64_t)kTransRowBytes / esize;
+        const uint64_t row_bytes = (uint64_t)c.shape[last] * esize;
+        uint64_t tc, tl;
+        if (row_bytes < (uint64_t)kTransRowBytes && (uint64_t)c.is[cdim] == row_bytes) {
+          // short image rows lying back to back: a tile is as many whole rows as fit the staging area
+          g.d = (uint32_t)std::max<uint64_t>(1, (uint64_t)kTransNarrowBytes / row_bytes);
+          tc = ((uint64_t)c.shape[cdim] + g.d - 1) / g.d;
+          tl = 1;
+        } else {
+          tc = ((uint64_t)c.shape[cdim] + kTransCols - 1) / kTransCols;
+          tl = ((uint64_t)c.shape[last] + per_row - 1) / per_row;
+        }
         g.b = (uint32_t)tl;
         g.a = tc * tl;
         uint64_t batch = 1;
