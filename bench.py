@@ -572,6 +572,23 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
     clocks = sampler.stop() if rank == 0 else None
     launches = lib.mlf_launch_count() - launches0
 
+    # ---- overlapped save: how long the caller is held before it may mutate the tensors again
+    async_block_ms = []
+    for _ in range(2):
+        if state["prev"] is not None:
+            com.delete_container(state["prev"])
+        ckpt = CheckpointContainerId(os.path.join(base, f"step-{state['step']}_ckpt"))
+        state["step"] += 1
+        state["prev"] = ckpt
+        saver.initialize_checkpoint(ckpt)
+        buckets = saver.prepare_write_data(ckpt, items, resolver, f"__{rank}_", bucket_count=1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        pending = saver.write_data_async(ckpt, buckets)
+        pending.wait_safe_to_mutate()
+        async_block_ms.append((time.perf_counter() - t0) * 1e3)
+        results = pending.result()
+
     # ---- restore (its own timed region; not part of the save step)
     restore = None
     if not args.no_restore:
@@ -667,6 +684,9 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
         "blocking_save_ms": {
             "time_to_safe_mutate": statistics.mean(kernel_ms),
             "call_to_return": statistics.mean(walls) * 1e3,
+            "overlapped_call_to_safe_mutate": min(async_block_ms),
+            "note": "time_to_safe_mutate = pack kernel (device); call_to_return = blocking write_data; "
+            "overlapped_call_to_safe_mutate = wall time write_data_async holds the caller (planning + launch + kernel)",
         },
         "e2e": {
             "value": total_payload * args.steps / 1e9 / slow_wall_s,

@@ -177,6 +177,25 @@ class MemoryStorageWriter(StorageWriter, staging.BlockingAsyncStager):
         done.set_result(write_results)
         return done
 
+    def launch_staged_data_buckets(
+        self,
+        checkpoint_id: CheckpointContainerId,
+        staged_write_buckets: list[ObjectWriteBucket],
+        replicate_after_write: bool = False,
+    ):
+        """Overlapped form of ``write_staged_data_buckets``: queues the pack kernels and transfers and
+        returns a ``PendingSave`` at once. Call ``complete_launched_buckets`` with it later to publish
+        the results (this is what a training loop uses to hide the host transfer behind compute)."""
+        return self._checkpoint_saver.write_data_async(checkpoint_id, staged_write_buckets, replicate_after_write)
+
+    def complete_launched_buckets(self, checkpoint_id: CheckpointContainerId, pending) -> list[WriteResult]:
+        """Waits for a ``PendingSave``, records its write results for ``get_write_results`` and signals
+        completion, exactly as ``write_staged_data_buckets`` does for a blocking write."""
+        write_results = pending.result()
+        self._write_results_per_checkpoint_id[checkpoint_id] = write_results
+        self._write_events_per_checkpoint_id[checkpoint_id].set()
+        return write_results
+
     @log_execution_time(logger=_LOGGER, name="write_data", level=logging.INFO)
     def write_data(self, plan: SavePlan, planner: SavePlanner) -> TorchFuture[list[WriteResult]]:
         self._check_checkpoint_id()

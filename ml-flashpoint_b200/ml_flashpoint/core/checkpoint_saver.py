@@ -57,6 +57,58 @@ class ObjectWriteBucket:
     tensor_data: list[tuple[WriteItem, torch.Tensor]]
 
 
+class PendingSave:
+    """A save whose bytes are still moving (returned by ``write_data_async``).
+
+    ``wait_safe_to_mutate`` returns once every source tensor has been read: the training loop may
+    then overwrite parameters and optimizer state while the host transfer continues.
+    ``safe_to_mutate_event`` is the CUDA event for the same moment, for
+    ``stream.wait_event`` without blocking the host. ``result`` blocks until every object is
+    complete in its buffer, closes the buffers and returns the write results.
+    """
+
+    def __init__(self, saver: "DefaultMLFlashpointCheckpointSaver", replicate_after_write: bool):
+        self._saver = saver
+        self._replicate = replicate_after_write
+        self._parts: list = []  # (bucket, writer, records, ticket)
+        self._results: Optional[list[WriteResult]] = None
+
+    def _add(self, bucket, writer, records, ticket) -> None:
+        self._parts.append((bucket, writer, records, ticket))
+
+    @property
+    def safe_to_mutate_event(self):
+        return self._parts[-1][3].mutate_event if self._parts else None
+
+    def wait_safe_to_mutate(self) -> None:
+        for _, _, _, ticket in self._parts:
+            ticket.mutate_event.synchronize()
+
+    def done(self) -> bool:
+        return all(ticket.done_event.query() for _, _, _, ticket in self._parts)
+
+    def result(self) -> list[WriteResult]:
+        if self._results is not None:
+            return self._results
+        results: list[WriteResult] = []
+        first_error: Optional[BaseException] = None
+        for bucket, writer, records, ticket in self._parts:
+            try:
+                ticket.wait()
+                results.extend(self._saver._to_write_results(bucket.object_name, records))
+            except BaseException as e:  # keep closing the remaining buffers
+                first_error = first_error or e
+            finally:
+                writer.close()
+        if first_error is not None:
+            raise first_error
+        if self._replicate:
+            for bucket, _, _, _ in self._parts:
+                self._saver.async_replicate_object(bucket.object_id)
+        self._results = results
+        return results
+
+
 class WriteItemResolver(Protocol):
     """Anything with ``resolve_data(write_item) -> Tensor | BytesIO``; a DCP ``SavePlanner`` qualifies."""
 
@@ -254,6 +306,36 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
             raise errors[0]
         return results
 
+    @log_execution_time(logger=_LOGGER, name="write_data_async", level=logging.INFO)
+    def write_data_async(
+        self,
+        checkpoint_id: CheckpointContainerId,
+        write_buckets: list[ObjectWriteBucket],
+        replicate_after_write: bool = False,
+    ) -> PendingSave:
+        """Starts writing every bucket and returns without waiting for the bytes to land.
+
+        This is the overlapped form of ``write_data``: one pack kernel per bucket is queued on the
+        engine's side stream (ordered after the caller's current stream), followed by the transfer
+        into the bucket's buffer. The call returns after the launches; see ``PendingSave`` for the
+        two completion points. Buffers are acquired here and closed by ``PendingSave.result``.
+        """
+        pending = PendingSave(self, replicate_after_write)
+        for bucket in write_buckets:
+            writer = self._chkpt_obj_manager.acquire_buffer(bucket.object_id, self._initial_buffer_size_bytes)
+            try:
+                records, ticket = self._write_bucket(bucket, writer, self._use_optimized_save, wait=False)
+            except BaseException:
+                writer.close()
+                for _, open_writer, _, open_ticket in pending._parts:
+                    try:
+                        open_ticket.wait()
+                    finally:
+                        open_writer.close()
+                raise
+            pending._add(bucket, writer, records, ticket)
+        return pending
+
     @log_execution_time(logger=_LOGGER, name="_write_to_buffer_from_queue_worker")
     def _write_to_buffer_from_queue_worker(
         self,
@@ -281,7 +363,7 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
             finally:
                 object_write_bucket_queue.task_done()
 
-    def _write_bucket(self, bucket: ObjectWriteBucket, writer, use_optimized_write: bool):
+    def _write_bucket(self, bucket: ObjectWriteBucket, writer, use_optimized_write: bool, wait: bool = True):
         if use_optimized_write:
             writer.set_format_signature(CheckpointFormat.MLF_FORMAT)
             layout = gpu_engine.plan_object_layout(bucket.tensor_data, bucket.bytesio_data, start_offset=0)
@@ -301,8 +383,11 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
 
             writer.ensure_total_size(METADATA_SIZE + start + layout.total_bytes)
         writer.next_buffer_slice(layout.total_bytes)  # claims the bytes; raises if they do not fit
-        self._engine().pack(layout, writer, start, object_id=str(bucket.object_id))
-        return [(r.item, start + r.offset, r.length) for r in layout.records]
+        records = [(r.item, start + r.offset, r.length) for r in layout.records]
+        if wait:
+            self._engine().pack(layout, writer, start, object_id=str(bucket.object_id))
+            return records
+        return records, self._engine().pack_async(layout, writer, start, object_id=str(bucket.object_id))
 
     @staticmethod
     def _to_write_results(object_name: str, records) -> list[WriteResult]:

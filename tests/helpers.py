@@ -25,8 +25,30 @@ def golden_object_bytes(golden_dir, entry):
         return f.read()
 
 
+class _FiredEvent:
+    def synchronize(self):
+        pass
+
+    def query(self):
+        return True
+
+
+class _FinishedTicket:
+    """What ``pack_async`` returns when the work is already done (the stand-in engine is synchronous)."""
+
+    mutate_event = _FiredEvent()
+    done_event = _FiredEvent()
+
+    def wait(self):
+        pass
+
+
 class NumpyCopyEngine:
-    """Drop-in for ``CudaCopyEngine`` in CPU tests: same ``pack`` / ``unpack`` signatures."""
+    """Drop-in for ``CudaCopyEngine`` in CPU tests: same ``pack`` / ``pack_async`` / ``unpack`` signatures."""
+
+    def pack_async(self, layout, buffer_io, start_pos=0, object_id=None):
+        self.pack(layout, buffer_io, start_pos, object_id)
+        return _FinishedTicket()
 
     def pack(self, layout, buffer_io, start_pos=0, object_id=None):
         base = buffer_io.host_address(start_pos)

@@ -220,3 +220,30 @@ def test_large_transposed_and_row_sliced_sources(esize, dtype, engine, tmp_path)
         cpu_case = {"tensors": {k: v.cpu() for k, v in tensors.items()}, "blobs": {}, "bucket_count": 1}
         ((_, want, _),) = oracle.save_case(cpu_case)
         assert data == want, (esize, prefix)
+
+
+def test_overlapped_save_reads_sources_before_safe_to_mutate(shm_path, golden_dir, engine):
+    """After ``wait_safe_to_mutate`` the sources may be overwritten: the object still holds the old values."""
+    from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
+    from ml_flashpoint.core.buffer_pool import BufferPoolConfig
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+
+    gold = load_golden(golden_dir, "gpt2_tiny.json")
+    case = case_to_device(cases.CASES["gpt2_tiny"](), "cuda")
+    CheckpointObjectManager._worker_pool = None
+    pool = BufferPoolConfig(str(shm_path / "pool"), 0, 1, 1 << 20, register_cuda=True)  # page-locked: the drain is asynchronous
+    saver, com = make_saver(copy_engine=engine, pool_config=pool)
+    ckpt = CheckpointContainerId(str(shm_path / "step-1_ckpt"))
+    saver.initialize_checkpoint(ckpt)
+    items, resolver = cases.write_items_and_resolver(case)
+    buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=1)
+    pending = saver.write_data_async(ckpt, buckets)
+    pending.wait_safe_to_mutate()
+    for t in case["tensors"].values():
+        t.zero_()  # the optimizer step of the next iteration
+    torch.cuda.synchronize()
+    results = pending.result()
+    data = open(str(buckets[0].object_id), "rb").read()
+    assert hashlib.sha256(data).hexdigest() == gold["objects"][0]["sha256"]
+    assert len(results) == len(gold["write_results"])
+    com.teardown_pool()

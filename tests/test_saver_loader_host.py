@@ -208,3 +208,23 @@ def test_legacy_torch_save_format_round_trip(tmp_path):
     for fqn, t in case["tensors"].items():
         assert torch.equal(targets[fqn], t)
     assert blobs == dict(case["blobs"])
+
+
+def test_overlapped_save_api_publishes_the_same_objects(tmp_path, golden_dir):
+    """``write_data_async`` + ``PendingSave.result`` must leave exactly what ``write_data`` leaves."""
+    gold = load_golden(golden_dir, "two_buckets.json")
+    case = cases.CASES["two_buckets"]()
+    saver, com = make_saver(copy_engine=NumpyCopyEngine())
+    ckpt = CheckpointContainerId(str(tmp_path / "step-5_ckpt"))
+    saver.initialize_checkpoint(ckpt)
+    items, resolver = cases.write_items_and_resolver(case)
+    buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=2)
+    pending = saver.write_data_async(ckpt, buckets)
+    pending.wait_safe_to_mutate()
+    assert pending.done() and pending.safe_to_mutate_event is not None
+    results = pending.result()
+    assert pending.result() is results  # idempotent
+    for bucket, g in zip(buckets, gold["objects"]):
+        assert open(str(bucket.object_id), "rb").read() == golden_object_bytes(golden_dir, g)
+    got = sorted((r.storage_data.relative_path, r.storage_data.offset, r.storage_data.length) for r in results)
+    assert got == [(w["relative_path"], w["offset"], w["length"]) for w in gold["write_results"]]
