@@ -76,7 +76,7 @@ class NumpyCopyEngine:
             target.copy_(carrier)
 
 
-def make_saver(copy_engine=None, rank=0, pool_config=None, initial_buffer_size_bytes=8 * 1024 * 1024, **kw):
+def make_saver(copy_engine=None, rank=0, pool_config=None, initial_buffer_size_bytes=8 * 1024 * 1024, replication_manager=None, **kw):
     from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
     from ml_flashpoint.core.checkpoint_saver import DefaultMLFlashpointCheckpointSaver
 
@@ -86,7 +86,7 @@ def make_saver(copy_engine=None, rank=0, pool_config=None, initial_buffer_size_b
         local_rank_getter=lambda: rank,
         global_barrier_func=lambda: None,
         ckpt_obj_manager=com,
-        replication_manager=None,
+        replication_manager=replication_manager,
         initial_buffer_size_bytes=initial_buffer_size_bytes,
         copy_engine=copy_engine,
         **kw,
