@@ -118,7 +118,18 @@ class MemoryStorageWriter(StorageWriter, staging.BlockingAsyncStager):
 
     @log_execution_time(logger=_LOGGER, name="stage", level=logging.INFO)
     def stage(self, state_dict: STATE_DICT_TYPE) -> STATE_DICT_TYPE:
-        return super().stage(state_dict)
+        """Snapshot for ``dcp.async_save``: every tensor is cloned where it lives.
+
+        The reference offloads the state dict to (pinned) host memory here. With 180 GB of HBM a
+        device-side clone is the cheaper snapshot: it runs at HBM speed, the trainer continues at
+        once, and the background save packs from the clone straight into the object.
+        """
+        from torch.utils._pytree import tree_map_only
+
+        snapshot = tree_map_only(torch.Tensor, lambda t: t.detach().clone(), state_dict)
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()
+        return snapshot
 
     # ------------------------------------------------------------------ split save path
     @log_execution_time(logger=_LOGGER, name="prepare_write_data_buckets")

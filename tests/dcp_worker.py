@@ -92,3 +92,54 @@ def run_rank(rank: int, world: int, root: str, port: int, engine_kind: str, resu
         manager.shutdown()
     finally:
         dist.destroy_process_group()
+
+
+def run_async_save(rank: int, root: str, port: int, result_path: str) -> None:
+    """``dcp.async_save`` through the writer: the tensors are overwritten as soon as the call returns."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    repo = os.path.dirname(here)
+    for p in (here, os.path.join(here, "golden"), os.path.join(repo, "oracle"), os.path.join(repo, "ml-flashpoint_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(
+        MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK="0", LOCAL_RANK="0", WORLD_SIZE="1", NNODES="1",
+        MLFLASHPOINT_LOG_LEVEL="ERROR",
+    )
+    import torch
+    import torch.distributed as dist
+    import torch.distributed.checkpoint as dcp
+    import torch.multiprocessing as torch_mp
+
+    import cases
+    from helpers import NumpyCopyEngine, make_loader, make_saver, tensor_bytes
+    from ml_flashpoint.adapter.pytorch.memory_storage_reader import MemoryStorageReader
+    from ml_flashpoint.adapter.pytorch.memory_storage_writer import MemoryStorageWriter
+
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        engine = NumpyCopyEngine()
+
+        class _NoRepl:
+            def async_replicate(self, buffer_io):
+                buffer_io.close()
+                return []
+
+        saver, com = make_saver(copy_engine=engine, replication_manager=_NoRepl())
+        manager = torch_mp.Manager()
+        fut = concurrent.futures.Future()
+        fut.set_result(manager)
+        state = dict(cases.CASES["gpt2_tiny"]()["tensors"])
+        originals = {k: v.clone() for k, v in state.items()}
+        ckpt = os.path.join(root, "step-1_ckpt")
+        handle = dcp.async_save(state, checkpoint_id=ckpt, storage_writer=MemoryStorageWriter(saver, fut))
+        for v in state.values():
+            v.zero_()
+        handle.result()
+        fresh = {k: torch.zeros_like(v) for k, v in originals.items()}
+        dcp.load(fresh, checkpoint_id=ckpt, storage_reader=MemoryStorageReader(ckpt, make_loader(com, copy_engine=engine)))
+        ok = all(tensor_bytes(fresh[k]) == tensor_bytes(v) for k, v in originals.items())
+        with open(result_path, "w") as f:
+            f.write(repr({"ok": ok}))
+        manager.shutdown()
+    finally:
+        dist.destroy_process_group()

@@ -46,3 +46,11 @@ def test_dcp_round_trip_two_ranks_with_cuda_engine(shm_path):
         pytest.skip("needs a CUDA device")
     outcomes = _run(shm_path, "cuda")
     assert all(o["ok"] for o in outcomes), outcomes
+
+
+def test_dcp_async_save_snapshots_the_state(tmp_path):
+    """``MemoryStorageWriter.stage`` must snapshot: tensors zeroed right after ``async_save`` returns
+    still load back with their old values."""
+    result = str(tmp_path / "async_result")
+    mp.spawn(dcp_worker.run_async_save, args=(str(tmp_path), _free_port(), result), nprocs=1, join=True)
+    assert ast.literal_eval(open(result).read())["ok"]
