@@ -38,9 +38,9 @@ import torch.distributed as dist  # noqa: E402
 METRIC = "checkpoint_save_throughput"
 UNIT = "GB/s"
 FSDP_WORLD = 8  # the named configuration shards the model 8 ways whatever --gpus is
-# DRAM bytes (read + write) per payload byte of the pack kernel, from the ncu capture summarised in
-# profiles/mlf_plan_kernel_bulk__llama3_8b_shard_2layers.md (5.154 GB for 2.602 GB of payload);
-# traffic grows in proportion to the payload, so a full launch is this ratio times its payload.
+# DRAM bytes (read + write) per payload byte of the pack kernel, from an ncu capture of the 2-layer
+# variant of this workload (dram__bytes_read.sum + dram__bytes_write.sum = 5.154 GB for 2.602 GB of
+# payload); traffic grows in proportion to the payload, so a full launch is this ratio times its payload.
 NCU_DRAM_BYTES_PER_PAYLOAD_BYTE = 1.981
 
 

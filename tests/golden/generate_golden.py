@@ -1,8 +1,8 @@
 """Generates the golden vectors under tests/golden/ by running the reference implementation.
 
-Run where the reference checkout is available (argument 1, default ``/root/reference``):
+Run where a checkout of the reference project is available and pass its root:
 
-    python tests/golden/generate_golden.py [/path/to/ml-flashpoint]
+    python tests/golden/generate_golden.py /path/to/ml-flashpoint
 
 The reference's two compiled extension modules cannot be built offline, so two small
 stand-ins are registered in ``sys.modules`` before the reference package is imported: a
@@ -251,7 +251,7 @@ def _narrow(workdir: str) -> list:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MLF_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
     _install_reference(ref_root)
     sys.path.insert(0, HERE)
     import cases
