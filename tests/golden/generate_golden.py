@@ -251,7 +251,9 @@ def _narrow(workdir: str) -> list:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MLF_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MLF_REFERENCE_ROOT")
+    if not ref_root:
+        sys.exit("usage: generate_golden.py /path/to/ml-flashpoint   (or set MLF_REFERENCE_ROOT)")
     _install_reference(ref_root)
     sys.path.insert(0, HERE)
     import cases
