@@ -138,7 +138,8 @@ int32_t mlf_buf_create(const char* object_id, uint64_t capacity, int32_t overwri
   int flags = O_CREAT | O_RDWR | O_CLOEXEC | (overwrite ? O_TRUNC : O_EXCL);
   int fd = open(object_id, flags, 0666);
   if (fd < 0) {
-    if (errno == EEXIST) return mlf::fail_errno(MLF_ERR_EXISTS, "open() failed, file exists and overwrite is off: " + id);
+    if (errno == EEXIST)
+      return mlf::fail(MLF_ERR_EXISTS, "open() failed for file: " + id + ". File already exists and overwrite is set to false.");
     return mlf::fail_errno(MLF_ERR_IO, "open() failed for file: " + id);
   }
   if (ftruncate(fd, (off_t)capacity) != 0) {
@@ -175,13 +176,17 @@ int32_t mlf_buf_open_ro(const char* object_id, mlf_buf** out) {
     close(fd);
     return rc;
   }
+  if (S_ISDIR(st.st_mode)) {
+    close(fd);
+    return mlf::fail(MLF_ERR_IO, "Path is a directory, not a file: " + id);
+  }
   if (!S_ISREG(st.st_mode)) {
     close(fd);
     return mlf::fail(MLF_ERR_IO, "not a regular file: " + id);
   }
   if (st.st_size == 0) {
     close(fd);
-    return mlf::fail(MLF_ERR_INVALID, "file is empty, nothing to map: " + id);
+    return mlf::fail(MLF_ERR_INVALID, "File cannot be empty, a zero-sized file cannot be mapped: " + id);
   }
   void* p = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_SHARED, fd, 0);
   if (p == MAP_FAILED) {

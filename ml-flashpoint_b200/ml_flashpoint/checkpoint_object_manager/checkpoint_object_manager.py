@@ -39,12 +39,13 @@ class CheckpointObjectManager:
                 cfg = self._pool_config
                 try:
                     _LOGGER.info("Initializing BufferPool with config: %s", cfg)
+                    extra = {"register_cuda": True} if getattr(cfg, "register_cuda", False) else {}
                     cls._worker_pool = BufferPool(
                         pool_dir_path=cfg.pool_dir_path,
-                        rank=cfg.rank,
                         num_buffers=cfg.num_buffers,
+                        rank=cfg.rank,
                         buffer_size=cfg.buffer_size,
-                        register_cuda=getattr(cfg, "register_cuda", False),
+                        **extra,
                     )
                 except Exception:
                     _LOGGER.exception("Failed to initialize BufferPool")

@@ -146,11 +146,30 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
             raise
 
     def read_tensor(self, buffer_slice: IO[bytes], req: ReadItem, use_optimized_loader: bool = False) -> torch.Tensor:
-        """Host-side read of one stored tensor, narrowed to the request (legacy ``torch.save`` items).
+        """One stored tensor from a file view, narrowed to the request, as a host tensor.
 
-        Kept for objects in the ``TORCH___`` format, whose items are opaque ``torch.save`` streams
-        and cannot be scattered by the kernel; ``MLF_TENS`` items never come through here.
+        ``read_data`` does not come through here for ``MLF_TENS`` objects (it scatters all items of an
+        object with one kernel launch); this per-item form is kept for callers of the reference API
+        and for objects in the ``TORCH___`` format, whose items are opaque ``torch.save`` streams.
+        With ``use_optimized_loader`` an ``MLF_TENS`` item is narrowed by the unpack kernel; anything
+        that does not parse as such an item falls back to ``torch.load``.
         """
+        start = buffer_slice.tell()
+        if use_optimized_loader:
+            prefix = buffer_slice.read(4)
+            if len(prefix) == 4:
+                (header_len,) = struct.unpack("<I", prefix)
+                if header_len < _MAX_HEADER_BYTES:
+                    try:
+                        header = pickle.loads(buffer_slice.read(header_len))
+                        payload = buffer_slice.read()
+                    except Exception:
+                        _LOGGER.exception("Failed to parse tensor header")
+                        raise
+                    return gpu_engine.unpack_payload_bytes(
+                        self._engine(), payload, header.dtype, header.shape, req.storage_offsets, req.lengths
+                    )
+        buffer_slice.seek(start)
         tensor = cast(torch.Tensor, torch.load(cast(IO[bytes], buffer_slice), map_location="cpu", weights_only=True))
         return narrow_tensor_by_index(tensor, req.storage_offsets, req.lengths)
 

@@ -36,7 +36,7 @@ from ml_flashpoint.core import gpu_engine
 from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId, CheckpointObjectId
 from ml_flashpoint.core.defaults import DIRTY_MARKER_SUFFIX, CheckpointFormat, default_metadata_object_name
 from ml_flashpoint.core.mlf_logging import get_logger
-from ml_flashpoint.core.utils import log_execution_time
+from ml_flashpoint.core.utils import get_accelerator_count, log_execution_time  # noqa: F401  (patch point kept)
 from ml_flashpoint.replication.replication_manager import ReplicationManager
 
 DEFAULT_INITIAL_BUFFER_SIZE_BYTES = 16 * 1024 * 1024 * 1024

@@ -541,6 +541,25 @@ class _ResidentLease:
         self._engine._lock.release()
 
 
+class _HostBytesView:
+    """Adapter that lets ``CudaCopyEngine.unpack`` read a payload held in a ``bytes`` object."""
+
+    def __init__(self, data: bytes):
+        self._keep = (ctypes.c_char * max(len(data), 1)).from_buffer_copy(data or b"\0")
+        self._addr = ctypes.addressof(self._keep)
+
+    def host_address(self, pos: int = 0) -> int:
+        return self._addr + pos
+
+
+def unpack_payload_bytes(engine: CudaCopyEngine, payload: bytes, dtype: torch.dtype, stored_shape, storage_offsets, lengths) -> torch.Tensor:
+    """The sub-block ``[storage_offsets, storage_offsets + lengths)`` of a stored tensor whose raw
+    C-order bytes are ``payload``, as a new host tensor (scattered by the unpack kernel)."""
+    out = torch.empty(tuple(lengths), dtype=dtype, device=engine.device)
+    engine.unpack([(out, 0, tuple(stored_shape), tuple(storage_offsets))], _HostBytesView(payload))
+    return out.cpu()
+
+
 _default_engine: Optional[CudaCopyEngine] = None
 _default_engine_lock = threading.Lock()
 

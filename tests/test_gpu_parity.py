@@ -247,3 +247,27 @@ def test_overlapped_save_reads_sources_before_safe_to_mutate(shm_path, golden_di
     assert hashlib.sha256(data).hexdigest() == gold["objects"][0]["sha256"]
     assert len(results) == len(gold["write_results"])
     com.teardown_pool()
+
+
+def test_read_tensor_per_item_api_matches_reference(tmp_path, golden_dir, engine):
+    """The per-item ``read_tensor(view, req, use_optimized_loader=True)`` call of the reference API."""
+    from torch.distributed.checkpoint.metadata import MetadataIndex
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+    from torch.distributed.checkpoint.utils import _create_file_view
+
+    rows = load_golden(golden_dir, "narrow.json")
+    tensors = {f"n.{i}": cases.narrow_source(i).cuda() for i in range(len(cases.NARROW_CASES))}
+    _, com, ckpt, buckets, results = _save({"tensors": tensors, "blobs": {}, "bucket_count": 1}, tmp_path, engine)
+    loader = make_loader(com, copy_engine=engine)
+    storage = {r.index.fqn: r.storage_data for r in results}
+    with com.get_buffer(buckets[0].object_id) as stream:
+        for row in rows:
+            shape, dtype, offs, lens = cases.NARROW_CASES[row["i"]]
+            if len(shape) == 0:
+                continue
+            idx = MetadataIndex(f"n.{row['i']}", torch.Size([0] * len(shape)))
+            req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0] * len(lens)), idx, torch.Size(offs), torch.Size(lens))
+            info = storage[f"n.{row['i']}"]
+            got = loader.read_tensor(_create_file_view(stream, info.offset, info.length), req, use_optimized_loader=True)
+            assert got.device.type == "cpu" and tuple(got.shape) == tuple(lens)
+            assert tensor_bytes(got).hex() == row["hex"], row["i"]
