@@ -299,9 +299,13 @@ def main() -> None:
             dist.init_process_group(
                 "nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=240)
             )
-    device = torch.device("cuda", local_rank if torch.cuda.is_available() else 0)
     if torch.cuda.is_available():
+        device = torch.device("cuda", local_rank)
         torch.cuda.set_device(device)
+    elif args.impl == "reference":
+        device = torch.device("cpu")  # the CPU arm also runs where there is no GPU (nothing to stage then)
+    else:
+        raise SystemExit("bench.py needs a CUDA device: this implementation has no CPU data path")
 
     shm_root = "/dev/shm" if os.path.isdir("/dev/shm") else "/tmp"
     workdir = args.workdir or os.path.join(shm_root, f"mlf_bench_{os.getuid()}", f"rank{rank}")
@@ -334,15 +338,19 @@ def run_reference_arm(args, device, workdir: str) -> None:
     payload_full = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
     tensors, nbytes = cpu_sample(shard, int(args.cpu_sample_gb * 1e9))
     path = os.path.join(workdir, "reference.distcp")
+    def sync():
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+
     for _ in range(max(args.warmup, 1)):
         cpu_path.timed_save(tensors, path)
-    torch.cuda.synchronize()
+    sync()
     t0 = time.perf_counter()
     stage_ms = []
     for _ in range(args.steps):
         r = cpu_path.timed_save(tensors, path)
         stage_ms.append(r["stage_s"] * 1e3)
-    torch.cuda.synchronize()
+    sync()
     elapsed = time.perf_counter() - t0
     value = nbytes * args.steps / 1e9 / elapsed
     sample = f"first {len(tensors)} tensors of one rank's shard ({nbytes / 1e9:.2f} of {payload_full / 1e9:.2f} GB) per step"
