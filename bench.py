@@ -215,6 +215,31 @@ def barrier():
 
 
 # --------------------------------------------------------------------------------------
+# Host-link calibration: what a plain pinned copy reaches while all ranks copy at once
+# --------------------------------------------------------------------------------------
+def calibrate_host_link(device, nbytes: int = 2 << 30) -> dict:
+    """Copy-engine D2H and H2D between HBM and driver-allocated pinned memory, all ranks at the
+    same time: the denominator for the save's drain and the restore's feed at this GPU count."""
+    dev = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    out = {}
+    for name, dst, src in (("d2h", host, dev), ("h2d", dev, host)):
+        best = 0.0
+        for _ in range(3):
+            barrier()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            dst.copy_(src, non_blocking=True)
+            t1.record()
+            torch.cuda.synchronize()
+            best = max(best, nbytes / 1e9 / (t0.elapsed_time(t1) / 1e3))
+        out[name] = -all_max(-best, device)  # the slowest rank's best
+    del dev, host
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # CPU baseline (the reference's host path, restated in oracle/cpu_path.py)
 # --------------------------------------------------------------------------------------
 def cpu_sample(shard, budget_bytes: int):
@@ -658,6 +683,8 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
     if world_size > 1 and not args.no_replication:
         replication = run_replication(args, rank, world_size, device, workdir, com, saver, engine, items, resolver, shard, one_save, state)
 
+    pinned_peak = calibrate_host_link(device)
+
     total_payload = all_sum(payload, device)
     slow_device_s = all_max(sum(device_ms) / 1e3, device)
     slow_region_s = all_max(region_s, device)
@@ -726,6 +753,9 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
             ),
             "note": "copy-engine drain of the HBM image into the page-locked object mapping (staged), "
             "or the kernel's own stores into it (direct)",
+            "pinned_copy_peak_d2h_gbs": pinned_peak["d2h"],
+            "pinned_copy_peak_h2d_gbs": pinned_peak["h2d"],
+            "peak_note": "plain copies to/from driver-allocated pinned memory, all ranks at once, slowest rank",
         },
         "cpu_baseline": cpu,
         "gpu_launches": int(launches),

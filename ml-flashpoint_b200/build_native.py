@@ -34,8 +34,10 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, out: str = OUT, defines: tuple = ()) -> str:
+    """Builds the library. ``defines`` (e.g. ``("MLF_RING_STAGES=8",)``) and ``out`` produce tuning
+    variants next to the default build; load one with the ``MLF_B200_LIB`` environment variable."""
+    if out == OUT and not defines and not force and not _stale():
         return OUT
     cmd = [
         _nvcc(),
@@ -57,14 +59,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
     ]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += [f"-D{d}" for d in defines]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
-    cmd += ["-o", OUT, "-lpthread"]
+    cmd += ["-o", out, "-lpthread"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stdout + res.stderr)
-    return OUT
+    return out
 
 
 if __name__ == "__main__":

@@ -19,8 +19,14 @@
 
 namespace mlf {
 
-constexpr uint32_t kStages = 4;
-constexpr uint32_t kStageBytes = 16 * 1024;
+#ifndef MLF_RING_STAGES
+#define MLF_RING_STAGES 4
+#endif
+#ifndef MLF_RING_STAGE_KIB
+#define MLF_RING_STAGE_KIB 16
+#endif
+constexpr uint32_t kStages = MLF_RING_STAGES;
+constexpr uint32_t kStageBytes = MLF_RING_STAGE_KIB * 1024;
 constexpr uint32_t kSlotBytes = kStageBytes + 16;  // one extra granule for a shifted source
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s: five orders of magnitude above a slot fill
 

@@ -32,7 +32,8 @@ MLF_IPC_HANDLE_BYTES = 64
 MLF_NOALLOC_MAX_DESCS = 1024
 
 LIB_NAME = "libmlf_b200.so"
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
+# MLF_B200_LIB selects another build of the same library (tuning variants); default is the in-tree one
+LIB_PATH = os.environ.get("MLF_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
 
 
 class NativeError(RuntimeError):
