@@ -155,12 +155,12 @@ def fill_desc(
         desc.image_stride[d] = int(image_stride[d])
 
 
-def default_host_threads() -> int:
-    """CPU threads for the bounce ring: half the cores, shared between the ranks on this host."""
+def default_host_threads(share: float = 0.5) -> int:
+    """CPU threads for the bounce ring: ``share`` of the cores, divided between the ranks on this host."""
     import os
 
     local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))
-    return max(2, (os.cpu_count() or 2) // 2 // local_world)
+    return max(2, int((os.cpu_count() or 2) * share) // local_world)
 
 
 # ======================================================================================
@@ -270,6 +270,8 @@ class CudaCopyEngine:
         self.host_ctas = get_env_val_int("GPU_HOST_CTAS", 32)
         # CPU threads feeding the bounce ring when host memory is not page-locked (0 = half the cores)
         self.host_threads = get_env_val_int("GPU_HOST_THREADS", default_host_threads())
+        # a restore runs before training starts, with the host otherwise idle: it may use every core
+        self.restore_threads = get_env_val_int("GPU_RESTORE_THREADS", default_host_threads(1.0))
         self._lock = threading.RLock()
         self._cache: "OrderedDict[tuple, _CachedPack]" = OrderedDict()
         self._cache_size = plan_cache_size
@@ -485,7 +487,7 @@ class CudaCopyEngine:
                 if reader is not None:
                     from ml_flashpoint.checkpoint_object_manager.buffer_metadata import METADATA_SIZE
 
-                    reader(METADATA_SIZE + lo, image.data_ptr(), hi - lo, self.host_threads)
+                    reader(METADATA_SIZE + lo, image.data_ptr(), hi - lo, self.restore_threads)
                 else:
                     _native.check(
                         _native.lib().mlf_bounce_copy(
@@ -493,7 +495,7 @@ class CudaCopyEngine:
                             ctypes.c_void_p(buffer_io.host_address(lo)),
                             hi - lo,
                             1,
-                            self.host_threads,
+                            self.restore_threads,
                         )
                     )
             t_copied.record(stream)
