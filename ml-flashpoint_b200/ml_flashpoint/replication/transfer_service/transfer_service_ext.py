@@ -17,6 +17,11 @@ The sender reuses the HBM image the save just produced when it is still resident
 ``gpu_engine.resident_image``); otherwise the object is first brought into HBM from the host
 pointer that was passed in. The receiving buffer is exported with CUDA IPC and opened by the
 sender; peers inside one process exchange the raw device pointer instead.
+
+CUDA IPC works between processes of one host only. Peers on different hosts (or without a CUDA
+device) therefore fall back to streaming the object over the same TCP connection, straight from
+the sender's mapping into the receiver's ``<object>.tmp`` mapping, which is what the reference does
+for every transfer. ``MLFLASHPOINT_REPL_TRANSPORT`` = ``auto`` (default) | ``nvlink`` | ``tcp``.
 """
 
 from __future__ import annotations
@@ -83,6 +88,34 @@ def _split_address(address: str) -> Tuple[str, int]:
     return host, int(port)
 
 
+def _host_identity() -> str:
+    """Identifies this machine boot: CUDA IPC handles are only meaningful between equal identities."""
+    try:
+        with open("/proc/sys/kernel/random/boot_id") as f:
+            boot = f.read().strip()
+    except OSError:
+        boot = ""
+    return f"{socket.gethostname()}/{boot}"
+
+
+def _cuda_usable() -> bool:
+    try:
+        import torch
+
+        return bool(torch.cuda.is_available())
+    except Exception:
+        return False
+
+
+def _recv_into(sock: socket.socket, view: memoryview) -> None:
+    got = 0
+    while got < len(view):
+        n = sock.recv_into(view[got:], min(len(view) - got, 4 << 20))
+        if n == 0:
+            raise ConnectionError("peer closed the connection in the middle of an object")
+        got += n
+
+
 class _DeviceBuffer:
     """Device memory from plain ``cudaMalloc`` (so that an IPC handle can be exported for it)."""
 
@@ -128,6 +161,8 @@ class TransferService:
         self._opened_ipc: Dict[str, int] = {}
         self._bounce: Optional[_DeviceBuffer] = None
         self._stream = ctypes.c_void_p()
+        self._transport = os.environ.get("MLFLASHPOINT_REPL_TRANSPORT", "auto").lower()
+        self._cuda = False
         # device timing of the most recent outgoing transfer: {"bytes", "hop_ms", "from_hbm_image"}
         self.last_put_stats: Optional[dict] = None
 
@@ -140,10 +175,16 @@ class TransferService:
         short-lived and not pooled.
         """
         try:
-            dev = ctypes.c_int32()
-            _native.check(_native.lib().mlf_get_device(ctypes.byref(dev)))
-            self._device = dev.value
-            _native.check(_native.lib().mlf_stream_create(ctypes.byref(self._stream)))
+            if self._transport not in ("auto", "nvlink", "tcp"):
+                raise ValueError(f"unknown MLFLASHPOINT_REPL_TRANSPORT '{self._transport}'")
+            self._cuda = self._transport != "tcp" and _cuda_usable()
+            if self._transport == "nvlink" and not self._cuda:
+                raise RuntimeError("the nvlink transport needs a CUDA device")
+            if self._cuda:
+                dev = ctypes.c_int32()
+                _native.check(_native.lib().mlf_get_device(ctypes.byref(dev)))
+                self._device = dev.value
+                _native.check(_native.lib().mlf_stream_create(ctypes.byref(self._stream)))
             self._rank = global_rank
             self._host = os.environ.get("MLFLASHPOINT_REPL_HOST", "127.0.0.1")
             listener = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
@@ -171,7 +212,8 @@ class TransferService:
 
         An exporter may free a buffer only after every importer has closed it, so ranks that shut
         down together call this first, synchronise, and then ``shutdown``."""
-        _native.lib().mlf_set_device(self._device)
+        if self._cuda:
+            _native.lib().mlf_set_device(self._device)
         with self._lock:
             opened, self._opened_ipc = self._opened_ipc, {}
         for ptr in opened.values():
@@ -194,7 +236,8 @@ class TransferService:
             self._listener.close()
         if self._workers:
             self._workers.shutdown(wait=True, cancel_futures=True)
-        _native.lib().mlf_set_device(self._device)
+        if self._cuda:
+            _native.lib().mlf_set_device(self._device)
         for ptr in self._opened_ipc.values():
             _native.lib().mlf_ipc_close(ctypes.c_void_p(ptr))
         self._opened_ipc.clear()
@@ -279,12 +322,27 @@ class TransferService:
         if data_size <= 0 or not data_ptr:
             raise ValueError("async_put needs a non-empty source")
         lib = _native.lib()
-        _native.check(lib.mlf_set_device(self._device))
+        if self._cuda:
+            _native.check(lib.mlf_set_device(self._device))
         with self._connect(dest_address) as sock:
-            _send_msg(sock, {"op": "put_begin", "obj": dest_object_id, "size": data_size, "src_rank": self._rank, "task": task_id, "exact_path": exact_path})
+            _send_msg(
+                sock,
+                {
+                    "op": "put_begin", "obj": dest_object_id, "size": data_size, "src_rank": self._rank, "task": task_id,
+                    "exact_path": exact_path, "host": _host_identity(), "gpu": self._cuda,
+                },
+            )
             reply = _recv_msg(sock)
             if not reply.get("ok"):
                 raise RuntimeError(f"peer refused put of '{dest_object_id}': {reply.get('error')}")
+            if reply.get("transport") == "tcp":
+                source = (ctypes.c_ubyte * data_size).from_address(data_ptr)
+                sock.sendall(memoryview(source).cast("B"))
+                self.last_put_stats = {"bytes": data_size, "hop_ms": None, "from_hbm_image": False, "transport": "tcp"}
+                final = _recv_msg(sock)
+                if not final.get("ok"):
+                    raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
+                return
             peer = self._peer_pointer(reply)
             stream = self._stream
             twin = None if exact_path else gpu_engine.resident_image(dest_object_id, data_size - METADATA_SIZE)
@@ -367,9 +425,15 @@ class TransferService:
         from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
 
         lib = _native.lib()
-        _native.check(lib.mlf_set_device(self._device))
         size = int(request["size"])
         source = int(request.get("src_rank", -1))
+        same_host = request.get("host") == _host_identity()
+        if not (self._cuda and request.get("gpu") and same_host):
+            if self._transport == "nvlink":
+                raise RuntimeError("the nvlink transport needs both peers on one host with CUDA devices")
+            self._serve_put_tcp(conn, request, size, source)
+            return
+        _native.check(lib.mlf_set_device(self._device))
         with self._lock:
             gate = self._inbound_locks.setdefault(source, threading.Lock())
         with gate:  # one inbound object per source at a time: they share the landing buffer
@@ -380,7 +444,7 @@ class TransferService:
                 landing = _DeviceBuffer(size)
                 self._inbound[source] = landing
             token = uuid.uuid4().hex
-            _send_msg(conn, {"ok": True, "token": token, "ipc": landing.ipc_hex, "ptr": landing.ptr, "pid": os.getpid(), "device": self._device})
+            _send_msg(conn, {"ok": True, "transport": "nvlink", "token": token, "ipc": landing.ipc_hex, "ptr": landing.ptr, "pid": os.getpid(), "device": self._device})
             commit = _recv_msg(conn)
             if commit.get("op") != "put_commit" or commit.get("token") != token:
                 raise RuntimeError("put was not committed by the sender")
@@ -420,6 +484,27 @@ class TransferService:
                 finally:
                     target.close()
                 os.rename(tmp_path, final_path)
+        _send_msg(conn, {"ok": True})
+
+    def _serve_put_tcp(self, conn: socket.socket, request: dict, size: int, source: int) -> None:
+        """Receives the object's bytes from the connection into ``<object>.tmp`` and renames it."""
+        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+        final_path = request["obj"] if request.get("exact_path") else self._map_path(request["obj"], source)
+        tmp_path = final_path + ".tmp"
+        target = BufferObject(tmp_path, size, overwrite=True)
+        try:
+            _send_msg(conn, {"ok": True, "transport": "tcp"})
+            _recv_into(conn, memoryview(target))
+        except BaseException:
+            target.close()
+            try:
+                os.remove(tmp_path)  # never leave a partial object behind
+            except OSError:
+                pass
+            raise
+        target.close()
+        os.rename(tmp_path, final_path)
         _send_msg(conn, {"ok": True})
 
     def _serve_get(self, conn: socket.socket, request: dict) -> None:

@@ -1,0 +1,97 @@
+"""The transfer service's TCP transport (peers on different hosts, or no GPU), on the CPU.
+
+Mirrors the reference's point-to-point service tests: two services on 127.0.0.1, put / get round
+trips, temporary file + rename on the receiver, failures surfacing on the future, shutdown failing
+what is pending. Failures are made on the host: a dead address, a missing object, a peer that
+closes the connection in the middle of an object."""
+
+import os
+import socket
+import threading
+
+import pytest
+
+from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+
+@pytest.fixture
+def pair(tmp_path, monkeypatch):
+    monkeypatch.setenv("MLFLASHPOINT_REPL_TRANSPORT", "tcp")
+    from ml_flashpoint.replication.transfer_service.transfer_service_ext import TransferService
+
+    replicas = str(tmp_path / "replicas")
+    a = TransferService()
+    b = TransferService(replica_path_mapper=lambda obj, src: os.path.join(replicas, f"src{src}", obj.lstrip("/")))
+    assert a.initialize(0, threads=4, global_rank=0) > 0 and b.initialize(0, threads=4, global_rank=1) > 0
+    yield a, b, replicas
+    a.shutdown()
+    b.shutdown()
+
+
+def _object(path, nbytes, seed):
+    import random
+
+    data = random.Random(seed).randbytes(nbytes)
+    buf = BufferObject(str(path), nbytes, overwrite=True)
+    memoryview(buf)[:] = data
+    buf.close()
+    return data
+
+
+@pytest.mark.parametrize("nbytes", [4096, 4096 + 1, 9 << 20])
+def test_put_and_get_round_trip_over_tcp(pair, tmp_path, nbytes):
+    a, b, replicas = pair
+    src = tmp_path / "primary" / "step-1_ckpt" / "o_src0.distcp"
+    data = _object(src, nbytes, nbytes)
+    ro = BufferObject(str(src))
+    result = a.async_put(ro.get_data_ptr(), ro.get_capacity(), b.address, str(src)).result(timeout=60)
+    ro.close()
+    assert result.success and a.last_put_stats["transport"] == "tcp"
+    landed = os.path.join(replicas, "src0", str(src).lstrip("/"))
+    assert open(landed, "rb").read() == data and not os.path.exists(landed + ".tmp")
+    back = str(tmp_path / "restored.distcp")
+    assert a.async_get(str(src), b.address, back).result(timeout=60).success
+    assert open(back, "rb").read() == data
+
+
+def test_failures_and_shutdown(pair, tmp_path):
+    a, b, replicas = pair
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        dead = f"127.0.0.1:{s.getsockname()[1]}"
+    src = tmp_path / "o.distcp"
+    _object(src, 8192, 1)
+    ro = BufferObject(str(src))
+    with pytest.raises(RuntimeError, match="cannot reach"):
+        a.async_put(ro.get_data_ptr(), ro.get_capacity(), dead, str(src)).result(timeout=60)
+    with pytest.raises(RuntimeError, match="not held here"):
+        a.async_get("/no/such/object", b.address, str(tmp_path / "x")).result(timeout=60)
+    with pytest.raises(RuntimeError):
+        a.async_put(ro.get_data_ptr(), ro.get_capacity(), "not-an-address", str(src)).result(timeout=60)
+    a.shutdown()
+    a.shutdown()  # idempotent
+    with pytest.raises(RuntimeError, match="not running"):
+        a.async_put(ro.get_data_ptr(), ro.get_capacity(), b.address, str(src)).result(timeout=5)
+    ro.close()
+
+
+def test_receiver_discards_a_partial_object(pair, tmp_path):
+    """A sender that dies in the middle of an object must not leave a file (or a .tmp) behind."""
+    import json
+    import struct
+
+    _, b, replicas = pair
+    host, port = b.address.split(":")
+    with socket.create_connection((host, int(port))) as s:
+        msg = json.dumps({"op": "put_begin", "obj": "/c/step-1_ckpt/o_src5.distcp", "size": 1 << 20, "src_rank": 5, "host": "elsewhere", "gpu": False}).encode()
+        s.sendall(struct.pack("<I", len(msg)) + msg)
+        (n,) = struct.unpack("<I", s.recv(4))
+        assert json.loads(s.recv(n))["transport"] == "tcp"
+        s.sendall(b"x" * 1000)  # then the "host" goes away
+    target = os.path.join(replicas, "src5", "c/step-1_ckpt/o_src5.distcp")
+    deadline = threading.Event()
+    for _ in range(100):
+        if not os.path.exists(target + ".tmp"):
+            break
+        deadline.wait(0.05)
+    assert not os.path.exists(target) and not os.path.exists(target + ".tmp")
