@@ -271,3 +271,92 @@ def test_read_tensor_per_item_api_matches_reference(tmp_path, golden_dir, engine
             got = loader.read_tensor(_create_file_view(stream, info.offset, info.length), req, use_optimized_loader=True)
             assert got.device.type == "cpu" and tuple(got.shape) == tuple(lens)
             assert tensor_bytes(got).hex() == row["hex"], row["i"]
+
+
+def test_resharded_reads_of_large_tensors(tmp_path, engine):
+    """Sub-block restores as a different sharding would issue them: long rows (chunked through the
+    staging ring), short rows, leading-dimension ranges and strided targets, against torch slicing."""
+    from torch.distributed.checkpoint.metadata import MetadataIndex
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    g = torch.Generator().manual_seed(11)
+    big = torch.randint(-9999, 9999, (48, 40000), generator=g, dtype=torch.int32).cuda()
+    wide = torch.randn((300, 515), generator=g).to(torch.bfloat16).cuda()
+    cube = torch.randint(0, 255, (20, 33, 70), generator=g, dtype=torch.uint8).cuda()
+    tensors = {"pad": torch.zeros(3, dtype=torch.uint8, device="cuda"), "big": big, "wide": wide, "cube": cube}
+    _, com, ckpt, buckets, results = _save({"tensors": tensors, "blobs": {}, "bucket_count": 1}, tmp_path, engine)
+    loader = make_loader(com, copy_engine=engine)
+    storage = {r.index.fqn: (r.index, r.storage_data) for r in results}
+    reads = [
+        ("big", (0, 1000), (48, 29000)),     # rows of 116 KB: chunked rows
+        ("big", (5, 0), (17, 40000)),        # leading-dimension range: one flat run
+        ("big", (7, 39990), (30, 10)),       # 40-byte rows
+        ("wide", (10, 3), (200, 500)),
+        ("wide", (0, 0), (300, 515)),
+        ("cube", (3, 4, 5), (10, 20, 60)),
+    ]
+    for fqn, offs, lens in reads:
+        idx, info = storage[fqn]
+        source = tensors[fqn]
+        want = source[tuple(slice(o, o + n) for o, n in zip(offs, lens))]
+        for strided in (False, True):
+            if strided and len(lens) == 2:
+                target = torch.zeros((lens[1], lens[0]), dtype=source.dtype, device="cuda").t()
+            else:
+                target = torch.zeros(lens, dtype=source.dtype, device="cuda")
+            req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0] * len(lens)), idx, torch.Size(offs), torch.Size(lens))
+
+            class _Planner:
+                def resolve_tensor(self, r):
+                    return target
+
+                def commit_tensor(self, r, t):
+                    pass
+
+            loader.read_data(buckets[0].object_id, [req], _Planner(), {idx: info})
+            torch.cuda.synchronize()
+            assert torch.equal(target, want), (fqn, offs, lens, strided)
+
+
+def test_single_tensor_larger_than_4_gib(shm_path, engine):
+    """64-bit offsets inside one segment: a 4.5 GiB tensor behind an odd-sized prefix."""
+    import numpy as np
+
+    free_dev = torch.cuda.mem_get_info()[0]
+    free_shm = os.statvfs(str(shm_path)).f_bavail * os.statvfs(str(shm_path)).f_frsize
+    n = (9 << 29) + 12345  # 4.5 GiB and a bit
+    if free_dev < 3 * n or free_shm < 2 * n:
+        pytest.skip("not enough memory for a > 4 GiB object on this box")
+    huge = torch.empty(n, dtype=torch.uint8, device="cuda")
+    huge.random_(0, 256)
+    tensors = {"pad": torch.arange(7, dtype=torch.uint8, device="cuda"), "huge": huge}
+    from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
+
+    CheckpointObjectManager._worker_pool = None
+    _, com, ckpt, buckets, results = _save({"tensors": tensors, "blobs": {}, "bucket_count": 1}, shm_path, engine, initial_buffer_size_bytes=n + (1 << 20))
+    info = {r.index.fqn: r.storage_data for r in results}["huge"]
+    header = len(oracle.header_bytes("uint8", (n,)))
+    mapped = np.memmap(str(buckets[0].object_id), dtype=np.uint8, mode="r")
+    payload_at = 4096 + info.offset + header
+    assert info.length == header + n and mapped.shape[0] == 4096 + info.offset + info.length
+    # spot checks around the 4 GiB boundary, both ends and tile edges, then a strided full compare on the GPU
+    host = huge.cpu().numpy()
+    for at in (0, 65535, 65536, (1 << 32) - 70000, (1 << 32) - 1, 1 << 32, (1 << 32) + 65537, n - 4097, n - 1):
+        lo, hi = max(0, at - 100), min(n, at + 100)
+        assert bytes(mapped[payload_at + lo : payload_at + hi]) == bytes(host[lo:hi]), at
+    back = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    idx = {r.index.fqn: r.index for r in results}["huge"]
+    req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0]), idx, torch.Size([0]), torch.Size([n]))
+
+    class _Planner:
+        def resolve_tensor(self, r):
+            return back
+
+        def commit_tensor(self, r, t):
+            pass
+
+    make_loader(com, copy_engine=engine).read_data(buckets[0].object_id, [req], _Planner(), {idx: info})
+    torch.cuda.synchronize()
+    assert torch.equal(back, huge)
