@@ -298,6 +298,11 @@ class CudaCopyEngine:
     def staging(self, nbytes: int) -> torch.Tensor:
         """HBM image buffer of at least ``nbytes`` (grown geometrically, reused across saves)."""
         if self._staging is None or self._staging.numel() < nbytes:
+            if self._last_done is not None:
+                # a transfer on the copy stream may still be reading the buffer that is about to be
+                # returned to the allocator, which knows nothing about that stream
+                self._last_done.synchronize()
+            self._resident = None
             self._staging = None
             grown = max(nbytes, 1 << 20)
             self._staging = torch.empty(grown, dtype=torch.uint8, device=self.device)
