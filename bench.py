@@ -302,6 +302,7 @@ def main() -> None:
     ap.add_argument("--no-restore", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replication", action="store_true")
+    ap.add_argument("--no-overlap-probe", action="store_true")
     ap.add_argument("--cpu-sample-gb", type=float, default=2.0)
     ap.add_argument("--workdir", default=None)
     ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
@@ -518,6 +519,54 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
     }
 
 
+def overlap_probe(saver, com, base, state, items, resolver, rank, device) -> dict:
+    """Runs a fixed batch of bf16 GEMMs (standing in for training compute) alone and again while an
+    overlapped save is in flight, and times both on the device."""
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+
+    a = torch.randn(8192, 8192, device=device, dtype=torch.bfloat16)
+    b = torch.randn(8192, 8192, device=device, dtype=torch.bfloat16)
+    reps = 150
+
+    def gemms():
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            torch.matmul(a, b)
+        t1.record()
+        return t0, t1
+
+    for _ in range(2):
+        t0, t1 = gemms()
+        torch.cuda.synchronize()
+    alone_ms = t0.elapsed_time(t1)
+
+    if state["prev"] is not None:
+        com.delete_container(state["prev"])
+    ckpt = CheckpointContainerId(os.path.join(base, f"step-{state['step']}_ckpt"))
+    state["step"] += 1
+    state["prev"] = ckpt
+    saver.initialize_checkpoint(ckpt)
+    buckets = saver.prepare_write_data(ckpt, items, resolver, f"__{rank}_", bucket_count=1)
+    torch.cuda.synchronize()
+    wall0 = time.perf_counter()
+    pending = saver.write_data_async(ckpt, buckets)
+    t0, t1 = gemms()  # queued right behind the launch: runs while the pack kernel and the drain do
+    results = pending.result()
+    save_wall_ms = (time.perf_counter() - wall0) * 1e3
+    torch.cuda.synchronize()
+    with_save_ms = t0.elapsed_time(t1)
+    return {
+        "gemm_batch_ms_alone": alone_ms,
+        "gemm_batch_ms_during_save": with_save_ms,
+        "slowdown": with_save_ms / alone_ms,
+        "save_wall_ms_with_gemms_running": save_wall_ms,
+        "what": f"{reps} x 8192^3 bf16 matmul on the training stream, queued while write_data_async's kernel and transfer run",
+        "_results": results,
+        "_buckets": buckets,
+    }
+
+
 def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> None:
     import ctypes
 
@@ -621,6 +670,12 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
         pending.wait_safe_to_mutate()
         async_block_ms.append((time.perf_counter() - t0) * 1e3)
         results = pending.result()
+
+    # ---- does a save in flight slow the training stream down? (background load: library GEMMs)
+    overlap = None
+    if world_size == 1 and not args.no_overlap_probe:
+        overlap = overlap_probe(saver, com, base, state, items, resolver, rank, device)
+        results, buckets = overlap.pop("_results"), overlap.pop("_buckets")
 
     # ---- restore (its own timed region; not part of the save step)
     restore = None
@@ -731,6 +786,7 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
             "api": "DefaultMLFlashpointCheckpointSaver.write_data (object closed on return)",
         },
         "restore": restore,
+        "overlap": overlap,
         "replication": replication,
         "roofline": {
             "kernel": "mlf_plan_kernel<PACK>",
