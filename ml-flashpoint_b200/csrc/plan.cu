@@ -6,8 +6,9 @@
 // over the tile prefix, and move that tile. Four segment kinds exist:
 //   FLAT       both sides contiguous: 64 KiB byte runs, destination-aligned 16-byte vectors
 //   ROWS       innermost dimension contiguous on both sides: runs per row (or per row chunk)
-//   TRANSPOSE  the tensor's unit-stride dimension is not the image's: tiles of 32 elements by 256
-//              bytes through shared memory so both sides are touched along their contiguous direction
+//   TRANSPOSE  the tensor's unit-stride dimension is not the image's: sub-tiles of 32 elements by 256
+//              bytes through shared memory so both sides are touched along their contiguous direction,
+//              the loads of one sub-tile in flight while the previous one is written out
 //   GENERIC    anything else (stepped slices, expands): one element per thread
 // The image side has byte alignment only, because the object format is unpadded.
 #include <stdlib.h>
@@ -28,10 +29,9 @@ constexpr uint32_t kThreads = 256;
 constexpr uint64_t kTileBytes = 64 * 1024;    // FLAT tile and ROWS chunk
 constexpr uint64_t kRowSplitBytes = 16 * 1024;  // rows at least this long are cut into chunks
 constexpr int kTransCols = 32;                // TRANSPOSE tile: elements along the tensor-contiguous dim
-constexpr int kTransRowBytes = 256;           // TRANSPOSE tile: bytes along the image-contiguous dim
 constexpr int kTransSmemBytes = 32 * 264 + 16;  // 32 rows at the widest pitch + slack for vector reads
-constexpr int kTransNarrowBytes = 8192;       // staging bytes of a tile made of whole short rows
 constexpr uint64_t kGenericTile = 4096;       // GENERIC elements per tile
+constexpr uint64_t kRowsPerTileMax = 64;      // short ROWS: at most this many rows per tile (8 per warp)
 
 enum SegKind : uint32_t { kFlat = 0, kRows = 1, kTranspose = 2, kGeneric = 3 };
 
@@ -45,8 +45,8 @@ struct Seg {
   uint32_t b;  // FLAT: destination address mod 128 | ROWS: rows per tile (0 = chunked rows) | TRANSPOSE: tiles along L
   uint32_t c;  // ROWS: chunks per row                   | TRANSPOSE: index of dimension C
   uint32_t image_aligned;  // 1 if every image element address is a multiple of esize
-  uint32_t d;  // TRANSPOSE: elements along C per tile when the tile spans whole image rows (0 = 32 x 256 B tiles)
-  uint32_t reserved;
+  uint32_t d;  // TRANSPOSE: image rows per sub-tile when sub-tiles span whole image rows (0 = 32-row sub-tiles)
+  uint32_t reserved;  // TRANSPOSE with d != 0: 1 = the rows are contiguous in the tensor too (no transposition)
   int64_t shape[MLF_MAX_DIMS];
   int64_t tstride[MLF_MAX_DIMS];  // bytes
   int64_t istride[MLF_MAX_DIMS];  // bytes
@@ -74,40 +74,82 @@ __device__ __forceinline__ void store_elem(uint8_t* p, T v, bool aligned) {
   for (int k = 0; k < (int)sizeof(T); ++k) p[k] = b[k];
 }
 
-// Copies `len` bytes from global memory at any alignment into a 4-byte aligned shared-memory
-// row with a group of `nthr` threads (a warp by default): aligned 32-bit loads, funnel-shifted into place.
-__device__ __forceinline__ void load_row_to_smem(uint8_t* __restrict__ row, const uint8_t* __restrict__ gsrc, uint32_t len,
-                                                 unsigned lane, unsigned nthr = 32) {
+// Geometry of a TRANSPOSE tile for elements of E bytes (shared by the planner and the kernel).
+// A tile is kTransSub sub-tiles that a CTA of kThreads threads moves one after the other through
+// one shared-memory staging area, software-pipelined: the global loads of sub-tile j+1 are in
+// flight while sub-tile j is written out.
+//   wide rows   : a sub-tile is 32 elements along C (contiguous in the tensor) by kRowBytes along L
+//                 (contiguous in the image); the sub-tiles of a tile follow one another along L
+//   narrow rows : image rows shorter than kRowBytes lying back to back; a sub-tile is as many whole
+//                 rows as fit kNarrowBytes, i.e. ONE contiguous run of the image
+constexpr int kTransSub = 4;
+template <int E>
+struct TransGeom {
+  static constexpr int kRowBytes = E == 1 ? 128 : 256;
+  static constexpr int kRowElems = kRowBytes / E;
+  static constexpr int kPitch = E == 8 ? kRowBytes + 8 : kRowBytes + 4;  // odd word count: columns spread over banks
+  static constexpr int kPerThread = kRowElems * kTransCols / (int)kThreads;  // 16, 16, 8, 4
+  static constexpr int kNarrowBytes = E == 1 ? 4096 : 8192;
+  static constexpr int kNarrowPerThread = kNarrowBytes / E / (int)kThreads;  // 16, 16, 8, 4
+  static constexpr int kWordsPerRow = kRowBytes / 4;
+  static constexpr int kRowsPerPass = (int)kThreads / kWordsPerRow;
+  static constexpr int kPasses = kTransCols / kRowsPerPass;  // 4 or 8
+  static constexpr int kNarrowWordsPerThread = kNarrowBytes / 4 / (int)kThreads;  // 4 or 8
+};
+inline uint32_t trans_row_bytes(uint32_t esize) { return esize == 1 ? 128u : 256u; }
+inline uint32_t trans_narrow_bytes(uint32_t esize) { return esize == 1 ? 4096u : 8192u; }
+
+// Misaligned global words -> aligned shared-memory words: word i of the run that starts at
+// `gsrc` (any alignment). Callers load lo/hi for a batch of words first and combine afterwards.
+__device__ __forceinline__ void ld_word_pair(const uint8_t* gsrc, uint32_t i, bool ok, uint32_t* lo, uint32_t* hi) {
   const uint32_t m = (uint32_t)((uintptr_t)gsrc & 3u);
-  const uint32_t* __restrict__ a = reinterpret_cast<const uint32_t*>(gsrc - m);
-  const uint32_t nwords = len >> 2;
-  uint32_t* __restrict__ out = reinterpret_cast<uint32_t*>(row);
-  for (uint32_t i = lane; i < nwords; i += nthr) {
-    const uint32_t lo = a[i];
-    const uint32_t hi = m ? a[i + 1] : 0u;
-    out[i] = __funnelshift_r(lo, hi, 8u * m);
-  }
-  const uint32_t tail = len & 3u;
-  if (lane < tail) row[(nwords << 2) + lane] = gsrc[(nwords << 2) + lane];
+  const uint32_t* a = reinterpret_cast<const uint32_t*>(gsrc - m);
+  *lo = ok ? __ldg(a + i) : 0u;
+  *hi = (ok && m) ? __ldg(a + i + 1) : 0u;
+}
+__device__ __forceinline__ uint32_t join_word_pair(const uint8_t* gsrc, uint32_t lo, uint32_t hi) {
+  return __funnelshift_r(lo, hi, 8u * (uint32_t)((uintptr_t)gsrc & 3u));
 }
 
-// One tile of a TRANSPOSE segment: 32 elements along C (contiguous in the tensor) by 256 bytes
-// along L (contiguous in the image), staged in shared memory as 32 image rows. The tensor side is
-// touched with naturally aligned element accesses coalesced along C; the image side, which has
-// byte alignment only, is moved a row at a time by a warp with 16-byte vectors (drain_slot) or
-// aligned words (load_row_to_smem).
+// Shared-memory swizzle of the narrow-row staging area: byte offset -> byte offset with the
+// 16-byte granule index inside each 128-byte line XORed with the line number. Image rows of 64 or
+// 128 bytes would otherwise put a whole warp's column accesses on one bank.
+__device__ __forceinline__ uint32_t swz(uint32_t off) { return off ^ ((off >> 3) & 0x70u); }
+
+// drain_slot for a swizzled staging area: staged byte k (logical offset) goes to dst[k].
+__device__ __forceinline__ void drain_swizzled(uint8_t* __restrict__ dst, const uint8_t* __restrict__ staged, uint32_t len,
+                                               unsigned tid, unsigned nthr) {
+  const uint32_t head = min((16u - (uint32_t)((uintptr_t)dst & 15u)) & 15u, len);
+  if (tid < head) dst[tid] = staged[swz(tid)];
+  const uint32_t nvec = (len - head) >> 4;
+  uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + head);
+  auto granule = [&](uint32_t v) { return *reinterpret_cast<const uint4*>(staged + swz(v << 4)); };
+  if (head == 0) {
+#pragma unroll 4
+    for (uint32_t i = tid; i < nvec; i += nthr) mlf::st_vec(d4 + i, granule(i));
+  } else {
+#pragma unroll 4
+    for (uint32_t i = tid; i < nvec; i += nthr) mlf::st_vec(d4 + i, mlf::realign(granule(i), granule(i + 1), head));
+  }
+  const uint32_t tail = (len - head) & 15u;
+  if (tid < tail) {
+    const uint32_t o = head + (nvec << 4) + tid;
+    dst[o] = staged[swz(o)];
+  }
+}
+
+// Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
 template <typename T, int DIR>
-__device__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
+__device__ __noinline__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
   constexpr int E = (int)sizeof(T);
-  constexpr int TL = kTransRowBytes / E;
-  constexpr int ROW = E == 8 ? 264 : 260;  // row pitch: odd word count keeps column accesses off one bank
+  using G = TransGeom<E>;
+  constexpr int TL = G::kRowElems;
+  constexpr int ROW = G::kPitch;
   const int L = (int)g.ndim - 1;
   const int C = (int)g.c;
   const uint32_t tiles_per_batch = (uint32_t)g.a;
   uint64_t batch = local / tiles_per_batch;
   const uint32_t in_batch = local % tiles_per_batch;
-  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransCols;
-  const int64_t l0 = (int64_t)(in_batch % g.b) * TL;
   int64_t toff = 0, ioff = 0;
   for (int d = L - 1; d >= 0; --d) {
     if (d == C) continue;
@@ -120,54 +162,187 @@ __device__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uin
   uint8_t* ibase = image + g.image_off + ioff;
   const int64_t nC = g.shape[C], nL = g.shape[L];
   const int64_t tsL = g.tstride[L], isC = g.istride[C];
+  const unsigned tid = threadIdx.x;
+
   if (g.d != 0) {
-    // Narrow image rows (shorter than 256 bytes) that follow one another without a gap: the tile
-    // takes g.d consecutive rows whole, which is ONE contiguous run in the image.
-    const int64_t cn0 = (int64_t)in_batch * g.d;
-    const int ncn = (int)min((int64_t)g.d, nC - cn0);
-    const int nln = (int)nL;
-    const uint32_t run = (uint32_t)ncn * (uint32_t)nln * E;
-    uint8_t* irun = ibase + cn0 * isC;
-    uint8_t* trun = tbase + cn0 * (int64_t)E;
+    // ---- narrow rows: a sub-tile is g.d whole image rows = one contiguous run of the image,
+    // staged in shared memory in image order (16-byte granules swizzled, see swz()). Threads walk
+    // the sub-tile's elements along the tensor's unit-stride dimension: element number n is
+    // (slow, fast) = (n / nfast, n % nfast), advanced incrementally by kThreads per step.
+    //   transposed (g.reserved == 0): fast = image row c, slow = position l in the row
+    //   row order  (g.reserved == 1): fast = position in the row, slow = image row
+    const bool row_order = g.reserved != 0;
+    const uint32_t nln = (uint32_t)nL;
+    const int64_t cfirst = (int64_t)in_batch * g.d * kTransSub;
+    const int nsub = (int)min((int64_t)kTransSub, (nC - cfirst + g.d - 1) / g.d);
+    const int64_t ts_row = g.tstride[C];                 // tensor step between image rows
+    const int64_t ts_slow = row_order ? ts_row : tsL;    // tensor step of the walk's slow index
+    struct Walk {
+      uint32_t slow, fast, dslow, dfast, nfast;
+      __device__ __forceinline__ void start(uint32_t n, unsigned t) {
+        nfast = n;
+        slow = t / n;
+        fast = t % n;
+        dslow = kThreads / n;
+        dfast = kThreads % n;
+      }
+      __device__ __forceinline__ void next() {
+        fast += dfast;
+        slow += dslow;
+        if (fast >= nfast) {
+          fast -= nfast;
+          ++slow;
+        }
+      }
+    };
+    auto rows_of = [&](int j) { return (uint32_t)min((int64_t)g.d, nC - (cfirst + (int64_t)j * g.d)); };
+    auto staged_at = [&](const Walk& w) { return swz((row_order ? w.slow * nln + w.fast : w.fast * nln + w.slow) * E); };
+    constexpr int NE = G::kNarrowPerThread;
     if (DIR == MLF_PACK) {
-      for (int l = 0; l < nln; ++l)
-        for (int c = (int)threadIdx.x; c < ncn; c += (int)blockDim.x)
-          *reinterpret_cast<T*>(smem + ((size_t)c * nln + l) * E) = *reinterpret_cast<const T*>(trun + c * (int64_t)E + l * tsL);
-      __syncthreads();
-      mlf::drain_slot(irun, smem, 0, run, threadIdx.x, blockDim.x);
+      T v[NE];
+      auto load = [&](int j) {
+        const uint32_t ncn = rows_of(j), nel = ncn * nln;
+        const uint8_t* trun = tbase + (cfirst + (int64_t)j * g.d) * ts_row;
+        Walk w;
+        w.start(row_order ? nln : ncn, tid);
+#pragma unroll
+        for (int k = 0; k < NE; ++k) {
+          v[k] = (tid + (uint32_t)k * kThreads < nel) ? __ldg(reinterpret_cast<const T*>(trun + (int64_t)w.fast * E + (int64_t)w.slow * ts_slow)) : T(0);
+          w.next();
+        }
+      };
+      load(0);
+      for (int j = 0; j < nsub; ++j) {
+        const uint32_t ncn = rows_of(j), nel = ncn * nln;
+        Walk w;
+        w.start(row_order ? nln : ncn, tid);
+#pragma unroll
+        for (int k = 0; k < NE; ++k) {
+          if (tid + (uint32_t)k * kThreads < nel) *reinterpret_cast<T*>(smem + staged_at(w)) = v[k];
+          w.next();
+        }
+        __syncthreads();
+        if (j + 1 < nsub) load(j + 1);
+        drain_swizzled(ibase + (cfirst + (int64_t)j * g.d) * isC, smem, nel * E, tid, kThreads);
+        __syncthreads();
+      }
     } else {
-      load_row_to_smem(smem, irun, run, threadIdx.x, blockDim.x);
-      __syncthreads();
-      for (int l = 0; l < nln; ++l)
-        for (int c = (int)threadIdx.x; c < ncn; c += (int)blockDim.x)
-          *reinterpret_cast<T*>(trun + c * (int64_t)E + l * tsL) = *reinterpret_cast<const T*>(smem + ((size_t)c * nln + l) * E);
+      constexpr int N = G::kNarrowWordsPerThread;
+      uint32_t lo[N], hi[N];
+      auto load = [&](int j) {
+        const uint8_t* irun = ibase + (cfirst + (int64_t)j * g.d) * isC;
+        const uint32_t nwords = (rows_of(j) * nln * E) >> 2;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const uint32_t i = tid + (uint32_t)k * kThreads;
+          ld_word_pair(irun, i, i < nwords, &lo[k], &hi[k]);
+        }
+      };
+      load(0);
+      for (int j = 0; j < nsub; ++j) {
+        const uint32_t ncn = rows_of(j), nel = ncn * nln, run = nel * E, nwords = run >> 2;
+        const uint8_t* irun = ibase + (cfirst + (int64_t)j * g.d) * isC;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const uint32_t i = tid + (uint32_t)k * kThreads;
+          if (i < nwords) *reinterpret_cast<uint32_t*>(smem + swz(i << 2)) = join_word_pair(irun, lo[k], hi[k]);
+        }
+        if (tid < (run & 3u)) smem[swz((nwords << 2) + tid)] = irun[(nwords << 2) + tid];
+        __syncthreads();
+        if (j + 1 < nsub) load(j + 1);
+        uint8_t* trun = tbase + (cfirst + (int64_t)j * g.d) * ts_row;
+        Walk w;
+        w.start(row_order ? nln : ncn, tid);
+#pragma unroll
+        for (int k = 0; k < NE; ++k) {
+          if (tid + (uint32_t)k * kThreads < nel)
+            *reinterpret_cast<T*>(trun + (int64_t)w.fast * E + (int64_t)w.slow * ts_slow) = *reinterpret_cast<const T*>(smem + staged_at(w));
+          w.next();
+        }
+        __syncthreads();
+      }
     }
-    __syncthreads();
     return;
   }
-  const int nc = (int)min((int64_t)kTransCols, nC - c0);  // rows of this tile
-  const int nl = (int)min((int64_t)TL, nL - l0);          // elements per row
-  const unsigned tx = threadIdx.x & 31u, ty = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+
+  // ---- wide rows
+  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransCols;
+  const int64_t lfirst = (int64_t)(in_batch % g.b) * (TL * kTransSub);
+  const int nsub = (int)min((int64_t)kTransSub, (nL - lfirst + TL - 1) / TL);
+  const int nc = (int)min((int64_t)kTransCols, nC - c0);  // image rows of this tile
+  const unsigned tx = tid & 31u, ty = tid >> 5;
+  constexpr int NW = (int)kThreads / 32;
+  auto elems_of = [&](int j) { return (int)min((int64_t)TL, nL - (lfirst + (int64_t)j * TL)); };
+  uint8_t* tcol = tbase + (c0 + tx) * (int64_t)E + lfirst * tsL;  // this thread's column on the tensor side
   if (DIR == MLF_PACK) {
-    if ((int)tx < nc)
-      for (int l = (int)ty; l < nl; l += (int)nwarp)
-        *reinterpret_cast<T*>(smem + tx * ROW + l * E) =
-            *reinterpret_cast<const T*>(tbase + (c0 + tx) * (int64_t)E + (l0 + l) * tsL);
-    __syncthreads();
-    for (int r = (int)ty; r < nc; r += (int)nwarp) {
-      const uint32_t at = (uint32_t)r * ROW;
-      mlf::drain_slot(ibase + (c0 + r) * isC + l0 * (int64_t)E, smem + (at & ~15u), at & 15u, (uint32_t)nl * E, tx, 32);
+    constexpr int N = G::kPerThread;
+    T v[N];
+    auto load = [&](int j) {
+      const int nl = elems_of(j);
+      const uint8_t* col = tcol + (int64_t)j * TL * tsL;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const int l = (int)ty + k * NW;
+        v[k] = ((int)tx < nc && l < nl) ? __ldg(reinterpret_cast<const T*>(col + l * tsL)) : T(0);
+      }
+    };
+    load(0);
+    for (int j = 0; j < nsub; ++j) {
+      const int nl = elems_of(j);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const int l = (int)ty + k * NW;
+        if ((int)tx < nc && l < nl) *reinterpret_cast<T*>(smem + tx * ROW + l * E) = v[k];
+      }
+      __syncthreads();
+      if (j + 1 < nsub) load(j + 1);
+      uint8_t* irow = ibase + c0 * isC + (lfirst + (int64_t)j * TL) * E;
+      for (int r = (int)ty; r < nc; r += NW) {
+        const uint32_t at = (uint32_t)r * ROW;
+        mlf::drain_slot(irow + r * isC, smem + (at & ~15u), at & 15u, (uint32_t)nl * E, tx, 32);
+      }
+      __syncthreads();
     }
   } else {
-    for (int r = (int)ty; r < nc; r += (int)nwarp)
-      load_row_to_smem(smem + (uint32_t)r * ROW, ibase + (c0 + r) * isC + l0 * (int64_t)E, (uint32_t)nl * E, tx);
-    __syncthreads();
-    if ((int)tx < nc)
-      for (int l = (int)ty; l < nl; l += (int)nwarp)
-        *reinterpret_cast<T*>(tbase + (c0 + tx) * (int64_t)E + (l0 + l) * tsL) =
-            *reinterpret_cast<const T*>(smem + tx * ROW + l * E);
+    constexpr int N = G::kPasses;
+    uint32_t lo[N], hi[N];
+    const uint32_t w = tid % G::kWordsPerRow, rsub = tid / G::kWordsPerRow;
+    auto load = [&](int j) {
+      const uint32_t nwords = ((uint32_t)elems_of(j) * E) >> 2;
+      const uint8_t* irow = ibase + c0 * isC + (lfirst + (int64_t)j * TL) * E;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const uint32_t r = rsub + (uint32_t)k * G::kRowsPerPass;
+        ld_word_pair(irow + r * isC, w, r < (uint32_t)nc && w < nwords, &lo[k], &hi[k]);
+      }
+    };
+    load(0);
+    for (int j = 0; j < nsub; ++j) {
+      const int nl = elems_of(j);
+      const uint32_t row_len = (uint32_t)nl * E, nwords = row_len >> 2;
+      const uint8_t* irow = ibase + c0 * isC + (lfirst + (int64_t)j * TL) * E;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const uint32_t r = rsub + (uint32_t)k * G::kRowsPerPass;
+        if (r < (uint32_t)nc && w < nwords)
+          *reinterpret_cast<uint32_t*>(smem + r * ROW + w * 4u) = join_word_pair(irow + r * isC, lo[k], hi[k]);
+      }
+      const uint32_t tail = row_len & 3u;  // bytes after the last whole word of each row
+      if (tail != 0 && tid < (unsigned)nc * tail) {
+        const uint32_t r = tid / tail, b = (nwords << 2) + tid % tail;
+        smem[r * ROW + b] = irow[r * isC + b];
+      }
+      __syncthreads();
+      if (j + 1 < nsub) load(j + 1);
+      uint8_t* col = tcol + (int64_t)j * TL * tsL;
+#pragma unroll
+      for (int k = 0; k < G::kPerThread; ++k) {
+        const int l = (int)ty + k * NW;
+        if ((int)tx < nc && l < nl) *reinterpret_cast<T*>(col + l * tsL) = *reinterpret_cast<const T*>(smem + tx * ROW + l * E);
+      }
+      __syncthreads();
+    }
   }
-  __syncthreads();
 }
 
 template <typename T, int DIR>
@@ -639,6 +814,21 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg*
       // mappings); if it is not, only the tile edges move, never the bytes
       g.b = (uint32_t)((direction == MLF_PACK ? d.image_off : d.tensor_ptr) & 127u);
       ntile = (g.b + g.a + kTileBytes - 1) / kTileBytes;
+    } else if (inner_contig && c.ndim >= 2 && (uint64_t)c.shape[last] * esize < trans_row_bytes(esize) &&
+               (uint64_t)c.is[last - 1] == (uint64_t)c.shape[last] * esize) {
+      // short rows that lie back to back in the image: staged like narrow TRANSPOSE rows, walked in row order
+      g.kind = kTranspose;
+      g.c = (uint32_t)(last - 1);
+      g.reserved = 1;
+      const uint64_t row_bytes = (uint64_t)c.shape[last] * esize;
+      g.d = (uint32_t)std::max<uint64_t>(1, (uint64_t)trans_narrow_bytes(esize) / row_bytes);
+      const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
+      g.a = ((uint64_t)c.shape[last - 1] + rows_per_tile - 1) / rows_per_tile;
+      g.b = 1;
+      uint64_t batch = 1;
+      for (int k = 0; k < last - 1; ++k) batch *= (uint64_t)c.shape[k];
+      ntile = batch * g.a;
+      if (g.a > 0xffffffffull) return mlf::fail(MLF_ERR_TOO_LARGE, where + ": box too large");
     } else if (inner_contig) {
       g.kind = kRows;
       g.a = (uint64_t)c.shape[last] * esize;
@@ -649,7 +839,7 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg*
         g.c = (uint32_t)((g.a + kTileBytes - 1) / kTileBytes);
         ntile = nrows * g.c;
       } else {
-        g.b = (uint32_t)std::max<uint64_t>(1, kTileBytes / g.a);
+        g.b = (uint32_t)std::min<uint64_t>(kRowsPerTileMax, std::max<uint64_t>(1, kTileBytes / g.a));
         ntile = (nrows + g.b - 1) / g.b;
       }
     } else {
@@ -660,17 +850,19 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg*
       if (cdim >= 0) {
         g.kind = kTranspose;
         g.c = (uint32_t)cdim;
-        const uint64_t per_row = (uint64_t)kTransRowBytes / esize;
+        const uint64_t row_cap = trans_row_bytes(esize);
+        const uint64_t per_row = row_cap / esize;
         const uint64_t row_bytes = (uint64_t)c.shape[last] * esize;
         uint64_t tc, tl;
-        if (row_bytes < (uint64_t)kTransRowBytes && (uint64_t)c.is[cdim] == row_bytes) {
-          // short image rows lying back to back: a tile is as many whole rows as fit the staging area
-          g.d = (uint32_t)std::max<uint64_t>(1, (uint64_t)kTransNarrowBytes / row_bytes);
-          tc = ((uint64_t)c.shape[cdim] + g.d - 1) / g.d;
+        if (row_bytes < row_cap && (uint64_t)c.is[cdim] == row_bytes) {
+          // short image rows lying back to back: a sub-tile is as many whole rows as fit the staging area
+          g.d = (uint32_t)std::max<uint64_t>(1, (uint64_t)trans_narrow_bytes(esize) / row_bytes);
+          const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
+          tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
         } else {
           tc = ((uint64_t)c.shape[cdim] + kTransCols - 1) / kTransCols;
-          tl = ((uint64_t)c.shape[last] + per_row - 1) / per_row;
+          tl = ((uint64_t)c.shape[last] + per_row * kTransSub - 1) / (per_row * kTransSub);
         }
         g.b = (uint32_t)tl;
         g.a = tc * tl;

@@ -222,6 +222,82 @@ def test_large_transposed_and_row_sliced_sources(esize, dtype, engine, tmp_path)
         assert data == want, (esize, prefix)
 
 
+def _views_for_regimes(dtype, g):
+    """Views that land in every staged regime of the plan kernel: narrow and wide transposes, with
+    and without batch dimensions, ragged in both directions, and short rows cut out of wider ones."""
+
+    def rnd(*shape):
+        if dtype == torch.complex128:
+            return torch.view_as_complex(torch.randn(*shape, 2, generator=g, dtype=torch.float64)).cuda()
+        return torch.randint(0, 120, shape, generator=g, dtype=torch.int64).to(dtype).cuda()
+
+    out = []
+    for rows in (1, 3, 17, 64, 100, 127, 128, 129, 255):  # image row length of x.t(), in elements
+        out.append(rnd(rows, 2311).t())
+    out.append(rnd(64, 33000).t())  # more than four sub-tiles of narrow rows per tile
+    out.append(rnd(300, 1000).t())
+    out.append(rnd(1029, 515).t())  # wide rows, several sub-tiles along the row, ragged edges
+    out.append(rnd(3, 65, 130).transpose(1, 2))
+    out.append(rnd(2, 3, 40, 50).transpose(-1, -2))
+    out.append(rnd(5, 70, 11).permute(2, 0, 1))
+    out.append(rnd(6, 9, 200).permute(1, 2, 0))
+    wide = rnd(700, 300)
+    for cols in (1, 3, 16, 64, 100, 127):  # short rows, back to back in the image only
+        out.append(wide[:, 5 : 5 + cols])
+    out.append(rnd(4, 600, 40)[:, :, 5:30])
+    out.append(wide[::2, 7:90])
+    return out
+
+
+@pytest.mark.parametrize(
+    "dtype", [torch.uint8, torch.int16, torch.int32, torch.int64, torch.complex128], ids=lambda d: str(d).split(".")[-1]
+)
+def test_every_staged_regime_packs_and_unpacks_bit_exactly(dtype):
+    """Plans through the C ABI, both directions, image offsets of every residue class mod 16:
+    the packed bytes equal the oracle's C-order payload, the unpacked views equal the sources and
+    nothing outside a view or a payload is written."""
+    from ml_flashpoint import _native
+    from ml_flashpoint.core.gpu_engine import _Plan, c_strides, fill_desc
+
+    g = torch.Generator().manual_seed(11)
+    views = _views_for_regimes(dtype, g)
+    n = len(views)
+    descs = (_native.CopyDesc * n)()
+    offsets, at = [], 5
+    for i, v in enumerate(views):
+        offsets.append(at)
+        at += v.numel() * v.element_size() + 16 + (i % 16)  # gaps walk through all residues
+    image = torch.full((at + 64,), 0xA5, dtype=torch.uint8, device="cuda")
+    for i, v in enumerate(views):
+        fill_desc(descs[i], v.data_ptr(), offsets[i], v.element_size(), v.shape, v.stride(), c_strides(v.shape))
+    plan = _Plan(descs, n, _native.MLF_PACK)
+    plan.launch(image.data_ptr(), image.numel(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    plan.status()
+    got = image.cpu().numpy().tobytes()
+    expect = bytearray(b"\xa5" * image.numel())
+    for v, o in zip(views, offsets):
+        payload = oracle.tensor_payload(v.cpu())
+        expect[o : o + len(payload)] = payload
+    assert got == bytes(expect)
+
+    targets, bases = [], []
+    for v in views:
+        base = torch.zeros_like(v._base)
+        bases.append(base)
+        targets.append(base.as_strided(v.shape, v.stride(), v.storage_offset()))
+    for i, t in enumerate(targets):
+        fill_desc(descs[i], t.data_ptr(), offsets[i], t.element_size(), t.shape, t.stride(), c_strides(t.shape))
+    plan = _Plan(descs, n, _native.MLF_UNPACK)
+    plan.launch(image.data_ptr(), image.numel(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    plan.status()
+    for v, t, base in zip(views, targets, bases):
+        want = torch.zeros_like(v._base)
+        want.as_strided(v.shape, v.stride(), v.storage_offset()).copy_(v)
+        assert torch.equal(torch.view_as_real(base) if base.is_complex() else base, torch.view_as_real(want) if want.is_complex() else want)
+
+
 def test_overlapped_save_reads_sources_before_safe_to_mutate(shm_path, golden_dir, engine):
     """After ``wait_safe_to_mutate`` the sources may be overwritten: the object still holds the old values."""
     from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
