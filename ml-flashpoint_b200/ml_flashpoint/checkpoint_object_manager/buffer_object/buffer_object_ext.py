@@ -67,7 +67,8 @@ class BufferObject:
 
     def __buffer__(self, flags: int) -> memoryview:
         if self.closed:
-            raise RuntimeError("Cannot create buffer view on a closed BufferObject")
+            message = "Cannot create buffer view on a closed BufferObject"
+            raise BufferError(message) from RuntimeError(message)
         raw = (ctypes.c_ubyte * self.get_capacity()).from_address(self.get_data_ptr())
         view = memoryview(raw).cast("B")
         return view.toreadonly() if self.is_readonly else view

@@ -320,7 +320,7 @@ class TransferService:
         from ml_flashpoint.core import gpu_engine
 
         if data_size <= 0 or not data_ptr:
-            raise ValueError("async_put needs a non-empty source")
+            raise RuntimeError("Empty buffer or null data_ptr: async_put needs a non-empty source")
         lib = _native.lib()
         if self._cuda:
             _native.check(lib.mlf_set_device(self._device))
@@ -386,7 +386,7 @@ class TransferService:
             _send_msg(sock, {"op": "get", "obj": remote_object_id, "dest_obj": local_object_id, "reply_to": self.address, "task": task_id, "src_rank": self._rank})
             reply = _recv_msg(sock)
             if not reply.get("ok"):
-                raise RuntimeError(f"peer could not serve '{remote_object_id}': {reply.get('error')}")
+                raise RuntimeError(f"Received error message from peer for '{remote_object_id}': {reply.get('error')}")
 
     # ------------------------------------------------------------------ receiver side
     def _accept_loop(self) -> None:

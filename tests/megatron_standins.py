@@ -5,8 +5,10 @@ The stand-ins implement the contract the adapter relies on, with identity conver
 "sharded state dict" here is already a flat DCP state dict.
 """
 
+import dataclasses
 import sys
 import types
+from typing import Any, Optional, Tuple
 
 import torch
 from torch.distributed.checkpoint.default_planner import DefaultLoadPlanner, DefaultSavePlanner
@@ -50,25 +52,63 @@ class MCoreLoadPlanner(DefaultLoadPlanner):
     pass
 
 
+@dataclasses.dataclass
 class ShardedTensor:
-    def __init__(self, key, data):
-        self.key, self.data = key, data
+    """Field-compatible stand-in for megatron-core's sharded tensor record."""
+
+    key: str
+    data: Optional[torch.Tensor] = dataclasses.field(default=None, repr=False)
+    dtype: Optional[torch.dtype] = None
+    local_shape: Tuple[int, ...] = ()
+    global_shape: Tuple[int, ...] = ()
+    global_offset: Tuple[int, ...] = ()
+    axis_fragmentations: Optional[Tuple[int, ...]] = None
+    replica_id: Any = 0
+    prepend_axis_num: int = 0
+    allow_shape_mismatch: bool = False
+    flattened_range: Optional[slice] = None
 
     @classmethod
-    def from_rank_offsets(cls, key, data, *offsets):
-        return cls(key, data)
+    def from_rank_offsets(cls, key, data, *rank_offsets, replica_id=0, prepend_axis_num=0, flattened_range=None, **init_kwargs):
+        shape = tuple(data.shape)
+        global_shape, global_offset, fragmentations = list(shape), [0] * len(shape), [1] * len(shape)
+        for axis, rank_offset, fragmentation in rank_offsets:
+            global_shape[axis] = shape[axis] * fragmentation
+            global_offset[axis] = shape[axis] * rank_offset
+            fragmentations[axis] = fragmentation
+        return cls(
+            key, data, data.dtype, shape, tuple(global_shape), tuple(global_offset), tuple(fragmentations),
+            replica_id, prepend_axis_num, flattened_range=flattened_range, **init_kwargs,
+        )
 
     def without_data(self):
-        return ShardedTensor(self.key, None)
+        return dataclasses.replace(self, data=None)
 
 
+@dataclasses.dataclass
 class ShardedObject:
-    def __init__(self, key):
-        self.unique_key = key
+    """Field-compatible stand-in for megatron-core's sharded non-tensor record."""
+
+    key: str
+    data: Any = None
+    global_shape: Tuple[int, ...] = (1,)
+    global_offset: Tuple[int, ...] = (0,)
+    replica_id: Any = 0
+
+    @property
+    def unique_key(self):
+        return f"{self.key}/shard_{'.'.join(map(str, self.global_offset))}_{'.'.join(map(str, self.global_shape))}"
 
     @classmethod
-    def empty_from_unique_key(cls, key):
-        return cls(key)
+    def empty_from_unique_key(cls, unique_key, replica_id=0):
+        key, sep, shard = unique_key.rpartition("/")
+        if not sep or not shard.startswith("shard_"):
+            raise ValueError(f"'{unique_key}' is not the unique key of a sharded object")
+        offset, shape = shard[len("shard_"):].split("_")
+        return cls(key, None, tuple(map(int, shape.split("."))), tuple(map(int, offset.split("."))), replica_id)
+
+    def without_data(self):
+        return dataclasses.replace(self, data=None)
 
 
 class AsyncCallsQueue:
@@ -140,8 +180,19 @@ def install_nemo():
         pass
 
     class AsyncFinalizableCheckpointIO(CheckpointIO):
+        """Wrapper that forwards to the wrapped checkpoint IO, as NeMo's does."""
+
         def __init__(self, checkpoint_io):
             self.checkpoint_io = checkpoint_io
+
+        def save_checkpoint(self, checkpoint, path, storage_options=None):
+            return self.checkpoint_io.save_checkpoint(checkpoint, path, storage_options)
+
+        def load_checkpoint(self, path, *args, **kwargs):
+            return self.checkpoint_io.load_checkpoint(path, *args, **kwargs)
+
+        def remove_checkpoint(self, path):
+            return self.checkpoint_io.remove_checkpoint(path)
 
         def teardown(self):
             self.torn_down = True
@@ -173,6 +224,13 @@ def install_nemo():
             self.barriers.append(name)
 
     class Trainer:
+        # class-level names so that a mock built with this class as its spec has them
+        strategy = None
+        callbacks = ()
+        global_rank = local_rank = node_rank = global_step = current_epoch = 0
+        world_size = num_nodes = num_devices = 1
+        model = lightning_module = optimizers = None
+
         def __init__(self, strategy, callbacks=(), global_rank=0, local_rank=0):
             self.strategy, self.callbacks = strategy, list(callbacks)
             self.global_rank, self.local_rank, self.global_step = global_rank, local_rank, 0
@@ -181,9 +239,20 @@ def install_nemo():
         def save_checkpoint(self, path, storage_options=None):
             self.saved.append((path, storage_options))
 
+    @dataclasses.dataclass
+    class RestoreConfig:
+        path: str
+        load_model_state: bool = True
+        load_optim_state: bool = False
+        load_artifacts: bool = True
+
     @dataclasses.dataclass(kw_only=True)
     class AutoResume:
+        restore_config: Optional[RestoreConfig] = None
+        resume_from_directory: Optional[str] = None
+        resume_from_path: Optional[str] = None
         resume_if_exists: bool = False
+        resume_past_end: bool = False
         resume_ignore_no_checkpoint: bool = False
         fallback_path: Optional[Path] = None
 
@@ -225,7 +294,9 @@ def install_nemo():
     module("nemo.lightning.io.pl", MegatronCheckpointIO=MegatronCheckpointIO, TrainerContext=TrainerContext, _fix_tensors_device=lambda sd: None)
     module("nemo.lightning.pytorch")
     module("nemo.lightning.pytorch.trainer", Trainer=Trainer)
-    module("nemo.lightning.pytorch.strategies", MegatronStrategy=MegatronStrategy)
+    strategies = module("nemo.lightning.pytorch.strategies", MegatronStrategy=MegatronStrategy, FSDPStrategy=type("FSDPStrategy", (), {}))
+    strategies.__path__ = []  # a package: it has the submodule below
+    strategies.utils = module("nemo.lightning.pytorch.strategies.utils", RestoreConfig=RestoreConfig)
     sys.modules["megatron.core.dist_checkpointing.strategies.async_utils"].AsyncCallsQueue = AsyncCallsQueue
     sys.modules["megatron.core.dist_checkpointing.strategies.common"].TorchCommonLoadStrategy = type("TorchCommonLoadStrategy", (), {})
     sys.modules["megatron.core.dist_checkpointing"].load = _dist_load

@@ -7,7 +7,7 @@ provides the small part of it they use, on top of ``unittest.mock``.
 import sys, types, unittest.mock as um, pytest
 pm = types.ModuleType("pytest_mock"); 
 class MockerFixture:
-    def __init__(self): self._patches=[]; self.patch=self._Patch(self); self.MagicMock=um.MagicMock; self.Mock=um.Mock; self.ANY=um.ANY; self.call=um.call; self.mock_open=um.mock_open; self.PropertyMock=um.PropertyMock; self.AsyncMock=um.AsyncMock; self.sentinel=um.sentinel; self.DEFAULT=um.DEFAULT
+    def __init__(self): self._patches=[]; self.patch=self._Patch(self); self.MagicMock=um.MagicMock; self.Mock=um.Mock; self.ANY=um.ANY; self.call=um.call; self.mock_open=um.mock_open; self.PropertyMock=um.PropertyMock; self.AsyncMock=um.AsyncMock; self.sentinel=um.sentinel; self.DEFAULT=um.DEFAULT; self.create_autospec=um.create_autospec; self.NonCallableMagicMock=um.NonCallableMagicMock; self.seal=um.seal
     class _Patch:
         def __init__(self, outer): self.o=outer
         def __call__(self, *a, **k): p=um.patch(*a, **k); m=p.start(); self.o._patches.append(p); return m
@@ -15,7 +15,11 @@ class MockerFixture:
         def dict(self, *a, **k): p=um.patch.dict(*a, **k); m=p.start(); self.o._patches.append(p); return m
         def multiple(self, *a, **k): p=um.patch.multiple(*a, **k); m=p.start(); self.o._patches.append(p); return m
     def spy(self, obj, name):
-        orig=getattr(obj,name); m=um.MagicMock(side_effect=orig); p=um.patch.object(obj,name,m); p.start(); self._patches.append(p); return m
+        import inspect
+        orig=getattr(obj,name); autospec=inspect.ismethod(orig) or inspect.isfunction(orig)
+        def wrapper(*a, **k):
+            r=orig(*a, **k); spy_obj.spy_return=r; return r
+        p=um.patch.object(obj,name,side_effect=wrapper,autospec=autospec); spy_obj=p.start(); self._patches.append(p); return spy_obj
     def stub(self, name=None): return um.MagicMock(name=name)
     def stopall(self):
         for p in reversed(self._patches):
@@ -27,3 +31,13 @@ pm.MockerFixture=MockerFixture; sys.modules["pytest_mock"]=pm
 @pytest.fixture
 def mocker():
     m=MockerFixture(); yield m; m.stopall()
+
+
+import os
+
+if os.environ.get("MLF_REFSUITE_STANDINS") == "1":
+    # adapter test files import megatron / nemo / lightning at module level; none is installed here
+    import megatron_standins
+
+    megatron_standins.install()
+    megatron_standins.install_nemo()
