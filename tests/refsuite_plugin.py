@@ -41,3 +41,13 @@ if os.environ.get("MLF_REFSUITE_STANDINS") == "1":
 
     megatron_standins.install()
     megatron_standins.install_nemo()
+
+if os.environ.get("MLF_REFSUITE_HOST_ENGINE") == "1":
+    # The saver's host logic (bucketing, naming, offsets, results, error paths) with the byte moves
+    # done by the numpy test double instead of the CUDA engine; for boxes without a GPU.
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import helpers
+    from ml_flashpoint.core import gpu_engine
+
+    gpu_engine.set_default_engine(helpers.NumpyCopyEngine())

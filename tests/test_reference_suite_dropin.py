@@ -61,7 +61,22 @@ ADAPTER_SUITES = [
 ]
 
 
-def _launch(entry, workdir, standins):
+# The reference's saver tests build savers over CPU tensors and check names, offsets, results, markers,
+# threading and error paths. Without a GPU the byte moves are done by the numpy test double of
+# tests/helpers.py instead of the CUDA engine (MLF_REFSUITE_HOST_ENGINE, see refsuite_plugin.py).
+# Deselected: tests of the reference's host copy internals, which have no counterpart here: staging
+# to the CPU (TestStageData), the private per-tensor memcpy (_save_tensor_optimized, _clone_if_needed)
+# and the torch intra-op thread count that write_data sets for that memcpy.
+HOST_ENGINE_SUITES = [
+    ("core/test_checkpoint_saver.py", 107, [
+        "test_write_data_resets_num_threads", "test_stage_data_defaults_to_non_blocking", "test_stage_data_moves_all_to_cpu_mocked",
+        "test_stage_data_cuda_synchronization[True-True]", "test_save_tensor_optimized_writes_correct_header_and_data",
+        "test_prepare_write_data_clone_if_needed_logic",
+    ]),
+]
+
+
+def _launch(entry, workdir, standins, host_engine=False):
     suite = entry[0]
     deselected = entry[2] if len(entry) > 2 else []
     env = dict(os.environ)
@@ -69,6 +84,8 @@ def _launch(entry, workdir, standins):
     env.pop("MLFLASHPOINT_LOG_LEVEL", None)
     if standins:
         env["MLF_REFSUITE_STANDINS"] = "1"
+    if host_engine:
+        env["MLF_REFSUITE_HOST_ENGINE"] = "1"
     cmd = [
         sys.executable, "-m", "pytest", os.path.join(REFERENCE_ROOT, "tests", suite),
         "-q", "-p", "refsuite_plugin", "-p", "no:cacheprovider", "--rootdir", workdir, "-c", os.devnull,
@@ -87,6 +104,8 @@ def suite_runs(tmp_path_factory):
         for entry in entries:
             workdir = str(tmp_path_factory.mktemp("refsuite"))
             runs[entry[0]] = pool.submit(_launch, entry, workdir, standins)
+    for entry in HOST_ENGINE_SUITES:
+        runs[entry[0]] = pool.submit(_launch, entry, str(tmp_path_factory.mktemp("refsuite")), False, True)
     yield runs
     pool.shutdown(wait=False, cancel_futures=True)
 
@@ -112,4 +131,10 @@ def test_reference_test_file_passes_against_this_package(entry, suite_runs):
 @_needs_reference
 @pytest.mark.parametrize("entry", ADAPTER_SUITES, ids=[e[0] for e in ADAPTER_SUITES])
 def test_reference_adapter_test_file_passes_with_standin_frameworks(entry, suite_runs):
+    _check(entry, suite_runs)
+
+
+@_needs_reference
+@pytest.mark.parametrize("entry", HOST_ENGINE_SUITES, ids=[e[0] for e in HOST_ENGINE_SUITES])
+def test_reference_saver_test_file_passes_with_host_engine_double(entry, suite_runs):
     _check(entry, suite_runs)
