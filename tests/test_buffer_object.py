@@ -29,8 +29,9 @@ def test_create_maps_a_zero_filled_file_and_creates_parents(tmp_path):
     buf.close()  # idempotent
     with pytest.raises(RuntimeError):
         buf.get_data_ptr()
-    with pytest.raises(RuntimeError):
+    with pytest.raises(BufferError) as closed_view:  # as the reference's binding: BufferError caused by a RuntimeError
         memoryview(buf)
+    assert isinstance(closed_view.value.__cause__, RuntimeError)
 
 
 def test_create_refuses_existing_file_unless_overwrite(tmp_path):
