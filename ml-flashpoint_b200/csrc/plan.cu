@@ -82,6 +82,9 @@ __device__ __forceinline__ void store_elem(uint8_t* p, T v, bool aligned) {
 //                 (contiguous in the image); the sub-tiles of a tile follow one another along L
 //   narrow rows : image rows shorter than kRowBytes lying back to back; a sub-tile is as many whole
 //                 rows as fit kNarrowBytes, i.e. ONE contiguous run of the image
+#ifndef MLF_TRANSPOSE_ATTR
+#define MLF_TRANSPOSE_ATTR __noinline__
+#endif
 constexpr int kTransSub = 4;
 template <int E>
 struct TransGeom {
@@ -140,7 +143,7 @@ __device__ __forceinline__ void drain_swizzled(uint8_t* __restrict__ dst, const 
 
 // Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
 template <typename T, int DIR>
-__device__ __noinline__ void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
+__device__ MLF_TRANSPOSE_ATTR void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
   constexpr int E = (int)sizeof(T);
   using G = TransGeom<E>;
   constexpr int TL = G::kRowElems;
@@ -479,6 +482,31 @@ __global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restric
   }
 }
 
+// A tile that is not one linear run: short rows, transposed sub-tiles, or single elements.
+#ifndef MLF_STAGED_ATTR
+#define MLF_STAGED_ATTR
+#endif
+template <int DIR>
+__device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* tsmem) {
+  if (g.kind == kRows) {
+    rows_tile<DIR>(g, local, image);
+  } else if (g.kind == kTranspose) {
+    switch (g.esize) {
+      case 1: transpose_tile<uint8_t, DIR>(g, local, image, tsmem); break;
+      case 2: transpose_tile<uint16_t, DIR>(g, local, image, tsmem); break;
+      case 4: transpose_tile<uint32_t, DIR>(g, local, image, tsmem); break;
+      default: transpose_tile<uint64_t, DIR>(g, local, image, tsmem); break;
+    }
+  } else {
+    switch (g.esize) {
+      case 1: generic_tile<uint8_t, DIR>(g, local, image); break;
+      case 2: generic_tile<uint16_t, DIR>(g, local, image); break;
+      case 4: generic_tile<uint32_t, DIR>(g, local, image); break;
+      default: generic_tile<uint64_t, DIR>(g, local, image); break;
+    }
+  }
+}
+
 // ---- bulk-copy staged variant -------------------------------------------------------------
 // Same tiles, same bytes. Linear tiles (FLAT, and chunks of long ROWS) stream through the
 // shared-memory ring of bulk_pipeline.cuh; the other kinds run exactly as in mlf_plan_kernel.
@@ -538,15 +566,15 @@ __device__ __forceinline__ uint32_t find_segment(const uint32_t* __restrict__ ti
   return lo;
 }
 
-template <int DIR>
+// STAGED = false is the instance for plans made of linear tiles only (every contiguous state dict):
+// it carries none of the staged-tile code, which keeps the streaming loop at its leanest.
+template <int DIR, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* __restrict__ segs,
                                                                  const uint32_t* __restrict__ tile_begin, uint32_t nseg,
                                                                  uint32_t ntiles, uint8_t* __restrict__ image,
                                                                  int32_t* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
   __shared__ __align__(8) uint64_t full[mlf::kStages];
-  __shared__ __align__(16) uint8_t tsmem[kTransSmemBytes];
-  __shared__ Seg g;
   __shared__ int abort_flag;
   const unsigned tid = threadIdx.x;
 
@@ -618,30 +646,18 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* _
       }
       continue;
     }
-    if (sg != cached) {
-      __syncthreads();
-      const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + sg);
-      uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
-      for (uint32_t w = tid; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
-      __syncthreads();
-      cached = sg;
-    }
-    if (g.kind == kRows) {
-      rows_tile<DIR>(g, local, image);
-    } else if (g.kind == kTranspose) {
-      switch (g.esize) {
-        case 1: transpose_tile<uint8_t, DIR>(g, local, image, tsmem); break;
-        case 2: transpose_tile<uint16_t, DIR>(g, local, image, tsmem); break;
-        case 4: transpose_tile<uint32_t, DIR>(g, local, image, tsmem); break;
-        default: transpose_tile<uint64_t, DIR>(g, local, image, tsmem); break;
+    if constexpr (STAGED) {
+      __shared__ __align__(16) uint8_t tsmem[kTransSmemBytes];
+      __shared__ Seg g;
+      if (sg != cached) {
+        __syncthreads();
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + sg);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
+        for (uint32_t w = tid; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
+        __syncthreads();
+        cached = sg;
       }
-    } else {
-      switch (g.esize) {
-        case 1: generic_tile<uint8_t, DIR>(g, local, image); break;
-        case 2: generic_tile<uint16_t, DIR>(g, local, image); break;
-        case 4: generic_tile<uint32_t, DIR>(g, local, image); break;
-        default: generic_tile<uint64_t, DIR>(g, local, image); break;
-      }
+      staged_tile<DIR>(g, local, image, tsmem);
     }
   }
   if (aborted && tid == 0) {
@@ -891,6 +907,7 @@ struct mlf_plan {
   uint32_t ntiles = 0;
   uint64_t extent = 0;
   uint64_t payload = 0;
+  bool staged = false;  // some tile is not a linear run (short rows, transposed, generic)
   Seg* d_segs = nullptr;
   uint32_t* d_tile_begin = nullptr;
   int32_t* d_status = nullptr;
@@ -910,6 +927,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   segs.reserve(n);
   tile_begin.reserve(n + 1);
   uint64_t tiles = 0, extent = 0, payload = 0;
+  bool staged = false;
 
   for (uint64_t i = 0; i < n; ++i) {
     Seg g;
@@ -923,10 +941,12 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
     tile_begin.push_back((uint32_t)tiles);
     segs.push_back(g);
     tiles += ntile;
+    if (!(g.kind == kFlat || (g.kind == kRows && g.b == 0))) staged = true;
   }
   tile_begin.push_back((uint32_t)tiles);
 
   mlf_plan* p = new mlf_plan();
+  p->staged = staged;
   p->direction = direction;
   p->nseg = (uint32_t)segs.size();
   p->ntiles = (uint32_t)tiles;
@@ -974,23 +994,23 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t* image = static_cast<uint8_t*>(image_base);
   if (use_bulk_kernel()) {
-    auto pack = mlf_plan_kernel_bulk<MLF_PACK>;
-    auto unpack = mlf_plan_kernel_bulk<MLF_UNPACK>;
+    using BulkKernel = void (*)(const Seg*, const uint32_t*, uint32_t, uint32_t, uint8_t*, int32_t*);
+    static const BulkKernel kernels[2][2] = {
+        {mlf_plan_kernel_bulk<MLF_PACK, false>, mlf_plan_kernel_bulk<MLF_PACK, true>},
+        {mlf_plan_kernel_bulk<MLF_UNPACK, false>, mlf_plan_kernel_bulk<MLF_UNPACK, true>},
+    };
     static std::once_flag opted_in;
     static cudaError_t opt_status = cudaSuccess;
     std::call_once(opted_in, [&]() {
-      opt_status = cudaFuncSetAttribute(pack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
-      if (opt_status == cudaSuccess)
-        opt_status = cudaFuncSetAttribute(unpack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
+      for (int d = 0; d < 2 && opt_status == cudaSuccess; ++d)
+        for (int v = 0; v < 2 && opt_status == cudaSuccess; ++v)
+          opt_status = cudaFuncSetAttribute(kernels[d][v], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
     });
     MLF_CUDA(opt_status);
-    int32_t rc = p->direction == MLF_PACK ? wave_grid(pack, max_ctas, p->ntiles, &grid, kBulkDynSmem)
-                                          : wave_grid(unpack, max_ctas, p->ntiles, &grid, kBulkDynSmem);
+    const BulkKernel kernel = kernels[p->direction == MLF_PACK ? 0 : 1][p->staged ? 1 : 0];
+    const int32_t rc = wave_grid(kernel, max_ctas, p->ntiles, &grid, kBulkDynSmem);
     if (rc != MLF_OK) return rc;
-    if (p->direction == MLF_PACK)
-      pack<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image, p->d_status);
-    else
-      unpack<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image, p->d_status);
+    kernel<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image, p->d_status);
   } else {
     int32_t rc = p->direction == MLF_PACK ? wave_grid(mlf_plan_kernel<MLF_PACK>, max_ctas, p->ntiles, &grid)
                                           : wave_grid(mlf_plan_kernel<MLF_UNPACK>, max_ctas, p->ntiles, &grid);
