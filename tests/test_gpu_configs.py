@@ -1,8 +1,9 @@
 """The benchmark's other configurations as parity cases on the GPU.
 
-Small variants are compared byte for byte with the CPU oracle; the full-size packing microbench
-(1 024 tensors, up to 8 GiB) is checked through size-independent properties: record arithmetic,
-bit-exact save -> restore round trip, and oracle bytes for a random sample of its tensors."""
+Small variants are compared byte for byte with the CPU oracle; the full-size ones (packing
+microbench: 1 024 tensors, up to 8 GiB; Mixtral expert-parallel rank: 11.3 GB; Llama-3-70B
+tensor-parallel rank: 17.6 GB) are checked through size-independent properties: record arithmetic,
+bit-exact save -> restore round trip, and oracle bytes for a sample of their items."""
 
 import os
 import random
@@ -127,6 +128,52 @@ def test_packing_microbench_full_size_properties(shm_path, engine):
             want = oracle.header_bytes(str(t.dtype).split(".")[-1], tuple(t.shape)) + oracle.tensor_payload(t.cpu())
             assert got == want, fqn
     # round trip
+    restored = _restore_all(com, engine, buckets, results, case)
+    for fqn, t in tensors.items():
+        assert torch.equal(restored[fqn], t), fqn
+    com.teardown_pool()
+
+
+@pytest.mark.parametrize("make", [
+    lambda: workloads.moe_expert_parallel_rank_full_size("cuda", rank=3),
+    lambda: workloads.tensor_parallel_rank_full_size("cuda", rank=5),
+], ids=["moe_ep_rank_11gb", "megatron_tp_rank_17gb"])
+def test_full_size_rank_objects_properties(make, shm_path, engine):
+    stat = os.statvfs(str(shm_path))
+    if stat.f_bavail * stat.f_frsize < (24 << 30) or torch.cuda.mem_get_info()[0] < (72 << 30):
+        pytest.skip("needs 24 GiB of tmpfs and 72 GiB of free device memory")
+    case = make()
+    tensors, blobs = case["tensors"], case["blobs"]
+    payload = sum(t.numel() * t.element_size() for t in tensors.values())
+    headers = sum(len(oracle.header_bytes(str(t.dtype).split(".")[-1], tuple(t.shape))) for t in tensors.values())
+    blob_bytes = sum(len(b) for b in blobs.values())
+    total = payload + headers + blob_bytes
+    assert payload > (10 << 30)
+    com, buckets, results = _save(case, shm_path, engine, pool_bytes=4096 + total)
+    path = str(buckets[0].object_id)
+    assert os.path.getsize(path) == 4096 + total
+    # records: tensors first in plan order, then the byte items, back to back
+    by_fqn = {r.index.fqn: r.storage_data for r in results}
+    pos = 0
+    for r in results:
+        assert r.storage_data.offset == pos
+        pos += r.storage_data.length
+    assert pos == total
+    assert [r.index.fqn for r in results[: len(tensors)]] == list(tensors)
+    rng = random.Random(9)
+    names = list(tensors)
+    strided = [n for n in names if not tensors[n].is_contiguous()]
+    sample = rng.sample(names, 6) + strided[:3] + [n for n in names if tensors[n].device.type == "cpu"]
+    with open(path, "rb") as f:
+        for fqn in sample:
+            t = tensors[fqn]
+            f.seek(4096 + by_fqn[fqn].offset)
+            got = f.read(by_fqn[fqn].length)
+            want = oracle.header_bytes(str(t.dtype).split(".")[-1], tuple(t.shape)) + oracle.tensor_payload(t.cpu())
+            assert got == want, fqn
+        for key, data in blobs.items():
+            f.seek(4096 + by_fqn[key].offset)
+            assert f.read(by_fqn[key].length) == data, key
     restored = _restore_all(com, engine, buckets, results, case)
     for fqn, t in tensors.items():
         assert torch.equal(restored[fqn], t), fqn

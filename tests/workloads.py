@@ -101,3 +101,50 @@ def tensor_parallel_rank(device, rank=0, tp=8, layers=2, d_model=512, d_ff=1792,
         tensors[p + "input_layernorm.weight"] = torch.ones(d_model, dtype=torch.bfloat16, device=device)
     tensors["output_layer.weight"] = shard(full(vocab, d_model), 0)
     return {"tensors": tensors, "blobs": {}, "bucket_count": 1}
+
+
+def tensor_parallel_rank_full_size(device, rank=0, tp=8, layers=80, d_model=8192, d_ff=28672, vocab=128256,
+                                   heads=64, kv_heads=8, seed=4):
+    """One tensor-parallel rank of a Llama-3-70B-shaped model in bf16 at full size (17.6 GB for
+    tp=8), drawn directly on the device. Column-wise shards are contiguous; the row-wise ones
+    (attention output, MLP down projection) are column slices of wider matrices, i.e. strided rows."""
+    g = torch.Generator(device=device).manual_seed(seed * 100 + rank)
+    tensors = {}
+
+    def draw(rows, cols):
+        return torch.randn((rows, cols), device=device, dtype=torch.bfloat16, generator=g) * 0.02
+
+    def row_sliced(rows, cols):
+        return draw(rows, 2 * cols)[:, cols // 2 : cols // 2 + cols]
+
+    qkv_rows = d_model + 2 * (d_model * kv_heads // heads)
+    tensors["embedding.word_embeddings.weight"] = draw(vocab // tp, d_model)
+    for layer in range(layers):
+        p = f"decoder.layers.{layer}."
+        tensors[p + "self_attention.linear_qkv.weight"] = draw(qkv_rows // tp, d_model)
+        tensors[p + "self_attention.linear_proj.weight"] = row_sliced(d_model, d_model // tp)
+        tensors[p + "mlp.linear_fc1.weight"] = draw(2 * d_ff // tp, d_model)
+        tensors[p + "mlp.linear_fc2.weight"] = row_sliced(d_model, d_ff // tp)
+        tensors[p + "input_layernorm.weight"] = torch.ones(d_model, dtype=torch.bfloat16, device=device)
+        tensors[p + "pre_mlp_layernorm.weight"] = torch.ones(d_model, dtype=torch.bfloat16, device=device)
+    tensors["decoder.final_layernorm.weight"] = torch.ones(d_model, dtype=torch.bfloat16, device=device)
+    tensors["output_layer.weight"] = draw(vocab // tp, d_model)
+    return {"tensors": tensors, "blobs": {}, "bucket_count": 1}
+
+
+def moe_expert_parallel_rank_full_size(device, rank=0, layers=32, d_model=4096, d_ff=14336, seed=3):
+    """The expert-parallel rank of ``moe_expert_parallel_rank`` at full size (one expert of
+    3 x 14336 x 4096 bf16 per layer, 11.3 GB), expert weights drawn directly on the device; the
+    host-resident scalars, RNG state bytes and the pickled configuration are the small generator's."""
+    small = moe_expert_parallel_rank(device, rank=rank, layers=1, d_model=64, d_ff=128, seed=seed)
+    g = torch.Generator(device=device).manual_seed(seed * 100 + rank)
+    tensors = {}
+    for layer in range(layers):
+        p = f"decoder.layers.{layer}.mlp.experts.local_experts.{rank}."
+        for name, shape in (("w1", (d_ff, d_model)), ("w3", (d_ff, d_model)), ("w2", (d_model, d_ff))):
+            tensors[p + name] = torch.randn(shape, device=device, dtype=torch.bfloat16, generator=g) * 0.02
+        tensors[f"decoder.layers.{layer}.router.weight"] = torch.randn((8, d_model), device=device, dtype=torch.bfloat16, generator=g) * 0.02
+    for name, t in small["tensors"].items():
+        if t.device.type == "cpu":
+            tensors[name] = t
+    return {"tensors": tensors, "blobs": small["blobs"], "bucket_count": 1}
