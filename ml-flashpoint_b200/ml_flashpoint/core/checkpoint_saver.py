@@ -190,12 +190,14 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
         self._initial_buffer_size_bytes = initial_buffer_size_bytes
         self._use_optimized_save = use_optimized_save
         self._copy_engine = copy_engine
+        self._layouts: dict = {}  # id(bucket) -> (bucket, layout) planned by _announce_save, consumed by _write_bucket
 
     # Worker processes get a saver without the replication manager and without CUDA state.
     def __getstate__(self):
         state = self.__dict__.copy()
         state.pop("_replication_manager", None)
         state["_copy_engine"] = None
+        state["_layouts"] = {}
         return state
 
     def __setstate__(self, state):
@@ -268,6 +270,7 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
         thread_count: int = 1,
     ) -> list[WriteResult]:
         thread_count = max(thread_count, 1)
+        self._announce_save(write_buckets)
         pending: queue.Queue = queue.Queue()
         for bucket in write_buckets:
             pending.put(bucket)
@@ -321,6 +324,7 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
         two completion points. Buffers are acquired here and closed by ``PendingSave.result``.
         """
         pending = PendingSave(self, replicate_after_write)
+        self._announce_save(write_buckets)
         for bucket in write_buckets:
             writer = self._chkpt_obj_manager.acquire_buffer(bucket.object_id, self._initial_buffer_size_bytes)
             try:
@@ -363,19 +367,39 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
             finally:
                 object_write_bucket_queue.task_done()
 
-    def _write_bucket(self, bucket: ObjectWriteBucket, writer, use_optimized_write: bool, wait: bool = True):
+    def _announce_save(self, write_buckets: list[ObjectWriteBucket]) -> None:
+        """Plans every bucket's layout once and tells the engine how much HBM the images of this save
+        take together, so that no bucket's pack kernel has to wait for another bucket's transfer."""
+        if not write_buckets:
+            return
+        total = 0
+        for bucket in write_buckets:
+            layout = self._plan_layout(bucket, self._use_optimized_save)
+            self._layouts[id(bucket)] = (bucket, layout)
+            total += layout.total_bytes
+        announce = getattr(self._engine(), "begin_save", None)
+        if announce is not None:
+            announce(total)
+
+    @staticmethod
+    def _plan_layout(bucket: ObjectWriteBucket, use_optimized_write: bool):
         if use_optimized_write:
-            writer.set_format_signature(CheckpointFormat.MLF_FORMAT)
-            layout = gpu_engine.plan_object_layout(bucket.tensor_data, bucket.bytesio_data, start_offset=0)
+            return gpu_engine.plan_object_layout(bucket.tensor_data, bucket.bytesio_data, start_offset=0)
+        # legacy format: every tensor is a torch.save stream; the streams travel as byte items
+        streams = []
+        for item, tensor in bucket.tensor_data:
+            sink = io.BytesIO()
+            torch.save(tensor, sink)
+            streams.append((item, sink))
+        return gpu_engine.plan_object_layout([], streams + list(bucket.bytesio_data), start_offset=0)
+
+    def _write_bucket(self, bucket: ObjectWriteBucket, writer, use_optimized_write: bool, wait: bool = True):
+        writer.set_format_signature(CheckpointFormat.MLF_FORMAT if use_optimized_write else CheckpointFormat.TORCH_SAVE)
+        planned = self._layouts.pop(id(bucket), None)
+        if planned is not None and planned[0] is bucket and use_optimized_write == self._use_optimized_save:
+            layout = planned[1]
         else:
-            # legacy format: every tensor is a torch.save stream; the streams travel as byte items
-            writer.set_format_signature(CheckpointFormat.TORCH_SAVE)
-            streams = []
-            for item, tensor in bucket.tensor_data:
-                sink = io.BytesIO()
-                torch.save(tensor, sink)
-                streams.append((item, sink))
-            layout = gpu_engine.plan_object_layout([], streams + list(bucket.bytesio_data), start_offset=0)
+            layout = self._plan_layout(bucket, use_optimized_write)
         start = writer.tell()
         if hasattr(writer, "ensure_total_size"):
             # pooled file: one remap to the exact final size instead of grow-then-trim

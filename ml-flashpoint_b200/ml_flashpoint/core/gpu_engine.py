@@ -216,6 +216,20 @@ class _CachedPack:
     plan: _Plan
     blob: _PinnedBlob
     keepalive: list  # device copies of CPU tensors referenced by the plan
+    last_kernel: Optional["torch.cuda.Event"] = None  # the last launch that read ``blob``
+
+
+@dataclasses.dataclass(eq=False)
+class _Image:
+    """One object image inside the engine's HBM arena."""
+
+    offset: int
+    nbytes: int
+    done: "torch.cuda.Event"  # fires when the transfer out of the region has finished
+    object_id: Optional[str]
+
+    def overlaps(self, offset: int, nbytes: int) -> bool:
+        return self.offset < offset + nbytes and offset < self.offset + self.nbytes
 
 
 class PackTicket:
@@ -275,12 +289,15 @@ class CudaCopyEngine:
         self._lock = threading.RLock()
         self._cache: "OrderedDict[tuple, _CachedPack]" = OrderedDict()
         self._cache_size = plan_cache_size
-        self._staging: Optional[torch.Tensor] = None
-        self._last_mutate: Optional[torch.cuda.Event] = None  # last kernel that read a pinned blob
-        self._last_done: Optional[torch.cuda.Event] = None  # last transfer that read the HBM image
+        # HBM arena holding the images of the objects being saved (and the image of a restore).
+        # Regions are handed out front to back within one save (``begin_save``), so the buckets of a
+        # multi-object save are packed back to back while earlier ones still drain to the host.
+        self._arena: Optional[torch.Tensor] = None
+        self._arena_goal = 0  # bytes the arena should hold: the largest save announced so far
+        self._cursor = 0
+        self._images: List[_Image] = []  # regions whose contents are still valid, oldest first
         self.last_ticket: Optional[PackTicket] = None  # most recent save, for timing queries
         self.last_unpack_ms: Optional[Tuple[float, float]] = None  # (host-to-HBM ms, kernel ms) of the last restore
-        self._resident: Optional[tuple] = None  # (object id, image tensor, nbytes, done event) of the last staged save
         with torch.cuda.device(self.device):
             self._bind()
             self.pack_stream = torch.cuda.Stream(device=self.device)
@@ -295,18 +312,60 @@ class CudaCopyEngine:
         obj = getattr(buffer_io, "buffer_obj", None)
         return bool(getattr(obj, "is_cuda_registered", False))
 
+    _ARENA_ALIGN = 256
+
+    def _ensure_arena(self, nbytes: int) -> None:
+        """Makes the arena at least ``nbytes`` (and the announced goal) large. Growing it waits for
+        every transfer that still reads the old one: the allocator knows nothing about those streams."""
+        want = max(nbytes, self._arena_goal, 1 << 20)
+        if self._arena is not None and self._arena.numel() >= want:
+            return
+        for image in self._images:
+            image.done.synchronize()
+        self._images = []
+        self._cursor = 0
+        self._arena = None
+        self._arena = torch.empty(want, dtype=torch.uint8, device=self.device)
+
+    def begin_save(self, total_bytes: int) -> None:
+        """Announces a save whose object images take ``total_bytes`` in all: the arena is sized for
+        the whole save and its objects are placed from the front, so none waits for another's transfer."""
+        with self._lock, torch.cuda.device(self.device):
+            self._arena_goal = max(self._arena_goal, int(total_bytes) + self._ARENA_ALIGN * 64)
+            self._cursor = 0
+
+    def _reserve_image(self, nbytes: int, stream: "torch.cuda.Stream") -> Tuple[torch.Tensor, int]:
+        """Region of ``nbytes`` for a new object image. Work queued on ``stream`` afterwards runs
+        after the transfers out of any older image the region overlaps; those images are forgotten."""
+        self._ensure_arena(nbytes)
+        if self._cursor + nbytes > self._arena.numel():
+            self._cursor = 0
+        offset = self._cursor
+        kept = []
+        for image in self._images:
+            if image.overlaps(offset, nbytes):
+                stream.wait_event(image.done)
+            else:
+                kept.append(image)
+        self._images = kept
+        self._cursor = (offset + nbytes + self._ARENA_ALIGN - 1) // self._ARENA_ALIGN * self._ARENA_ALIGN
+        return self._arena[offset : offset + nbytes], offset
+
     def staging(self, nbytes: int) -> torch.Tensor:
-        """HBM image buffer of at least ``nbytes`` (grown geometrically, reused across saves)."""
-        if self._staging is None or self._staging.numel() < nbytes:
-            if self._last_done is not None:
-                # a transfer on the copy stream may still be reading the buffer that is about to be
-                # returned to the allocator, which knows nothing about that stream
-                self._last_done.synchronize()
-            self._resident = None
-            self._staging = None
-            grown = max(nbytes, 1 << 20)
-            self._staging = torch.empty(grown, dtype=torch.uint8, device=self.device)
-        return self._staging
+        """The front of the arena for a restore's image; every resident object image is given up
+        (after the transfers out of them have finished)."""
+        self._ensure_arena(nbytes)
+        for image in self._images:
+            image.done.synchronize()
+        self._images = []
+        self._cursor = 0
+        return self._arena[:nbytes]
+
+    def drop_resident_images(self) -> None:
+        """Forgets the object images kept in HBM after their saves (they stay valid until reused)."""
+        with self._lock:
+            for image in self._images:
+                image.object_id = None
 
     @staticmethod
     def _tensor_key(t: torch.Tensor) -> tuple:
@@ -350,6 +409,9 @@ class CudaCopyEngine:
                     self._cache.popitem(last=False)
         else:
             self._cache.move_to_end(key)
+        if entry.last_kernel is not None:
+            # the previous launch of this plan may still be reading the pinned blob about to be refilled
+            entry.last_kernel.synchronize()
         entry.blob.fill(layout.host_chunks)
         return entry
 
@@ -365,33 +427,29 @@ class CudaCopyEngine:
         """
         with self._lock, torch.cuda.device(self.device):
             self._bind()
-            self._resident = None
-            if self._last_mutate is not None:
-                # the previous kernel may still be reading the pinned blob this save is about to refill
-                self._last_mutate.synchronize()
             entry = self._pack_entry(layout)
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
             self.pack_stream.wait_event(ready)
-            if self._last_done is not None:
-                # the HBM image is reused: the previous drain must have finished reading it
-                self.pack_stream.wait_event(self._last_done)
             start_event = torch.cuda.Event(enable_timing=True)
             mutate_event = torch.cuda.Event(enable_timing=True)
             done_event = torch.cuda.Event(enable_timing=True)
             total = layout.total_bytes
-            start_event.record(self.pack_stream)
             if total == 0:
+                start_event.record(self.pack_stream)
                 mutate_event.record(self.pack_stream)
                 done_event.record(self.pack_stream)
                 return PackTicket(self, entry, start_event, mutate_event, done_event, 0)
             if self.mode == "direct":
+                start_event.record(self.pack_stream)
                 base = buffer_io.device_address(start_pos)
                 entry.plan.launch(base, total, self.pack_stream.cuda_stream, self.host_ctas)
                 mutate_event.record(self.pack_stream)
                 done_event.record(self.pack_stream)
             else:
-                image = self.staging(total)
+                # the region may hold an older image: the kernel is ordered after the transfer out of it
+                image, offset = self._reserve_image(total, self.pack_stream)
+                start_event.record(self.pack_stream)
                 entry.plan.launch(image.data_ptr(), total, self.pack_stream.cuda_stream)
                 mutate_event.record(self.pack_stream)
                 if self._is_registered(buffer_io):
@@ -421,9 +479,9 @@ class CudaCopyEngine:
                         )
                     )
                     done_event.record(self.pack_stream)
-                if object_id is not None and start_pos == 0:
-                    self._resident = (str(object_id), image, total, done_event)
-            self._last_mutate, self._last_done = mutate_event, done_event
+                resident_id = str(object_id) if object_id is not None and start_pos == 0 else None
+                self._images.append(_Image(offset, total, done_event, resident_id))
+            entry.last_kernel = mutate_event
             self.last_ticket = PackTicket(self, entry, start_event, mutate_event, done_event, total)
             return self.last_ticket
 
@@ -431,14 +489,15 @@ class CudaCopyEngine:
         self.pack_async(layout, buffer_io, start_pos, object_id).wait()
 
     def resident_image(self, object_id: str, nbytes: int) -> Optional["_ResidentLease"]:
-        """Lease on the HBM image of ``object_id``'s data section, if the last staged save left one
-        of exactly ``nbytes``. While the lease is held no other save or restore can reuse the buffer."""
-        held = self._resident
-        if held is None or held[0] != str(object_id) or held[2] != nbytes:
-            return None
-        return _ResidentLease(self, held)
+        """Lease on the HBM image of ``object_id``'s data section, if a staged save left one of
+        exactly ``nbytes`` that has not been reused since. While the lease is held no save or restore
+        can reuse the arena."""
+        with self._lock:
+            for image in reversed(self._images):
+                if image.object_id == str(object_id) and image.nbytes == nbytes:
+                    return _ResidentLease(self, image)
+        return None
 
-    # ------------------------------------------------------------------ restore
     def unpack(self, reads: Sequence[Tuple[torch.Tensor, int, Sequence[int], Sequence[int]]], buffer_io) -> None:
         """Scatters stored tensors (or sub-blocks) from ``buffer_io`` into target tensors.
 
@@ -453,7 +512,6 @@ class CudaCopyEngine:
             return
         with self._lock, torch.cuda.device(self.device):
             self._bind()
-            self._resident = None
             lo = None
             hi = 0
             prepared = []
@@ -532,17 +590,18 @@ class CudaCopyEngine:
 class _ResidentLease:
     """Context manager yielding the device address of a resident object image (see ``resident_image``)."""
 
-    def __init__(self, engine: CudaCopyEngine, held: tuple):
+    def __init__(self, engine: CudaCopyEngine, image: _Image):
         self._engine = engine
-        self._held = held
+        self._image = image
 
     def __enter__(self) -> int:
-        self._engine._lock.acquire()
-        if self._engine._resident is not self._held:
-            self._engine._lock.release()
+        engine = self._engine
+        engine._lock.acquire()
+        if not any(held is self._image for held in engine._images) or self._image.object_id is None:
+            engine._lock.release()
             raise RuntimeError("the resident image was overwritten before it could be leased")
-        self._held[3].synchronize()  # the image is complete once its drain to the host has finished
-        return self._held[1].data_ptr()
+        self._image.done.synchronize()  # the image is complete once its drain to the host has finished
+        return engine._arena.data_ptr() + self._image.offset
 
     def __exit__(self, *exc) -> None:
         self._engine._lock.release()

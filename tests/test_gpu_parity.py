@@ -325,6 +325,46 @@ def test_overlapped_save_reads_sources_before_safe_to_mutate(shm_path, golden_di
     com.teardown_pool()
 
 
+def test_overlapped_save_of_several_objects_packs_them_back_to_back(shm_path):
+    """A save that writes two objects per rank: the second object's pack kernel does not wait for the
+    first object's transfer to the host, both objects match the oracle, and both images stay
+    resident in HBM for replication."""
+    from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
+    from ml_flashpoint.core.buffer_pool import BufferPoolConfig
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+    from ml_flashpoint.core.gpu_engine import CudaCopyEngine
+
+    engine = CudaCopyEngine(mode="staged")
+    g = torch.Generator(device="cuda").manual_seed(21)
+    tensors = {f"w{i}": torch.randint(-100, 100, (128 << 20,), device="cuda", dtype=torch.int32, generator=g) for i in range(4)}
+    case = {"tensors": tensors, "blobs": {"note": b"two objects"}, "bucket_count": 2}
+    CheckpointObjectManager._worker_pool = None
+    pool = BufferPoolConfig(str(shm_path / "pool"), 0, 2, (1 << 30) + (1 << 20), register_cuda=True)
+    saver, com = make_saver(copy_engine=engine, pool_config=pool)
+    ckpt = CheckpointContainerId(str(shm_path / "step-1_ckpt"))
+    items, resolver = cases.write_items_and_resolver(case)
+    for step in range(2):  # the first save sizes the arena, the second one runs in the steady state
+        saver.initialize_checkpoint(ckpt)
+        buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=2)
+        assert len(buckets) == 2
+        pending = saver.write_data_async(ckpt, buckets)
+        pending.wait_safe_to_mutate()
+        pending.result()
+        tickets = [part[3] for part in pending._parts]
+    first, second = tickets
+    second_packed = first.start_event.elapsed_time(second.mutate_event)
+    first_drained = first.start_event.elapsed_time(first.done_event)
+    assert second_packed < first_drained, (second_packed, first_drained)
+    cpu_case = {"tensors": {k: v.cpu() for k, v in tensors.items()}, "blobs": case["blobs"], "bucket_count": 2}
+    want = {name: data for name, data, _ in oracle.save_case(cpu_case)}
+    for bucket in buckets:
+        with open(str(bucket.object_id), "rb") as f:
+            data = f.read()
+        assert data == want[bucket.object_name], bucket.object_name
+        assert engine.resident_image(str(bucket.object_id), len(data) - 4096) is not None
+    com.teardown_pool()
+
+
 def test_read_tensor_per_item_api_matches_reference(tmp_path, golden_dir, engine):
     """The per-item ``read_tensor(view, req, use_optimized_loader=True)`` call of the reference API."""
     from torch.distributed.checkpoint.metadata import MetadataIndex

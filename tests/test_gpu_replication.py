@@ -59,7 +59,7 @@ def test_put_then_get_round_trip(shm_path, services, resident):
     com, oid = _save_object(shm_path, engine)
     primary = open(str(oid), "rb").read()
     if not resident:
-        engine._resident = None  # as after a later save reused the HBM image: source is the host mapping
+        engine.drop_resident_images()  # as after a later save reused the HBM image: source is the host mapping
     else:
         assert gpu_engine.resident_image(str(oid), len(primary) - 4096) is not None
     buf = com.get_buffer(oid)
