@@ -64,7 +64,10 @@ int32_t mlf_buf_is_closed(const mlf_buf* b);
 int32_t mlf_buf_is_readonly(const mlf_buf* b);
 /* Page-lock the mapping and map it for the current CUDA device (cudaHostRegister with the
  * portable+mapped flags, plus read-only for RO mappings). Pages are touched first so that
- * registration does not fault them in one by one. No-op if already registered. */
+ * registration does not fault them in one by one. No-op if already registered. The mapping is
+ * locked in 512 MiB chunks: mlf_buf_resize of a registered buffer then re-locks only the chunks
+ * behind the smaller of the old and new end, and mlf_memcpy_async cuts its transfers at chunk
+ * boundaries. Kernels still see one contiguous range (mlf_buf_dev_ptr). */
 int32_t mlf_buf_register(mlf_buf* b);
 int32_t mlf_buf_unregister(mlf_buf* b);
 int32_t mlf_buf_is_registered(const mlf_buf* b);

@@ -5,8 +5,10 @@
 // O_EXCL or O_TRUNC + ftruncate + mmap(MAP_SHARED), read-only open sized by fstat, resize as
 // munmap/ftruncate/mmap, close with optional truncation. What is new is the page-locking
 // lifecycle: a mapping can be registered with CUDA so that the pack kernel and the copy engines
-// address it directly, and every operation that unmaps or shrinks the file drops the
-// registration first (pinned pages of a truncated tmpfs file would otherwise be orphaned).
+// address it directly. The mapping is page-locked in chunks of kRegChunk bytes, so that resizing a
+// registered buffer (a pool buffer shrunk to the object's exact size) only touches the chunks
+// behind the new end instead of page-locking the whole file again; pages are never left pinned
+// behind the end of a truncated file (they would be orphaned).
 #include <errno.h>
 #include <fcntl.h>
 #include <string.h>
@@ -14,6 +16,9 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <functional>
+#include <map>
+#include <mutex>
 #include <string>
 #include <thread>
 #include <vector>
@@ -35,6 +40,8 @@ struct mlf_buf {
   bool readonly = false;
   bool closed = true;
   bool registered = false;
+  uint64_t reg_chunk = 0;             // chunk size of this registration (the capacity if it is one range)
+  std::vector<uint64_t> reg_lens;     // bytes page-locked in chunk i, which starts at ptr + i * reg_chunk
 };
 
 namespace {
@@ -85,28 +92,149 @@ void populate(void* p, uint64_t n, bool writable) {
   for (auto& th : pool) th.join();
 }
 
-int32_t drop_registration(mlf_buf* b) {
-  if (!b->registered) return MLF_OK;
-  cudaError_t e = cudaHostUnregister(b->ptr);
-  b->registered = false;
+constexpr uint64_t kRegChunk = 512ull << 20;
+constexpr int32_t kNotInPlace = 1;  // internal: the mapping cannot be resized where it is
+
+// Address ranges page-locked by this library, for cutting copies at their boundaries.
+std::mutex g_locked_mu;
+std::map<uintptr_t, uintptr_t> g_locked;  // start -> end
+
+int32_t lock_range(char* p, uint64_t len, bool readonly) {
+  unsigned flags = cudaHostRegisterPortable | cudaHostRegisterMapped;
+  if (readonly) flags |= cudaHostRegisterReadOnly;
+  cudaError_t e = cudaHostRegister(p, len, flags);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return mlf::cuda_fail(e, "cudaHostRegister");
+  }
+  std::lock_guard<std::mutex> hold(g_locked_mu);
+  g_locked[(uintptr_t)p] = (uintptr_t)p + len;
+  return MLF_OK;
+}
+
+int32_t unlock_range(char* p) {
+  {
+    std::lock_guard<std::mutex> hold(g_locked_mu);
+    g_locked.erase((uintptr_t)p);
+  }
+  cudaError_t e = cudaHostUnregister(p);
   if (e != cudaSuccess) return mlf::cuda_fail(e, "cudaHostUnregister");
   return MLF_OK;
 }
 
+// Unlocks chunks from the back until `keep` chunks remain.
+int32_t unlock_chunks_from(mlf_buf* b, size_t keep) {
+  int32_t rc = MLF_OK;
+  while (b->reg_lens.size() > keep) {
+    const size_t i = b->reg_lens.size() - 1;
+    const int32_t r = unlock_range(static_cast<char*>(b->ptr) + i * b->reg_chunk);
+    if (r != MLF_OK && rc == MLF_OK) rc = r;
+    b->reg_lens.pop_back();
+  }
+  return rc;
+}
+
+// Page-locks [from, capacity) of the mapping, chunk by chunk; `from` is a chunk boundary.
+int32_t lock_chunks_to_end(mlf_buf* b, uint64_t from) {
+  for (uint64_t at = from; at < b->capacity; at += b->reg_chunk) {
+    const uint64_t len = std::min<uint64_t>(b->reg_chunk, b->capacity - at);
+    const int32_t rc = lock_range(static_cast<char*>(b->ptr) + at, len, b->readonly);
+    if (rc != MLF_OK) return rc;
+    b->reg_lens.push_back(len);
+  }
+  return MLF_OK;
+}
+
+int32_t drop_registration(mlf_buf* b) {
+  if (!b->registered) return MLF_OK;
+  const int32_t rc = unlock_chunks_from(b, 0);
+  b->registered = false;
+  return rc;
+}
+
 int32_t do_register(mlf_buf* b) {
   populate(b->ptr, b->capacity, !b->readonly);
-  unsigned flags = cudaHostRegisterPortable | cudaHostRegisterMapped;
-  if (b->readonly) flags |= cudaHostRegisterReadOnly;
-  cudaError_t e = cudaHostRegister(b->ptr, b->capacity, flags);
-  if (e != cudaSuccess) {
+  // Kernels address the whole mapping through one device pointer. Chunks keep that property only
+  // where registered host memory is addressed by its host pointer; elsewhere lock one range.
+  int dev = 0, same_pointer = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&same_pointer, cudaDevAttrCanUseHostPointerForRegisteredMem, dev) != cudaSuccess) {
     (void)cudaGetLastError();
-    return mlf::cuda_fail(e, "cudaHostRegister");
+    same_pointer = 0;
+  }
+  b->reg_chunk = same_pointer ? kRegChunk : std::max<uint64_t>(b->capacity, 1);
+  b->reg_lens.clear();
+  const int32_t rc = lock_chunks_to_end(b, 0);
+  if (rc != MLF_OK) {
+    (void)unlock_chunks_from(b, 0);
+    return rc;
   }
   b->registered = true;
   return MLF_OK;
 }
 
+// Resizes a registered mapping without moving it: only the chunks behind the smaller of the two
+// ends are unlocked and locked again. Returns kNotInPlace (nothing changed) if the mapping
+// cannot grow where it is; the caller then takes the general path.
+int32_t resize_registered_in_place(mlf_buf* b, uint64_t new_capacity) {
+  const uint64_t chunk = b->reg_chunk;
+  if (chunk != kRegChunk) return kNotInPlace;  // one-range registration
+  const uint64_t old_capacity = b->capacity;
+  const uint64_t edge = std::min(old_capacity, new_capacity);
+  const size_t keep = (size_t)(edge / chunk);  // chunks entirely in front of the edge stay locked
+  if (new_capacity > old_capacity) {
+    if (ftruncate(b->fd, (off_t)new_capacity) != 0) return mlf::fail_errno(MLF_ERR_IO, "ftruncate() failed during resize of " + b->id);
+    // the partial chunk at the old end is unlocked first: it will be locked again, longer
+    int32_t rc = unlock_chunks_from(b, keep);
+    if (rc != MLF_OK) return rc;
+    void* p = mremap(b->ptr, old_capacity, new_capacity, 0);
+    if (p == MAP_FAILED) {
+      (void)ftruncate(b->fd, (off_t)old_capacity);
+      rc = lock_chunks_to_end(b, keep * chunk);  // as before
+      return rc != MLF_OK ? rc : kNotInPlace;
+    }
+    b->capacity = new_capacity;
+    populate(static_cast<char*>(b->ptr) + keep * chunk, new_capacity - keep * chunk, true);
+    return lock_chunks_to_end(b, keep * chunk);
+  }
+  int32_t rc = unlock_chunks_from(b, keep);
+  if (rc != MLF_OK) return rc;
+  if (mremap(b->ptr, old_capacity, new_capacity, 0) == MAP_FAILED)
+    return mlf::fail_errno(MLF_ERR_IO, "mremap() failed during resize of " + b->id);
+  b->capacity = new_capacity;
+  if (ftruncate(b->fd, (off_t)new_capacity) != 0) return mlf::fail_errno(MLF_ERR_IO, "ftruncate() failed during resize of " + b->id);
+  return lock_chunks_to_end(b, keep * chunk);
+}
+
 }  // namespace
+
+namespace mlf {
+void for_each_locked_piece(const void* p, uint64_t n, const std::function<void(const void*, uint64_t)>& fn) {
+  uintptr_t at = (uintptr_t)p;
+  const uintptr_t end = at + n;
+  std::vector<std::pair<uintptr_t, uintptr_t>> cuts;
+  {
+    std::lock_guard<std::mutex> hold(g_locked_mu);
+    auto it = g_locked.upper_bound(at);
+    if (it != g_locked.begin()) --it;
+    for (; it != g_locked.end() && it->first < end; ++it)
+      if (it->second > at) cuts.emplace_back(it->first, it->second);
+  }
+  for (const auto& range : cuts) {
+    if (range.first > at) {  // bytes in front of this range that are not page-locked by this library
+      fn(reinterpret_cast<const void*>(at), std::min(range.first, end) - at);
+      at = std::min(range.first, end);
+    }
+    if (at >= end) break;
+    const uintptr_t stop = std::min(range.second, end);
+    if (stop > at) {
+      fn(reinterpret_cast<const void*>(at), stop - at);
+      at = stop;
+    }
+  }
+  if (at < end) fn(reinterpret_cast<const void*>(at), end - at);
+}
+}  // namespace mlf
 
 namespace mlf {
 std::atomic<uint64_t> g_launches{0};
@@ -212,7 +340,18 @@ int32_t mlf_buf_resize(mlf_buf* b, uint64_t new_capacity) {
   if (new_capacity == 0) return mlf::fail(MLF_ERR_INVALID, "cannot resize to 0 bytes: " + b->id);
   if (new_capacity == b->capacity) return MLF_OK;
   bool was_registered = b->registered;
-  int32_t rc = drop_registration(b);
+  int32_t rc = MLF_OK;
+  if (was_registered) {
+    rc = resize_registered_in_place(b, new_capacity);
+    if (rc != kNotInPlace) {
+      if (rc != MLF_OK) {  // half-done: give the page locks up, the mapping itself is still consistent
+        (void)drop_registration(b);
+      }
+      return rc;
+    }
+    mlf::clear_error();
+  }
+  rc = drop_registration(b);
   if (rc != MLF_OK) return rc;
   if (munmap(b->ptr, b->capacity) != 0) return mlf::fail_errno(MLF_ERR_IO, "munmap() failed during resize of " + b->id);
   b->ptr = nullptr;
@@ -288,8 +427,17 @@ int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr,
   if (offset > b->capacity || nbytes > b->capacity - offset)
     return mlf::fail(MLF_ERR_BOUNDS, "read of " + std::to_string(nbytes) + " bytes at " + std::to_string(offset) +
                                          " leaves the object " + b->id);
-  if (b->registered) {  // page-locked already: one copy-engine transfer, no CPU copy
-    MLF_CUDA(cudaMemcpy(dev_ptr, static_cast<char*>(b->ptr) + offset, nbytes, cudaMemcpyHostToDevice));
+  if (b->registered) {  // page-locked already: copy-engine transfers, no CPU copy
+    const char* src = static_cast<const char*>(b->ptr) + offset;
+    char* dst = static_cast<char*>(dev_ptr);
+    int32_t rc = MLF_OK;
+    mlf::for_each_locked_piece(src, nbytes, [&](const void* piece, uint64_t len) {
+      if (rc != MLF_OK) return;
+      cudaError_t e = cudaMemcpyAsync(dst + (static_cast<const char*>(piece) - src), piece, len, cudaMemcpyHostToDevice, 0);
+      if (e != cudaSuccess) rc = mlf::cuda_fail(e, "cudaMemcpyAsync");
+    });
+    if (rc != MLF_OK) return rc;
+    MLF_CUDA(cudaStreamSynchronize(0));
     return MLF_OK;
   }
   return mlf::bounce_transfer(dev_ptr, nullptr, b->fd, offset, nbytes, 1, nthreads);

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <functional>
 #include <string>
 
 #include "mlf_b200.h"
@@ -22,6 +23,11 @@ extern std::atomic<uint64_t> g_launches;
 
 int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off, uint64_t nbytes, int32_t to_device,
                         int32_t nthreads);
+
+// Calls fn(piece, length) for consecutive pieces of the host range [p, p + n), cut wherever a
+// range page-locked by this library starts or ends: a copy-engine transfer must stay inside one
+// page-locked range to be treated as such.
+void for_each_locked_piece(const void* p, uint64_t n, const std::function<void(const void*, uint64_t)>& fn);
 
 inline int32_t cuda_fail(cudaError_t e, const char* what) {
   return fail(MLF_ERR_CUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");

@@ -69,8 +69,21 @@ int32_t mlf_memcpy_async(void* dst, const void* src, uint64_t nbytes, int32_t ki
     case MLF_COPY_D2D: k = cudaMemcpyDeviceToDevice; break;
     default: return mlf::fail(MLF_ERR_INVALID, "mlf_memcpy_async: unknown copy kind");
   }
-  MLF_CUDA(cudaMemcpyAsync(dst, src, nbytes, k, static_cast<cudaStream_t>(stream)));
-  return MLF_OK;
+  if (k == cudaMemcpyDeviceToDevice) {
+    MLF_CUDA(cudaMemcpyAsync(dst, src, nbytes, k, static_cast<cudaStream_t>(stream)));
+    return MLF_OK;
+  }
+  // a page-locked mapping is locked in chunks: one transfer per chunk it touches
+  const char* host = static_cast<const char*>(k == cudaMemcpyDeviceToHost ? dst : src);
+  int32_t rc = MLF_OK;
+  mlf::for_each_locked_piece(host, nbytes, [&](const void* piece, uint64_t len) {
+    if (rc != MLF_OK) return;
+    const uint64_t off = (uint64_t)(static_cast<const char*>(piece) - host);
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(dst) + off, static_cast<const char*>(src) + off, len, k,
+                                    static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) rc = mlf::cuda_fail(e, "cudaMemcpyAsync");
+  });
+  return rc;
 }
 
 }  // extern "C"

@@ -365,6 +365,73 @@ def test_overlapped_save_of_several_objects_packs_them_back_to_back(shm_path):
     com.teardown_pool()
 
 
+def test_page_locked_buffer_resizes_in_place_and_copies_cross_its_chunks(shm_path):
+    """A registered buffer larger than one page-lock chunk: copy-engine transfers and kernel stores
+    that span chunk boundaries land byte-exactly, and shrinking / growing the buffer keeps it
+    registered at the same address with its contents, re-locking only its tail."""
+    import time
+
+    from ml_flashpoint import _native
+    from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+    lib = _native.lib()
+    chunk = 512 << 20
+    size = 3 * chunk + 12345
+    buf = BufferObject(str(shm_path / "big.distcp"), size, overwrite=True)
+    t0 = time.perf_counter()
+    buf.register_cuda()
+    full_lock_s = time.perf_counter() - t0
+    assert buf.is_cuda_registered and buf.get_device_ptr() == buf.get_data_ptr()
+    base = buf.get_data_ptr()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    src = torch.randint(0, 256, (size,), device="cuda", dtype=torch.uint8, generator=g)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def check(offset, nbytes):
+        got = bytes(memoryview(buf)[offset : offset + nbytes])
+        assert got == bytes(src[offset : offset + nbytes].cpu().numpy()), (offset, nbytes)
+
+    # copy engine: one call across all four chunks, at an odd offset
+    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(base + 7), ctypes.c_void_p(src.data_ptr() + 7), size - 7, _native.MLF_COPY_D2H, ctypes.c_void_p(stream)))
+    torch.cuda.synchronize()
+    for edge in (chunk, 2 * chunk, 3 * chunk):
+        check(edge - 4096, 8192)
+    check(7, 4096)
+    check(size - 4096, 4096)
+    # kernel stores into the mapping across the first chunk boundary
+    memoryview(buf)[chunk - 1000 : chunk + 1000] = bytes(2000)
+    _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(buf.get_device_ptr() + chunk - 1000), ctypes.c_void_p(src.data_ptr() + chunk - 1000), 2000, ctypes.c_void_p(stream), 4))
+    torch.cuda.synchronize()
+    check(chunk - 1000, 2000)
+
+    # shrink to a size that is neither chunk- nor page-aligned: same address, still registered
+    smaller = 2 * chunk + 300 * 1024 * 1024 + 123
+    t0 = time.perf_counter()
+    buf.resize(smaller)
+    shrink_s = time.perf_counter() - t0
+    assert buf.get_capacity() == smaller and os.path.getsize(buf.get_id()) == smaller
+    assert buf.is_cuda_registered and buf.get_data_ptr() == base
+    assert shrink_s < full_lock_s / 2, (shrink_s, full_lock_s)
+    check(2 * chunk - 4096, 8192)
+    check(smaller - 4096, 4096)
+    back = torch.zeros(smaller, dtype=torch.uint8, device="cuda")
+    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(back.data_ptr()), ctypes.c_void_p(base), smaller, _native.MLF_COPY_H2D, ctypes.c_void_p(stream)))
+    torch.cuda.synchronize()
+    assert torch.equal(back, src[:smaller])
+
+    # grow again: registered afterwards wherever the mapping ends up, old bytes kept, new bytes zero
+    buf.resize(size)
+    assert buf.is_cuda_registered and buf.get_capacity() == size
+    check(0, 4096)
+    check(smaller - 4096, 4096)
+    assert bytes(memoryview(buf)[smaller : smaller + 4096]) == bytes(4096)
+    base = buf.get_data_ptr()
+    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(base + smaller - 100), ctypes.c_void_p(src.data_ptr() + smaller - 100), size - smaller + 100, _native.MLF_COPY_D2H, ctypes.c_void_p(stream)))
+    torch.cuda.synchronize()
+    check(smaller - 100, size - smaller + 100)
+    buf.close()
+
+
 def test_read_tensor_per_item_api_matches_reference(tmp_path, golden_dir, engine):
     """The per-item ``read_tensor(view, req, use_optimized_loader=True)`` call of the reference API."""
     from torch.distributed.checkpoint.metadata import MetadataIndex
