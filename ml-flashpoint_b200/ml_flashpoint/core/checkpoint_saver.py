@@ -357,8 +357,10 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
             try:
                 # existing objects are overwritten: a restarted job may rewrite steps it abandoned
                 with self._chkpt_obj_manager.acquire_buffer(bucket.object_id, self._initial_buffer_size_bytes) as writer:
-                    records = self._write_bucket(bucket, writer, use_optimized_write)
-                results_from_threads.put((self._to_write_results(bucket.object_name, records), None))
+                    records, ticket = self._write_bucket(bucket, writer, use_optimized_write, wait=False)
+                    results = self._to_write_results(bucket.object_name, records)  # while the bytes move
+                    ticket.wait()
+                results_from_threads.put((results, None))
                 if replicate_after_write:
                     self.async_replicate_object(bucket.object_id)
             except Exception as e:
