@@ -524,6 +524,18 @@ class CudaCopyEngine:
                 hi = max(hi, first + span * esize)
                 prepared.append((target, first, istr))
             lo -= lo % 16  # keep image offsets congruent mod 16 between the mapping and the HBM copy
+            # the plan (tables uploaded once) is built before the bytes start to move
+            descs = (_native.CopyDesc * len(prepared))()
+            host_targets = []
+            for k, (target, first, istr) in enumerate(prepared):
+                dev_target = target
+                if target.device.type != "cuda":
+                    dev_target = torch.empty(target.shape, dtype=target.dtype, device=self.device)
+                    host_targets.append((target, dev_target))
+                elif target.device != self.device:
+                    raise ValueError(f"target lives on {target.device}, engine on {self.device}")
+                fill_desc(descs[k], dev_target.data_ptr(), first - lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
+            plan = _Plan(descs, len(prepared), _native.MLF_UNPACK)
             image = self.staging(hi - lo)
             stream = self.pack_stream
             ready = torch.cuda.Event()
@@ -562,17 +574,6 @@ class CudaCopyEngine:
                         )
                     )
             t_copied.record(stream)
-            descs = (_native.CopyDesc * len(prepared))()
-            host_targets = []
-            for k, (target, first, istr) in enumerate(prepared):
-                dev_target = target
-                if target.device.type != "cuda":
-                    dev_target = torch.empty(target.shape, dtype=target.dtype, device=self.device)
-                    host_targets.append((target, dev_target))
-                elif target.device != self.device:
-                    raise ValueError(f"target lives on {target.device}, engine on {self.device}")
-                fill_desc(descs[k], dev_target.data_ptr(), first - lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
-            plan = _Plan(descs, len(prepared), _native.MLF_UNPACK)
             t_launch = torch.cuda.Event(enable_timing=True)
             t_launch.record(stream)
             plan.launch(image.data_ptr(), hi - lo, stream.cuda_stream)
