@@ -298,6 +298,87 @@ def test_every_staged_regime_packs_and_unpacks_bit_exactly(dtype):
         assert torch.equal(torch.view_as_real(base) if base.is_complex() else base, torch.view_as_real(want) if want.is_complex() else want)
 
 
+def _random_view(rng, dtype):
+    """A random strided view: random rank and extents, then a random permutation, random slices
+    (sometimes stepped) and now and then an expanded dimension."""
+    rank = rng.randint(1, 5)
+    budget = rng.choice([40, 3000, 200000, 1500000])
+    dims = []
+    for _ in range(rank):
+        d = max(1, int(round(budget ** (rng.random() / rank * 2))))
+        dims.append(min(d, 700))
+    base = torch.randint(0, 120, tuple(dims), dtype=torch.int64).to(dtype)
+    view = base.permute(*rng.sample(range(rank), rank)) if rank > 1 and rng.random() < 0.7 else base
+    index = []
+    for n in view.shape:
+        kind = rng.random()
+        if kind < 0.5 or n < 3:
+            index.append(slice(None))
+        elif kind < 0.85:
+            a = rng.randint(0, n - 2)
+            index.append(slice(a, rng.randint(a + 1, n)))
+        else:
+            index.append(slice(rng.randint(0, 1), None, rng.randint(2, 3)))
+    view = view[tuple(index)]
+    return base.cuda().as_strided(view.shape, view.stride(), view.storage_offset())
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_views_pack_and_unpack_like_the_oracle(seed):
+    """Differential test over random strided views (permutations, slices, steps) of every element
+    size: packed bytes equal the oracle's C-order payload, unpacking into zeroed copies of the
+    same views restores exactly the viewed elements and nothing else."""
+    import random as _random
+
+    from ml_flashpoint import _native
+    from ml_flashpoint.core.gpu_engine import _Plan, c_strides, fill_desc
+
+    rng = _random.Random(1000 + seed)
+    torch.manual_seed(seed)
+    dtypes = [torch.uint8, torch.int16, torch.int32, torch.int64]
+    views = [_random_view(rng, rng.choice(dtypes)) for _ in range(40)]
+    views = [v for v in views if v.numel() > 0]
+    n = len(views)
+    descs = (_native.CopyDesc * n)()
+    offsets, at = [], rng.randint(0, 15)
+    for v in views:
+        offsets.append(at)
+        at += v.numel() * v.element_size() + rng.randint(0, 40)
+    image = torch.full((at + 64,), 0x5A, dtype=torch.uint8, device="cuda")
+    for i, v in enumerate(views):
+        fill_desc(descs[i], v.data_ptr(), offsets[i], v.element_size(), v.shape, v.stride(), c_strides(v.shape))
+    stream = torch.cuda.current_stream().cuda_stream
+    plan = _Plan(descs, n, _native.MLF_PACK)
+    plan.launch(image.data_ptr(), image.numel(), stream)
+    torch.cuda.synchronize()
+    plan.status()
+    expect = bytearray(b"\x5a" * image.numel())
+    for v, o in zip(views, offsets):
+        payload = oracle.tensor_payload(v.cpu())
+        expect[o : o + len(payload)] = payload
+    got = image.cpu().numpy().tobytes()
+    if got != bytes(expect):
+        bad = next(i for i in range(len(got)) if got[i] != expect[i])
+        which = max(k for k, o in enumerate(offsets) if o <= bad)
+        pytest.fail(f"seed {seed}: byte {bad} differs, view {which}: shape {tuple(views[which].shape)} stride {views[which].stride()} {views[which].dtype}")
+
+    targets, bases = [], []
+    for v in views:
+        base = torch.zeros_like(v._base if v._base is not None else v)
+        bases.append(base)
+        targets.append(base.as_strided(v.shape, v.stride(), v.storage_offset()))
+    for i, t in enumerate(targets):
+        fill_desc(descs[i], t.data_ptr(), offsets[i], t.element_size(), t.shape, t.stride(), c_strides(t.shape))
+    plan = _Plan(descs, n, _native.MLF_UNPACK)
+    plan.launch(image.data_ptr(), image.numel(), stream)
+    torch.cuda.synchronize()
+    plan.status()
+    for k, (v, base) in enumerate(zip(views, bases)):
+        want = torch.zeros_like(base)
+        want.as_strided(v.shape, v.stride(), v.storage_offset()).copy_(v)
+        assert torch.equal(base, want), f"seed {seed}: view {k}: shape {tuple(v.shape)} stride {v.stride()} {v.dtype}"
+
+
 def test_overlapped_save_reads_sources_before_safe_to_mutate(shm_path, golden_dir, engine):
     """After ``wait_safe_to_mutate`` the sources may be overwritten: the object still holds the old values."""
     from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
