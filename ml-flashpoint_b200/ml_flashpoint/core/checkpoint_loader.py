@@ -13,6 +13,7 @@ copy engine and the kernel writes every target (any strides, any sub-block) dire
 """
 
 import abc
+import contextlib
 import fcntl
 import io
 import logging
@@ -187,10 +188,19 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
             _LOGGER.error(error_msg)
             raise FileNotFoundError(error_msg)
 
-        with self._checkpoint_object_manager.get_buffer(checkpoint_object_id) as stream:
+        with contextlib.ExitStack() as scope:
+            stream = scope.enter_context(self._checkpoint_object_manager.get_buffer(checkpoint_object_id))
             optimized = stream.format_signature == CheckpointFormat.MLF_FORMAT
             scatter = []  # (target, payload offset, stored shape, storage offsets)
             commits = []  # (req, target)
+            # The bytes start moving into HBM now; headers are parsed and the plan is built meanwhile.
+            prefetched = None
+            tensor_items = [storage_data[req.storage_index] for req in read_items if req.type != LoadItemType.BYTE_IO]
+            start_read = getattr(self._engine(), "object_read", None) if optimized and tensor_items else None
+            if start_read is not None:
+                lo = min(md.offset for md in tensor_items)
+                hi = max(md.offset + md.length for md in tensor_items)
+                prefetched = scope.enter_context(start_read(stream, lo, hi))
             for req in read_items:
                 item_md = storage_data[req.storage_index]
                 if req.type == LoadItemType.BYTE_IO:
@@ -220,7 +230,10 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
                 scatter.append((target, item_md.offset + header_bytes, tuple(shape), tuple(req.storage_offsets)))
                 commits.append((req, target))
             if scatter:
-                self._engine().unpack(scatter, stream)
+                if prefetched is not None:
+                    self._engine().unpack(scatter, stream, prefetched=prefetched)
+                else:
+                    self._engine().unpack(scatter, stream)
             for req, target in commits:
                 planner.commit_tensor(req, target)
 

@@ -296,6 +296,7 @@ class CudaCopyEngine:
         self._arena_goal = 0  # bytes the arena should hold: the largest save announced so far
         self._cursor = 0
         self._images: List[_Image] = []  # regions whose contents are still valid, oldest first
+        self._active_read: Optional["_ObjectRead"] = None  # a restore's image being filled right now
         self.last_ticket: Optional[PackTicket] = None  # most recent save, for timing queries
         self.last_unpack_ms: Optional[Tuple[float, float]] = None  # (host-to-HBM ms, kernel ms) of the last restore
         with torch.cuda.device(self.device):
@@ -337,6 +338,9 @@ class CudaCopyEngine:
     def _reserve_image(self, nbytes: int, stream: "torch.cuda.Stream") -> Tuple[torch.Tensor, int]:
         """Region of ``nbytes`` for a new object image. Work queued on ``stream`` afterwards runs
         after the transfers out of any older image the region overlaps; those images are forgotten."""
+        if self._active_read is not None:
+            self._active_read.wait()  # a restore's image occupies the arena until it has arrived
+            self._active_read = None
         self._ensure_arena(nbytes)
         if self._cursor + nbytes > self._arena.numel():
             self._cursor = 0
@@ -498,14 +502,60 @@ class CudaCopyEngine:
                     return _ResidentLease(self, image)
         return None
 
-    def unpack(self, reads: Sequence[Tuple[torch.Tensor, int, Sequence[int], Sequence[int]]], buffer_io) -> None:
+    def _fill_image(self, image: torch.Tensor, buffer_io, lo: int, nbytes: int, stream: "torch.cuda.Stream") -> None:
+        """Brings data-section bytes ``[lo, lo + nbytes)`` of ``buffer_io`` into ``image``. Asynchronous on
+        ``stream`` for a page-locked mapping, blocking (CPU threads feeding the bounce ring) otherwise."""
+        if self._is_registered(buffer_io):
+            _native.check(
+                _native.lib().mlf_memcpy_async(
+                    ctypes.c_void_p(image.data_ptr()),
+                    ctypes.c_void_p(buffer_io.host_address(lo)),
+                    nbytes,
+                    _native.MLF_COPY_H2D,
+                    ctypes.c_void_p(stream.cuda_stream),
+                )
+            )
+            return
+        # read-only object mappings cannot be page-locked: feed HBM through the bounce ring,
+        # reading the file descriptor so that the mapping's pages are never faulted in
+        stream.synchronize()
+        reader = getattr(getattr(buffer_io, "buffer_obj", None), "read_to_device", None)
+        if reader is not None:
+            from ml_flashpoint.checkpoint_object_manager.buffer_metadata import METADATA_SIZE
+
+            reader(METADATA_SIZE + lo, image.data_ptr(), nbytes, self.restore_threads)
+        else:
+            _native.check(
+                _native.lib().mlf_bounce_copy(
+                    ctypes.c_void_p(image.data_ptr()),
+                    ctypes.c_void_p(buffer_io.host_address(lo)),
+                    nbytes,
+                    1,
+                    self.restore_threads,
+                )
+            )
+
+    def object_read(self, buffer_io, lo: int, hi: int) -> "_ObjectRead":
+        """Context manager that starts moving data-section bytes ``[lo, hi)`` of ``buffer_io`` into HBM
+        at once, on a helper thread, so that the caller can parse headers and plan the restore while
+        the bytes travel. Pass the object to ``unpack(..., prefetched=...)`` inside the ``with`` block.
+        The engine is reserved for the calling thread until the block ends."""
+        return _ObjectRead(self, buffer_io, lo, hi)
+
+    def unpack(
+        self,
+        reads: Sequence[Tuple[torch.Tensor, int, Sequence[int], Sequence[int]]],
+        buffer_io,
+        prefetched: Optional["_ObjectRead"] = None,
+    ) -> None:
         """Scatters stored tensors (or sub-blocks) from ``buffer_io`` into target tensors.
 
         Each read is ``(target, image_off, stored_shape, storage_offsets)``: ``image_off`` is the
         data-section offset of the stored tensor's first payload byte, ``stored_shape`` its shape as
         saved, ``storage_offsets`` where the wanted block starts in it; the block's extent is
         ``target.shape``. Targets may be strided; host targets are filled through a device
-        temporary. Returns when all targets hold their data.
+        temporary. ``prefetched`` is an ``object_read`` of the same buffer that is already bringing
+        the bytes into HBM. Returns when all targets hold their data.
         """
         reads = [r for r in reads if r[0].numel() > 0]
         if not reads:
@@ -524,7 +574,13 @@ class CudaCopyEngine:
                 hi = max(hi, first + span * esize)
                 prepared.append((target, first, istr))
             lo -= lo % 16  # keep image offsets congruent mod 16 between the mapping and the HBM copy
-            # the plan (tables uploaded once) is built before the bytes start to move
+            use_prefetch = prefetched is not None and prefetched.covers(buffer_io, lo, hi)
+            if use_prefetch:
+                lo, hi = prefetched.lo, prefetched.hi
+            elif self._active_read is not None:
+                self._active_read.wait()  # its image is about to be given up
+                self._active_read = None
+            # the plan (tables uploaded once) is built before the bytes have arrived
             descs = (_native.CopyDesc * len(prepared))()
             host_targets = []
             for k, (target, first, istr) in enumerate(prepared):
@@ -536,44 +592,21 @@ class CudaCopyEngine:
                     raise ValueError(f"target lives on {target.device}, engine on {self.device}")
                 fill_desc(descs[k], dev_target.data_ptr(), first - lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
             plan = _Plan(descs, len(prepared), _native.MLF_UNPACK)
-            image = self.staging(hi - lo)
             stream = self.pack_stream
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
             stream.wait_event(ready)
-            t_begin = torch.cuda.Event(enable_timing=True)
-            t_copied = torch.cuda.Event(enable_timing=True)
-            t_begin.record(stream)
-            if self._is_registered(buffer_io):
-                _native.check(
-                    _native.lib().mlf_memcpy_async(
-                        ctypes.c_void_p(image.data_ptr()),
-                        ctypes.c_void_p(buffer_io.host_address(lo)),
-                        hi - lo,
-                        _native.MLF_COPY_H2D,
-                        ctypes.c_void_p(stream.cuda_stream),
-                    )
-                )
+            if use_prefetch:
+                image = prefetched.image
+                fill_ms = prefetched.wait()
             else:
-                # read-only object mappings cannot be page-locked: feed HBM through the bounce ring,
-                # reading the file descriptor so that the mapping's pages are never faulted in
-                stream.synchronize()
-                reader = getattr(getattr(buffer_io, "buffer_obj", None), "read_to_device", None)
-                if reader is not None:
-                    from ml_flashpoint.checkpoint_object_manager.buffer_metadata import METADATA_SIZE
-
-                    reader(METADATA_SIZE + lo, image.data_ptr(), hi - lo, self.restore_threads)
-                else:
-                    _native.check(
-                        _native.lib().mlf_bounce_copy(
-                            ctypes.c_void_p(image.data_ptr()),
-                            ctypes.c_void_p(buffer_io.host_address(lo)),
-                            hi - lo,
-                            1,
-                            self.restore_threads,
-                        )
-                    )
-            t_copied.record(stream)
+                image = self.staging(hi - lo)
+                t_begin = torch.cuda.Event(enable_timing=True)
+                t_copied = torch.cuda.Event(enable_timing=True)
+                t_begin.record(stream)
+                self._fill_image(image, buffer_io, lo, hi - lo, stream)
+                t_copied.record(stream)
+                fill_ms = None
             t_launch = torch.cuda.Event(enable_timing=True)
             t_launch.record(stream)
             plan.launch(image.data_ptr(), hi - lo, stream.cuda_stream)
@@ -581,11 +614,103 @@ class CudaCopyEngine:
             done.record(stream)
             done.synchronize()
             plan.status()
-            self.last_unpack_ms = (t_begin.elapsed_time(t_copied), t_launch.elapsed_time(done))
+            if fill_ms is None:
+                fill_ms = t_begin.elapsed_time(t_copied)
+            self.last_unpack_ms = (fill_ms, t_launch.elapsed_time(done))
             for target, dev_target in host_targets:
                 target.copy_(dev_target)
             # later work on the caller's stream must see the restored values
             torch.cuda.current_stream(self.device).wait_event(done)
+
+
+class _ObjectRead:
+    """An object's bytes on their way into the engine's HBM arena (see ``CudaCopyEngine.object_read``)."""
+
+    def __init__(self, engine: CudaCopyEngine, buffer_io, lo: int, hi: int):
+        self._engine = engine
+        self._buffer_io = buffer_io
+        self.lo = lo - lo % 16
+        self.hi = hi
+        self.image: Optional[torch.Tensor] = None
+        self._thread: Optional[threading.Thread] = None
+        self._error: Optional[BaseException] = None
+        self._ms = 0.0
+        self._events = None
+        self._entered = False
+
+    def covers(self, buffer_io, lo: int, hi: int) -> bool:
+        return self.image is not None and buffer_io is self._buffer_io and self.lo <= lo and hi <= self.hi
+
+    def __enter__(self) -> "_ObjectRead":
+        engine = self._engine
+        engine._lock.acquire()
+        self._entered = True
+        try:
+            if self.hi <= self.lo:
+                return self
+            with torch.cuda.device(engine.device):
+                engine._bind()
+                if engine._active_read is not None:
+                    engine._active_read.wait()
+                self.image = engine.staging(self.hi - self.lo)
+                stream = engine.pack_stream
+                if engine._is_registered(self._buffer_io):
+                    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    begin.record(stream)
+                    engine._fill_image(self.image, self._buffer_io, self.lo, self.hi - self.lo, stream)
+                    end.record(stream)
+                    self._events = (begin, end)
+                else:
+                    stream.synchronize()
+                    self._events = None
+                    self._thread = threading.Thread(target=self._run, name="mlf-object-read", daemon=True)
+                    self._thread.start()
+            engine._active_read = self
+            return self
+        except BaseException:
+            self._entered = False
+            engine._lock.release()
+            raise
+
+    def _run(self) -> None:
+        import time
+
+        engine = self._engine
+        started = time.perf_counter()
+        try:
+            with torch.cuda.device(engine.device):
+                engine._bind()
+                engine._fill_image(self.image, self._buffer_io, self.lo, self.hi - self.lo, engine.pack_stream)
+        except BaseException as e:  # surfaces in wait()
+            self._error = e
+        self._ms = (time.perf_counter() - started) * 1e3
+
+    def wait(self) -> float:
+        """Blocks until the bytes are in HBM (or queued ahead of later work on the engine's stream);
+        returns the milliseconds the transfer took."""
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+            if self._error is not None:
+                raise self._error
+        elif self._events is not None:
+            self._events[1].synchronize()
+            self._ms = self._events[0].elapsed_time(self._events[1])
+            self._events = None
+        return self._ms
+
+    def __exit__(self, *exc) -> None:
+        engine = self._engine
+        try:
+            if self._thread is not None:
+                self._thread.join()
+                self._thread = None
+            if engine._active_read is self:
+                engine._active_read = None
+        finally:
+            if self._entered:
+                self._entered = False
+                engine._lock.release()
 
 
 class _ResidentLease:
