@@ -789,7 +789,7 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
         "overlap": overlap,
         "replication": replication,
         "roofline": {
-            "kernel": "mlf_plan_kernel<PACK>",
+            "kernel": "mlf_plan_kernel_stream<PACK>",
             "bound": "hbm",
             "achieved": achieved,
             "peak": peak,

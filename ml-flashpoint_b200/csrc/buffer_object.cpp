@@ -189,7 +189,9 @@ int32_t resize_registered_in_place(mlf_buf* b, uint64_t new_capacity) {
     if (rc != MLF_OK) return rc;
     void* p = mremap(b->ptr, old_capacity, new_capacity, 0);
     if (p == MAP_FAILED) {
-      (void)ftruncate(b->fd, (off_t)old_capacity);
+      if (ftruncate(b->fd, (off_t)old_capacity) != 0) {
+        // best effort: a longer file behind an unchanged mapping is harmless
+      }
       rc = lock_chunks_to_end(b, keep * chunk);  // as before
       return rc != MLF_OK ? rc : kNotInPlace;
     }

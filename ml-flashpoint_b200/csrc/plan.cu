@@ -566,6 +566,108 @@ __device__ __forceinline__ uint32_t find_segment(const uint32_t* __restrict__ ti
   return lo;
 }
 
+// Streaming kernel for plans made of linear tiles only (every contiguous state dict). One elected
+// thread walks this CTA's tiles, issues the bulk loads and publishes, per ring slot, where the
+// slot's bytes go; the other threads never look at the plan tables: they wait for a slot, read its
+// destination from shared memory and drain it. A slot whose published length is 0 ends the loop.
+struct SlotMeta {
+  uint8_t* dst;    // destination of the slot's first payload byte
+  uint32_t len;    // payload bytes in the slot; 0 = no more stages
+  uint32_t shift;  // the payload starts this many bytes into the slot (source misalignment)
+};
+
+template <int DIR>
+__global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg* __restrict__ segs,
+                                                                   const uint32_t* __restrict__ tile_begin, uint32_t nseg,
+                                                                   uint32_t ntiles, uint8_t* __restrict__ image,
+                                                                   int32_t* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
+  __shared__ __align__(8) uint64_t full[mlf::kStages];
+  __shared__ SlotMeta meta[mlf::kStages];
+  __shared__ int abort_flag;
+  const unsigned tid = threadIdx.x;
+
+  // producer state (thread 0 only)
+  uint32_t p_tile = blockIdx.x, p_stage = 0, issued = 0;
+  bool p_finished = false;
+  LinearTile p_lt;
+  p_lt.nstage = 0;
+  auto seek = [&]() {  // loads the span of tile p_tile (every tile of such a plan is linear)
+    if (p_tile < ntiles) {
+      const uint32_t sg = find_segment(tile_begin, nseg, p_tile);
+      (void)linear_span<DIR>(segs[sg], p_tile - tile_begin[sg], image, &p_lt);
+    }
+  };
+  // Fills every free slot: slot (issued % kStages) is free once stage (issued - kStages) was drained.
+  auto top_up = [&](uint32_t consumed) {
+    while (issued < consumed + mlf::kStages && !p_finished) {
+      const uint32_t slot = issued % mlf::kStages;
+      if (p_tile >= ntiles) {
+        meta[slot].len = 0;
+        p_finished = true;
+        ++issued;
+        break;
+      }
+      const uint64_t off = (uint64_t)p_stage * mlf::kStageBytes;
+      const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, p_lt.len - off);
+      const uint8_t* src = p_lt.src + off;
+      const uint32_t shift = (uint32_t)((uintptr_t)src & 15u);
+      const uint32_t bytes = (shift + slen + 15u) & ~15u;
+      meta[slot].dst = p_lt.dst + off;
+      meta[slot].len = slen;
+      meta[slot].shift = shift;
+      mlf::mbar_expect_tx(&full[slot], bytes);
+      mlf::bulk_load(ring + (size_t)slot * mlf::kSlotBytes, src - shift, bytes, &full[slot]);
+      ++issued;
+      if (++p_stage == p_lt.nstage) {
+        p_stage = 0;
+        p_tile += gridDim.x;
+        seek();
+      }
+    }
+  };
+
+  if (tid == 0) {
+    for (uint32_t k = 0; k < mlf::kStages; ++k) mlf::mbar_init(&full[k], 1);
+    mlf::mbar_init_fence();
+    abort_flag = 0;
+    seek();
+    top_up(0);
+  }
+  __syncthreads();  // publishes the first slots' destinations
+
+  uint32_t consumed = 0;
+  bool aborted = false;
+  for (;;) {
+    const uint32_t slot = consumed % mlf::kStages;
+    // written by thread 0 at least one barrier ago: stage `consumed` was issued before the barrier
+    // that ended stage `consumed - 1` (or before the barrier above)
+    const SlotMeta m = meta[slot];
+    if (m.len == 0) break;
+    const bool ok = mlf::mbar_wait_bounded(&full[slot], (consumed / mlf::kStages) & 1u);
+    if (ok) {
+      mlf::drain_slot(m.dst, ring + (size_t)slot * mlf::kSlotBytes, m.shift, m.len, tid, blockDim.x);
+    } else {
+      abort_flag = 1;
+    }
+    __syncthreads();  // the slot is free again; also publishes abort_flag
+    ++consumed;
+    if (abort_flag) {
+      aborted = true;
+      break;
+    }
+    if (tid == 0) top_up(consumed);  // refills the slot just freed; its destination is published by the next barrier
+  }
+  if (aborted && tid == 0) {
+    atomicCAS(status, 0, MLF_ERR_TIMEOUT);
+    // the CTA may not exit while bulk copies still target its shared memory: wait for them too,
+    // again with a budget (the end marker, if one was written, took a slot number but no load)
+    const uint32_t loads_issued = issued - (p_finished ? 1u : 0u);
+    for (uint32_t n = consumed - 1; n < loads_issued; ++n)  // from the stage whose wait ran out
+      (void)mlf::mbar_wait_bounded(&full[n % mlf::kStages], (n / mlf::kStages) & 1u);
+  }
+}
+
 // STAGED = false is the instance for plans made of linear tiles only (every contiguous state dict):
 // it carries none of the staged-tile code, which keeps the streaming loop at its leanest.
 template <int DIR, bool STAGED>
@@ -996,8 +1098,8 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
   if (use_bulk_kernel()) {
     using BulkKernel = void (*)(const Seg*, const uint32_t*, uint32_t, uint32_t, uint8_t*, int32_t*);
     static const BulkKernel kernels[2][2] = {
-        {mlf_plan_kernel_bulk<MLF_PACK, false>, mlf_plan_kernel_bulk<MLF_PACK, true>},
-        {mlf_plan_kernel_bulk<MLF_UNPACK, false>, mlf_plan_kernel_bulk<MLF_UNPACK, true>},
+        {mlf_plan_kernel_stream<MLF_PACK>, mlf_plan_kernel_bulk<MLF_PACK, true>},
+        {mlf_plan_kernel_stream<MLF_UNPACK>, mlf_plan_kernel_bulk<MLF_UNPACK, true>},
     };
     static std::once_flag opted_in;
     static cudaError_t opt_status = cudaSuccess;
