@@ -41,7 +41,7 @@ FSDP_WORLD = 8  # the named configuration shards the model 8 ways whatever --gpu
 # DRAM bytes (read + write) per payload byte of the pack kernel, from an ncu capture of the 2-layer
 # variant of this workload (dram__bytes_read.sum + dram__bytes_write.sum = 5.154 GB for 2.602 GB of
 # payload); traffic grows in proportion to the payload, so a full launch is this ratio times its payload.
-NCU_DRAM_BYTES_PER_PAYLOAD_BYTE = 1.981
+NCU_DRAM_BYTES_PER_PAYLOAD_BYTE = 1.982
 
 
 # --------------------------------------------------------------------------------------
