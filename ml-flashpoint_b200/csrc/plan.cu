@@ -566,10 +566,14 @@ __device__ __forceinline__ uint32_t find_segment(const uint32_t* __restrict__ ti
   return lo;
 }
 
-// Streaming kernel for plans made of linear tiles only (every contiguous state dict). One elected
-// thread walks this CTA's tiles, issues the bulk loads and publishes, per ring slot, where the
-// slot's bytes go; the other threads never look at the plan tables: they wait for a slot, read its
-// destination from shared memory and drain it. A slot whose published length is 0 ends the loop.
+// The plan tables list the segments made of linear tiles first: tiles [0, nlinear) are linear runs,
+// tiles [nlinear, ntiles) are staged tiles (short rows, transposed sub-tiles, single elements).
+//
+// Streaming phase over this CTA's linear tiles. One elected thread walks the tiles, issues the
+// bulk loads and publishes, per ring slot, where the slot's bytes go; the other threads never look
+// at the plan tables: they wait for a slot, read its destination from shared memory and drain it.
+// A slot whose published length is 0 ends the phase. Returns false if a bounded wait ran out
+// (status recorded, outstanding copies awaited): the CTA must then return.
 struct SlotMeta {
   uint8_t* dst;    // destination of the slot's first payload byte
   uint32_t len;    // payload bytes in the slot; 0 = no more stages
@@ -577,23 +581,18 @@ struct SlotMeta {
 };
 
 template <int DIR>
-__global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg* __restrict__ segs,
-                                                                   const uint32_t* __restrict__ tile_begin, uint32_t nseg,
-                                                                   uint32_t ntiles, uint8_t* __restrict__ image,
-                                                                   int32_t* __restrict__ status) {
-  extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
-  __shared__ __align__(8) uint64_t full[mlf::kStages];
-  __shared__ SlotMeta meta[mlf::kStages];
-  __shared__ int abort_flag;
+__device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs, const uint32_t* __restrict__ tile_begin,
+                                                    uint32_t nseg, uint32_t nlinear, uint8_t* __restrict__ image,
+                                                    int32_t* __restrict__ status, uint8_t* ring, uint64_t* full, SlotMeta* meta,
+                                                    int* abort_flag) {
   const unsigned tid = threadIdx.x;
-
   // producer state (thread 0 only)
   uint32_t p_tile = blockIdx.x, p_stage = 0, issued = 0;
   bool p_finished = false;
   LinearTile p_lt;
   p_lt.nstage = 0;
-  auto seek = [&]() {  // loads the span of tile p_tile (every tile of such a plan is linear)
-    if (p_tile < ntiles) {
+  auto seek = [&]() {  // loads the span of tile p_tile
+    if (p_tile < nlinear) {
       const uint32_t sg = find_segment(tile_begin, nseg, p_tile);
       (void)linear_span<DIR>(segs[sg], p_tile - tile_begin[sg], image, &p_lt);
     }
@@ -602,7 +601,7 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg*
   auto top_up = [&](uint32_t consumed) {
     while (issued < consumed + mlf::kStages && !p_finished) {
       const uint32_t slot = issued % mlf::kStages;
-      if (p_tile >= ntiles) {
+      if (p_tile >= nlinear) {
         meta[slot].len = 0;
         p_finished = true;
         ++issued;
@@ -630,7 +629,7 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg*
   if (tid == 0) {
     for (uint32_t k = 0; k < mlf::kStages; ++k) mlf::mbar_init(&full[k], 1);
     mlf::mbar_init_fence();
-    abort_flag = 0;
+    *abort_flag = 0;
     seek();
     top_up(0);
   }
@@ -648,11 +647,11 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg*
     if (ok) {
       mlf::drain_slot(m.dst, ring + (size_t)slot * mlf::kSlotBytes, m.shift, m.len, tid, blockDim.x);
     } else {
-      abort_flag = 1;
+      *abort_flag = 1;
     }
     __syncthreads();  // the slot is free again; also publishes abort_flag
     ++consumed;
-    if (abort_flag) {
+    if (*abort_flag) {
       aborted = true;
       break;
     }
@@ -666,107 +665,53 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg*
     for (uint32_t n = consumed - 1; n < loads_issued; ++n)  // from the stage whose wait ran out
       (void)mlf::mbar_wait_bounded(&full[n % mlf::kStages], (n / mlf::kStages) & 1u);
   }
+  return !aborted;
 }
 
-// STAGED = false is the instance for plans made of linear tiles only (every contiguous state dict):
-// it carries none of the staged-tile code, which keeps the streaming loop at its leanest.
-template <int DIR, bool STAGED>
+// Plans made of linear tiles only (every contiguous state dict): the streaming phase is the kernel.
+template <int DIR>
+__global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg* __restrict__ segs,
+                                                                   const uint32_t* __restrict__ tile_begin, uint32_t nseg,
+                                                                   uint32_t nlinear, uint32_t ntiles, uint8_t* __restrict__ image,
+                                                                   int32_t* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
+  __shared__ __align__(8) uint64_t full[mlf::kStages];
+  __shared__ SlotMeta meta[mlf::kStages];
+  __shared__ int abort_flag;
+  (void)ntiles;
+  (void)stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, full, meta, &abort_flag);
+}
+
+// Plans that also hold staged tiles: the streaming phase over the linear tiles, then this CTA's
+// share of the staged tiles, each found in the plan tables by all threads.
+template <int DIR>
 __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* __restrict__ segs,
                                                                  const uint32_t* __restrict__ tile_begin, uint32_t nseg,
-                                                                 uint32_t ntiles, uint8_t* __restrict__ image,
+                                                                 uint32_t nlinear, uint32_t ntiles, uint8_t* __restrict__ image,
                                                                  int32_t* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
   __shared__ __align__(8) uint64_t full[mlf::kStages];
+  __shared__ SlotMeta meta[mlf::kStages];
   __shared__ int abort_flag;
+  __shared__ __align__(16) uint8_t tsmem[kTransSmemBytes];
+  __shared__ Seg g;
+  if (!stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, full, meta, &abort_flag)) return;
   const unsigned tid = threadIdx.x;
-
-  if (tid == 0) {
-    for (uint32_t k = 0; k < mlf::kStages; ++k) mlf::mbar_init(&full[k], 1);
-    mlf::mbar_init_fence();
-    abort_flag = 0;
-  }
-  __syncthreads();
-
-  // producer cursor (thread 0): the next stage to load, always ahead of the consumers
-  uint32_t p_tile = blockIdx.x, p_stage = 0, issued = 0;
-  LinearTile p_lt;
-  p_lt.nstage = 0;
-  auto seek = [&]() {  // moves p_tile to the next linear tile of this CTA's sequence
-    while (p_tile < ntiles) {
-      const uint32_t sg = find_segment(tile_begin, nseg, p_tile);
-      if (linear_span<DIR>(segs[sg], p_tile - tile_begin[sg], image, &p_lt)) return;
-      p_tile += gridDim.x;
-    }
-  };
-  if (tid == 0) seek();
-
-  uint32_t consumed = 0;
   uint32_t cached = 0xffffffffu;
-  bool aborted = false;
-  for (uint32_t tile = blockIdx.x; tile < ntiles && !aborted; tile += gridDim.x) {
+  // this CTA's staged tiles: the same stride as before, continued behind the linear tiles
+  const uint32_t first = nlinear + (blockIdx.x + gridDim.x - nlinear % gridDim.x) % gridDim.x;
+  for (uint32_t tile = first; tile < ntiles; tile += gridDim.x) {
     const uint32_t sg = find_segment(tile_begin, nseg, tile);
     const uint32_t local = tile - tile_begin[sg];
-    LinearTile lt;
-    if (linear_span<DIR>(segs[sg], local, image, &lt)) {
-      for (uint32_t st = 0; st < lt.nstage; ++st) {
-        if (tid == 0) {
-          // keep the ring full: slot (issued % kStages) was released by the barrier that ended
-          // stage (issued - kStages)
-          while (issued < consumed + mlf::kStages && p_tile < ntiles) {
-            const uint64_t off = (uint64_t)p_stage * mlf::kStageBytes;
-            const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, p_lt.len - off);
-            const uint8_t* src = p_lt.src + off;
-            const uint32_t shift = (uint32_t)((uintptr_t)src & 15u);
-            const uint32_t bytes = (shift + slen + 15u) & ~15u;
-            const uint32_t slot = issued % mlf::kStages;
-            mlf::mbar_expect_tx(&full[slot], bytes);
-            mlf::bulk_load(ring + (size_t)slot * mlf::kSlotBytes, src - shift, bytes, &full[slot]);
-            ++issued;
-            if (++p_stage == p_lt.nstage) {
-              p_stage = 0;
-              p_tile += gridDim.x;
-              seek();
-            }
-          }
-        }
-        const uint32_t slot = consumed % mlf::kStages;
-        const bool ok = mlf::mbar_wait_bounded(&full[slot], (consumed / mlf::kStages) & 1u);
-        if (ok) {
-          const uint64_t off = (uint64_t)st * mlf::kStageBytes;
-          const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, lt.len - off);
-          const uint32_t shift = (uint32_t)((uintptr_t)(lt.src + off) & 15u);
-          mlf::drain_slot(lt.dst + off, ring + (size_t)slot * mlf::kSlotBytes, shift, slen, tid, blockDim.x);
-        } else {
-          abort_flag = 1;
-        }
-        __syncthreads();  // slot is free again; also publishes abort_flag
-        ++consumed;
-        if (abort_flag) {
-          aborted = true;
-          break;
-        }
-      }
-      continue;
+    if (sg != cached) {
+      __syncthreads();
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + sg);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
+      for (uint32_t w = tid; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
+      __syncthreads();
+      cached = sg;
     }
-    if constexpr (STAGED) {
-      __shared__ __align__(16) uint8_t tsmem[kTransSmemBytes];
-      __shared__ Seg g;
-      if (sg != cached) {
-        __syncthreads();
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + sg);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
-        for (uint32_t w = tid; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
-        __syncthreads();
-        cached = sg;
-      }
-      staged_tile<DIR>(g, local, image, tsmem);
-    }
-  }
-  if (aborted && tid == 0) {
-    atomicCAS(status, 0, MLF_ERR_TIMEOUT);
-    // the CTA may not exit while bulk copies still target its shared memory: wait for them too,
-    // again with a budget
-    for (uint32_t n = consumed; n < issued; ++n) (void)mlf::mbar_wait_bounded(&full[n % mlf::kStages], (n / mlf::kStages) & 1u);
+    staged_tile<DIR>(g, local, image, tsmem);
   }
 }
 
@@ -1009,7 +954,7 @@ struct mlf_plan {
   uint32_t ntiles = 0;
   uint64_t extent = 0;
   uint64_t payload = 0;
-  bool staged = false;  // some tile is not a linear run (short rows, transposed, generic)
+  uint32_t nlinear = 0;  // tiles [0, nlinear) are linear runs, the rest are staged tiles
   Seg* d_segs = nullptr;
   uint32_t* d_tile_begin = nullptr;
   int32_t* d_status = nullptr;
@@ -1024,12 +969,11 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   if (direction != MLF_PACK && direction != MLF_UNPACK)
     return mlf::fail(MLF_ERR_INVALID, "mlf_plan_create: direction must be MLF_PACK or MLF_UNPACK");
 
-  std::vector<Seg> segs;
-  std::vector<uint32_t> tile_begin;
-  segs.reserve(n);
-  tile_begin.reserve(n + 1);
+  // Segments in table order: those made of linear tiles first, so that tiles [0, nlinear) are the
+  // linear ones (a segment carries its own addresses, so the table order is free).
+  std::vector<Seg> linear_segs, staged_segs;
+  std::vector<uint64_t> linear_tiles, staged_tiles;
   uint64_t tiles = 0, extent = 0, payload = 0;
-  bool staged = false;
 
   for (uint64_t i = 0; i < n; ++i) {
     Seg g;
@@ -1040,15 +984,29 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
     payload += seg_payload;
     extent = std::max(extent, seg_extent);
     if (tiles + ntile > 0xfffffff0ull) return mlf::fail(MLF_ERR_TOO_LARGE, "plan has too many tiles");
-    tile_begin.push_back((uint32_t)tiles);
-    segs.push_back(g);
     tiles += ntile;
-    if (!(g.kind == kFlat || (g.kind == kRows && g.b == 0))) staged = true;
+    const bool linear = g.kind == kFlat || (g.kind == kRows && g.b == 0);
+    (linear ? linear_segs : staged_segs).push_back(g);
+    (linear ? linear_tiles : staged_tiles).push_back(ntile);
   }
-  tile_begin.push_back((uint32_t)tiles);
+  std::vector<Seg> segs(linear_segs);
+  segs.insert(segs.end(), staged_segs.begin(), staged_segs.end());
+  std::vector<uint32_t> tile_begin;
+  tile_begin.reserve(segs.size() + 1);
+  uint64_t at = 0, nlinear = 0;
+  for (uint64_t ntile : linear_tiles) {
+    tile_begin.push_back((uint32_t)at);
+    at += ntile;
+  }
+  nlinear = at;
+  for (uint64_t ntile : staged_tiles) {
+    tile_begin.push_back((uint32_t)at);
+    at += ntile;
+  }
+  tile_begin.push_back((uint32_t)at);
 
   mlf_plan* p = new mlf_plan();
-  p->staged = staged;
+  p->nlinear = (uint32_t)nlinear;
   p->direction = direction;
   p->nseg = (uint32_t)segs.size();
   p->ntiles = (uint32_t)tiles;
@@ -1096,10 +1054,10 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t* image = static_cast<uint8_t*>(image_base);
   if (use_bulk_kernel()) {
-    using BulkKernel = void (*)(const Seg*, const uint32_t*, uint32_t, uint32_t, uint8_t*, int32_t*);
+    using BulkKernel = void (*)(const Seg*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint8_t*, int32_t*);
     static const BulkKernel kernels[2][2] = {
-        {mlf_plan_kernel_stream<MLF_PACK>, mlf_plan_kernel_bulk<MLF_PACK, true>},
-        {mlf_plan_kernel_stream<MLF_UNPACK>, mlf_plan_kernel_bulk<MLF_UNPACK, true>},
+        {mlf_plan_kernel_stream<MLF_PACK>, mlf_plan_kernel_bulk<MLF_PACK>},
+        {mlf_plan_kernel_stream<MLF_UNPACK>, mlf_plan_kernel_bulk<MLF_UNPACK>},
     };
     static std::once_flag opted_in;
     static cudaError_t opt_status = cudaSuccess;
@@ -1109,10 +1067,11 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
           opt_status = cudaFuncSetAttribute(kernels[d][v], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
     });
     MLF_CUDA(opt_status);
-    const BulkKernel kernel = kernels[p->direction == MLF_PACK ? 0 : 1][p->staged ? 1 : 0];
+    const bool staged = p->nlinear < p->ntiles;
+    const BulkKernel kernel = kernels[p->direction == MLF_PACK ? 0 : 1][staged ? 1 : 0];
     const int32_t rc = wave_grid(kernel, max_ctas, p->ntiles, &grid, kBulkDynSmem);
     if (rc != MLF_OK) return rc;
-    kernel<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->ntiles, image, p->d_status);
+    kernel<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->nlinear, p->ntiles, image, p->d_status);
   } else {
     int32_t rc = p->direction == MLF_PACK ? wave_grid(mlf_plan_kernel<MLF_PACK>, max_ctas, p->ntiles, &grid)
                                           : wave_grid(mlf_plan_kernel<MLF_UNPACK>, max_ctas, p->ntiles, &grid);
