@@ -669,8 +669,11 @@ __device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs
 }
 
 // Plans made of linear tiles only (every contiguous state dict): the streaming phase is the kernel.
+#ifndef MLF_STREAM_MIN_CTAS
+#define MLF_STREAM_MIN_CTAS 3
+#endif
 template <int DIR>
-__global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_stream(const Seg* __restrict__ segs,
+__global__ void __launch_bounds__(kThreads, MLF_STREAM_MIN_CTAS) mlf_plan_kernel_stream(const Seg* __restrict__ segs,
                                                                    const uint32_t* __restrict__ tile_begin, uint32_t nseg,
                                                                    uint32_t nlinear, uint32_t ntiles, uint8_t* __restrict__ image,
                                                                    int32_t* __restrict__ status) {
