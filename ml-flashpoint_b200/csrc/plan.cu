@@ -27,7 +27,10 @@ namespace {
 
 constexpr uint32_t kThreads = 256;
 constexpr uint64_t kTileBytes = 64 * 1024;    // FLAT tile and ROWS chunk
-constexpr uint64_t kRowSplitBytes = 16 * 1024;  // rows at least this long are cut into chunks
+#ifndef MLF_ROW_SPLIT_KIB
+#define MLF_ROW_SPLIT_KIB 5
+#endif
+constexpr uint64_t kRowSplitBytes = MLF_ROW_SPLIT_KIB * 1024;  // rows at least this long are linear tiles (cut into 64 KiB chunks)
 constexpr int kTransCols = 32;                // TRANSPOSE tile: elements along the tensor-contiguous dim
 constexpr int kTransSmemBytes = 32 * 264 + 16;  // 32 rows at the widest pitch + slack for vector reads
 constexpr uint64_t kGenericTile = 4096;       // GENERIC elements per tile
