@@ -148,6 +148,12 @@ int32_t mlf_plan_status(mlf_plan* p);
 int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_base, uint64_t image_capacity, void* stream);
 /* Kernel launches issued by this library since load (for launch accounting in benchmarks). */
 uint64_t mlf_launch_count(void);
+/* Self-test of the kernels' bounded waits (no counterpart in the reference implementation): one
+ * thread waits on a barrier that nothing will complete, gives up after `budget_ns` (at most 100 ms)
+ * and records MLF_ERR_TIMEOUT in a status word, exactly as the plan kernels do when a bulk copy
+ * does not arrive. Returns MLF_ERR_TIMEOUT when the wait gave up as designed, MLF_OK if it did
+ * not. Blocking; the context stays usable afterwards. */
+int32_t mlf_selftest_wait_timeout(uint64_t budget_ns, void* stream);
 
 /* ------------------------------------------------------------------ bulk movers
  * Replace the byte movers around the object: the staging copy

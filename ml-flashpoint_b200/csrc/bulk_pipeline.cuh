@@ -60,14 +60,14 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 // Waits for the phase with the given parity. Returns false if the time budget ran out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t start = global_ns();
   for (;;) {
 #pragma unroll 1
     for (int spin = 0; spin < 64; ++spin)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - start > kWaitBudgetNs) return false;
+    if (global_ns() - start > budget_ns) return false;
   }
 }
 // Global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned),

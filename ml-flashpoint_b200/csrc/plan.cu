@@ -721,6 +721,17 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* _
   }
 }
 
+// Self-test of the bounded wait: a barrier that nothing will ever complete. The wait has to give
+// up after `budget_ns` and report it through the status word, like the streaming phase does.
+__global__ void mlf_wait_selftest_kernel(uint64_t budget_ns, int32_t* __restrict__ status) {
+  __shared__ __align__(8) uint64_t never;
+  if (threadIdx.x == 0) {
+    mlf::mbar_init(&never, 1);
+    mlf::mbar_init_fence();
+    if (!mlf::mbar_wait_bounded(&never, 0, budget_ns)) atomicCAS(status, 0, MLF_ERR_TIMEOUT);
+  }
+}
+
 constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
@@ -1159,6 +1170,27 @@ int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_bas
   mlf_plan_kernel<MLF_PACK><<<grid, kThreads, 0, s>>>(d_segs, d_tiles, nseg, (uint32_t)tiles, static_cast<uint8_t*>(image_base));
   MLF_CUDA(cudaGetLastError());
   mlf::g_launches.fetch_add(1);
+  return MLF_OK;
+}
+
+int32_t mlf_selftest_wait_timeout(uint64_t budget_ns, void* stream) {
+  if (budget_ns == 0 || budget_ns > 100000000ull)
+    return mlf::fail(MLF_ERR_INVALID, "mlf_selftest_wait_timeout: budget must be between 1 ns and 100 ms");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t* d_status = nullptr;
+  MLF_CUDA(cudaMalloc(&d_status, sizeof(int32_t)));
+  cudaError_t e = cudaMemsetAsync(d_status, 0, sizeof(int32_t), s);
+  int32_t recorded = 0;
+  if (e == cudaSuccess) {
+    mlf_wait_selftest_kernel<<<1, 32, 0, s>>>(budget_ns, d_status);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&recorded, d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(d_status);
+  if (e != cudaSuccess) return mlf::cuda_fail(e, "mlf_selftest_wait_timeout");
+  mlf::g_launches.fetch_add(1);
+  if (recorded == MLF_ERR_TIMEOUT) return mlf::fail(MLF_ERR_TIMEOUT, "bounded device-side wait gave up after its budget (as this self-test expects)");
   return MLF_OK;
 }
 

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "mlf_last_error": (c_char_p, []),
     "mlf_version": (c_char_p, []),
     "mlf_launch_count": (c_uint64, []),
+    "mlf_selftest_wait_timeout": (c_int32, [c_uint64, c_void_p]),
     "mlf_buf_create": (c_int32, [c_char_p, c_uint64, c_int32, POINTER(c_void_p)]),
     "mlf_buf_open_ro": (c_int32, [c_char_p, POINTER(c_void_p)]),
     "mlf_buf_resize": (c_int32, [c_void_p, c_uint64]),

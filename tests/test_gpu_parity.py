@@ -173,6 +173,31 @@ def test_flat_copy_every_misalignment_and_small_size():
             assert torch.equal(out, expect), (so, do)  # also proves nothing outside the spans was touched
 
 
+def test_bounded_device_wait_gives_up_and_reports_through_the_status_word():
+    """The kernels' waits are bounded: a wait on a barrier that nothing completes returns after its
+    budget, the kernel records MLF_ERR_TIMEOUT and exits, and the context stays usable."""
+    import time
+
+    from ml_flashpoint import _native
+
+    lib = _native.lib()
+    t0 = time.perf_counter()
+    rc = lib.mlf_selftest_wait_timeout(2_000_000, None)  # 2 ms budget
+    elapsed = time.perf_counter() - t0
+    assert rc == _native.MLF_ERR_TIMEOUT
+    assert b"gave up" in lib.mlf_last_error()
+    assert elapsed < 1.0
+    with pytest.raises(_native.NativeError) as refused:
+        _native.check(lib.mlf_selftest_wait_timeout(10**9, None))  # budgets above 100 ms are refused
+    assert refused.value.code == _native.MLF_ERR_INVALID
+    # the context is intact: an ordinary copy still works
+    src = torch.arange(100000, dtype=torch.int32, device="cuda")
+    dst = torch.zeros_like(src)
+    _flat_copy(dst.data_ptr(), src.data_ptr(), src.numel() * 4)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src)
+
+
 def test_plan_rejects_out_of_window_launch(engine):
     from ml_flashpoint import _native
 
