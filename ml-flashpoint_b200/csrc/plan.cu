@@ -28,7 +28,7 @@ namespace {
 constexpr uint32_t kThreads = 256;
 constexpr uint64_t kTileBytes = 64 * 1024;    // FLAT tile and ROWS chunk
 #ifndef MLF_ROW_SPLIT_KIB
-#define MLF_ROW_SPLIT_KIB 5
+#define MLF_ROW_SPLIT_KIB 8
 #endif
 constexpr uint64_t kRowSplitBytes = MLF_ROW_SPLIT_KIB * 1024;  // rows at least this long are linear tiles (cut into 64 KiB chunks)
 constexpr int kTransCols = 32;                // TRANSPOSE tile: elements along the tensor-contiguous dim
@@ -514,17 +514,31 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
 // Same tiles, same bytes. Linear tiles (FLAT, and chunks of long ROWS) stream through the
 // shared-memory ring of bulk_pipeline.cuh; the other kinds run exactly as in mlf_plan_kernel.
 
+// One tile of the streaming phase: a single contiguous run (rows == 0), or `rows` whole short rows
+// of segment `seg` starting at flattened row number `first_row`, each `len` bytes.
 struct LinearTile {
   const uint8_t* src;
   uint8_t* dst;
   uint64_t len;
   uint32_t nstage;
+  uint32_t rows;            // 0: one run; otherwise the number of rows in this tile
+  uint32_t rows_per_stage;  // short rows: how many share one ring slot
+  uint32_t pitch;           // short rows: bytes between rows inside a slot
+  uint64_t first_row;
+  const Seg* seg;
 };
 
-// Span of tile `local` of segment g if the tile is one contiguous run on both sides.
+constexpr uint32_t kMaxStageRows = 32;  // one producer lane per row
+
+// Slot pitch of short rows: room for the row behind a source shift of up to 15 bytes, rounded to
+// whole granules, plus the granule the shifted drain reads ahead.
+__device__ __host__ __forceinline__ uint32_t short_row_pitch(uint32_t row_bytes) { return ((row_bytes + 30u) & ~15u) + 16u; }
+
+// Span of tile `local` of segment g if the tile belongs to the streaming phase.
 template <int DIR>
 __device__ __forceinline__ bool linear_span(const Seg& g, uint32_t local, uint8_t* image, LinearTile* out) {
   uint64_t toff, ioff, len;
+  out->rows = 0;
   if (g.kind == kFlat) {
     const uint64_t lo_edge = (uint64_t)local * kTileBytes;
     const uint64_t off = lo_edge > g.b ? lo_edge - g.b : 0;
@@ -545,6 +559,21 @@ __device__ __forceinline__ bool linear_span(const Seg& g, uint32_t local, uint8_
     len = min(kTileBytes, g.a - off);
     toff = (uint64_t)t + off;
     ioff = (uint64_t)i + off;
+  } else if (g.kind == kRows) {
+    // short rows: g.b of them per tile, several per ring slot
+    uint64_t nrows = 1;
+    for (int d = 0; d < (int)g.ndim - 1; ++d) nrows *= (uint64_t)g.shape[d];
+    const uint64_t r0 = (uint64_t)local * g.b;
+    out->first_row = r0;
+    out->rows = (uint32_t)min((uint64_t)g.b, nrows - r0);
+    out->pitch = short_row_pitch((uint32_t)g.a);
+    out->rows_per_stage = min(kMaxStageRows, mlf::kStageBytes / out->pitch);
+    out->len = g.a;
+    out->nstage = (out->rows + out->rows_per_stage - 1) / out->rows_per_stage;
+    out->seg = &g;
+    out->src = nullptr;
+    out->dst = nullptr;
+    return true;
   } else {
     return false;
   }
@@ -578,22 +607,33 @@ __device__ __forceinline__ uint32_t find_segment(const uint32_t* __restrict__ ti
 // A slot whose published length is 0 ends the phase. Returns false if a bounded wait ran out
 // (status recorded, outstanding copies awaited): the CTA must then return.
 struct SlotMeta {
-  uint8_t* dst;    // destination of the slot's first payload byte
-  uint32_t len;    // payload bytes in the slot; 0 = no more stages
-  uint32_t shift;  // the payload starts this many bytes into the slot (source misalignment)
+  uint8_t* dst;    // one run: destination of the slot's first payload byte
+  uint32_t len;    // payload bytes of the run, or of each row; 0 = no more stages
+  uint32_t shift;  // one run: the payload starts this many bytes into the slot (source misalignment)
+  uint32_t rows;   // 0: the slot holds one run; otherwise this many short rows, `pitch` bytes apart
+  uint32_t pitch;
+};
+
+// Shared memory of the streaming phase besides the ring itself.
+struct StreamShared {
+  uint64_t full[mlf::kStages];  // one mbarrier per slot
+  SlotMeta meta[mlf::kStages];
+  uint8_t* row_dst[mlf::kStages][kMaxStageRows];  // short rows: where each row of the slot goes
+  uint8_t row_shift[mlf::kStages][kMaxStageRows];
+  int abort_flag;
 };
 
 template <int DIR>
 __device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs, const uint32_t* __restrict__ tile_begin,
                                                     uint32_t nseg, uint32_t nlinear, uint8_t* __restrict__ image,
-                                                    int32_t* __restrict__ status, uint8_t* ring, uint64_t* full, SlotMeta* meta,
-                                                    int* abort_flag) {
-  const unsigned tid = threadIdx.x;
-  // producer state (thread 0 only)
+                                                    int32_t* __restrict__ status, uint8_t* ring, StreamShared* sh) {
+  const unsigned tid = threadIdx.x, lane = tid & 31u;
+  // producer state, kept identically by all lanes of warp 0
   uint32_t p_tile = blockIdx.x, p_stage = 0, issued = 0;
   bool p_finished = false;
   LinearTile p_lt;
   p_lt.nstage = 0;
+  p_lt.rows = 0;
   auto seek = [&]() {  // loads the span of tile p_tile
     if (p_tile < nlinear) {
       const uint32_t sg = find_segment(tile_begin, nseg, p_tile);
@@ -601,25 +641,68 @@ __device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs
     }
   };
   // Fills every free slot: slot (issued % kStages) is free once stage (issued - kStages) was drained.
+  // Runs on warp 0 with all lanes: lane 0 issues the load of a run, lane r the load of a slot's row r.
   auto top_up = [&](uint32_t consumed) {
     while (issued < consumed + mlf::kStages && !p_finished) {
       const uint32_t slot = issued % mlf::kStages;
+      uint8_t* slot_base = ring + (size_t)slot * mlf::kSlotBytes;
       if (p_tile >= nlinear) {
-        meta[slot].len = 0;
+        if (lane == 0) sh->meta[slot].len = 0;
         p_finished = true;
         ++issued;
         break;
       }
-      const uint64_t off = (uint64_t)p_stage * mlf::kStageBytes;
-      const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, p_lt.len - off);
-      const uint8_t* src = p_lt.src + off;
-      const uint32_t shift = (uint32_t)((uintptr_t)src & 15u);
-      const uint32_t bytes = (shift + slen + 15u) & ~15u;
-      meta[slot].dst = p_lt.dst + off;
-      meta[slot].len = slen;
-      meta[slot].shift = shift;
-      mlf::mbar_expect_tx(&full[slot], bytes);
-      mlf::bulk_load(ring + (size_t)slot * mlf::kSlotBytes, src - shift, bytes, &full[slot]);
+      if (p_lt.rows == 0) {
+        if (lane == 0) {
+          const uint64_t off = (uint64_t)p_stage * mlf::kStageBytes;
+          const uint32_t slen = (uint32_t)min((uint64_t)mlf::kStageBytes, p_lt.len - off);
+          const uint8_t* src = p_lt.src + off;
+          const uint32_t shift = (uint32_t)((uintptr_t)src & 15u);
+          const uint32_t bytes = (shift + slen + 15u) & ~15u;
+          sh->meta[slot].dst = p_lt.dst + off;
+          sh->meta[slot].len = slen;
+          sh->meta[slot].shift = shift;
+          sh->meta[slot].rows = 0;
+          mlf::mbar_expect_tx(&sh->full[slot], bytes);
+          mlf::bulk_load(slot_base, src - shift, bytes, &sh->full[slot]);
+        }
+      } else {
+        const Seg& g = *p_lt.seg;
+        const uint32_t r_in_tile = p_stage * p_lt.rows_per_stage;
+        const uint32_t n = min(p_lt.rows_per_stage, p_lt.rows - r_in_tile);
+        const uint8_t* src = nullptr;
+        uint32_t shift = 0, bytes = 0;
+        if (lane < n) {
+          uint64_t row = p_lt.first_row + r_in_tile + lane;
+          int64_t t = 0, i = 0;
+          for (int d = (int)g.ndim - 2; d >= 0; --d) {
+            const int64_t idx = (int64_t)(row % (uint64_t)g.shape[d]);
+            row /= (uint64_t)g.shape[d];
+            t += idx * g.tstride[d];
+            i += idx * g.istride[d];
+          }
+          uint8_t* tp = reinterpret_cast<uint8_t*>(g.tensor) + t;
+          uint8_t* ip = image + g.image_off + i;
+          src = DIR == MLF_PACK ? tp : ip;
+          shift = (uint32_t)((uintptr_t)src & 15u);
+          bytes = (shift + (uint32_t)p_lt.len + 15u) & ~15u;
+          sh->row_dst[slot][lane] = DIR == MLF_PACK ? ip : tp;
+          sh->row_shift[slot][lane] = (uint8_t)shift;
+        }
+        uint32_t total = bytes;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (lane == 0) {
+          sh->meta[slot].dst = nullptr;
+          sh->meta[slot].len = (uint32_t)p_lt.len;
+          sh->meta[slot].shift = 0;
+          sh->meta[slot].rows = n;
+          sh->meta[slot].pitch = p_lt.pitch;
+          mlf::mbar_expect_tx(&sh->full[slot], total);
+        }
+        __syncwarp();
+        if (lane < n) mlf::bulk_load(slot_base + (size_t)lane * p_lt.pitch, src - shift, bytes, &sh->full[slot]);
+      }
       ++issued;
       if (++p_stage == p_lt.nstage) {
         p_stage = 0;
@@ -630,9 +713,12 @@ __device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs
   };
 
   if (tid == 0) {
-    for (uint32_t k = 0; k < mlf::kStages; ++k) mlf::mbar_init(&full[k], 1);
+    for (uint32_t k = 0; k < mlf::kStages; ++k) mlf::mbar_init(&sh->full[k], 1);
     mlf::mbar_init_fence();
-    *abort_flag = 0;
+    sh->abort_flag = 0;
+  }
+  __syncthreads();
+  if (tid < 32) {
     seek();
     top_up(0);
   }
@@ -642,23 +728,29 @@ __device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs
   bool aborted = false;
   for (;;) {
     const uint32_t slot = consumed % mlf::kStages;
-    // written by thread 0 at least one barrier ago: stage `consumed` was issued before the barrier
+    // written by warp 0 at least one barrier ago: stage `consumed` was issued before the barrier
     // that ended stage `consumed - 1` (or before the barrier above)
-    const SlotMeta m = meta[slot];
+    const SlotMeta m = sh->meta[slot];
     if (m.len == 0) break;
-    const bool ok = mlf::mbar_wait_bounded(&full[slot], (consumed / mlf::kStages) & 1u);
+    const bool ok = mlf::mbar_wait_bounded(&sh->full[slot], (consumed / mlf::kStages) & 1u);
     if (ok) {
-      mlf::drain_slot(m.dst, ring + (size_t)slot * mlf::kSlotBytes, m.shift, m.len, tid, blockDim.x);
+      const uint8_t* slot_base = ring + (size_t)slot * mlf::kSlotBytes;
+      if (m.rows == 0) {
+        mlf::drain_slot(m.dst, slot_base, m.shift, m.len, tid, blockDim.x);
+      } else {
+        for (uint32_t r = tid >> 5; r < m.rows; r += blockDim.x >> 5)
+          mlf::drain_slot(sh->row_dst[slot][r], slot_base + (size_t)r * m.pitch, sh->row_shift[slot][r], m.len, lane, 32);
+      }
     } else {
-      *abort_flag = 1;
+      sh->abort_flag = 1;
     }
     __syncthreads();  // the slot is free again; also publishes abort_flag
     ++consumed;
-    if (*abort_flag) {
+    if (sh->abort_flag) {
       aborted = true;
       break;
     }
-    if (tid == 0) top_up(consumed);  // refills the slot just freed; its destination is published by the next barrier
+    if (tid < 32) top_up(consumed);  // refills the slot just freed; its destination is published by the next barrier
   }
   if (aborted && tid == 0) {
     atomicCAS(status, 0, MLF_ERR_TIMEOUT);
@@ -666,7 +758,7 @@ __device__ __forceinline__ bool stream_linear_tiles(const Seg* __restrict__ segs
     // again with a budget (the end marker, if one was written, took a slot number but no load)
     const uint32_t loads_issued = issued - (p_finished ? 1u : 0u);
     for (uint32_t n = consumed - 1; n < loads_issued; ++n)  // from the stage whose wait ran out
-      (void)mlf::mbar_wait_bounded(&full[n % mlf::kStages], (n / mlf::kStages) & 1u);
+      (void)mlf::mbar_wait_bounded(&sh->full[n % mlf::kStages], (n / mlf::kStages) & 1u);
   }
   return !aborted;
 }
@@ -681,11 +773,9 @@ __global__ void __launch_bounds__(kThreads, MLF_STREAM_MIN_CTAS) mlf_plan_kernel
                                                                    uint32_t nlinear, uint32_t ntiles, uint8_t* __restrict__ image,
                                                                    int32_t* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
-  __shared__ __align__(8) uint64_t full[mlf::kStages];
-  __shared__ SlotMeta meta[mlf::kStages];
-  __shared__ int abort_flag;
+  __shared__ __align__(16) StreamShared shared;
   (void)ntiles;
-  (void)stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, full, meta, &abort_flag);
+  (void)stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, &shared);
 }
 
 // Plans that also hold staged tiles: the streaming phase over the linear tiles, then this CTA's
@@ -696,12 +786,10 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* _
                                                                  uint32_t nlinear, uint32_t ntiles, uint8_t* __restrict__ image,
                                                                  int32_t* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t ring[];  // kStages slots of kSlotBytes
-  __shared__ __align__(8) uint64_t full[mlf::kStages];
-  __shared__ SlotMeta meta[mlf::kStages];
-  __shared__ int abort_flag;
+  __shared__ __align__(16) StreamShared shared;
   __shared__ __align__(16) uint8_t tsmem[kTransSmemBytes];
   __shared__ Seg g;
-  if (!stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, full, meta, &abort_flag)) return;
+  if (!stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, &shared)) return;
   const unsigned tid = threadIdx.x;
   uint32_t cached = 0xffffffffu;
   // this CTA's staged tiles: the same stride as before, continued behind the linear tiles
@@ -1002,7 +1090,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
     extent = std::max(extent, seg_extent);
     if (tiles + ntile > 0xfffffff0ull) return mlf::fail(MLF_ERR_TOO_LARGE, "plan has too many tiles");
     tiles += ntile;
-    const bool linear = g.kind == kFlat || (g.kind == kRows && g.b == 0);
+    const bool linear = g.kind == kFlat || g.kind == kRows;  // everything the streaming phase moves
     (linear ? linear_segs : staged_segs).push_back(g);
     (linear ? linear_tiles : staged_tiles).push_back(ntile);
   }
