@@ -5,12 +5,15 @@
 // kernel per object: CTAs stride over the tiles, find the owning segment with a binary search
 // over the tile prefix, and move that tile. Four segment kinds exist:
 //   FLAT       both sides contiguous: 64 KiB byte runs, destination-aligned 16-byte vectors
-//   ROWS       innermost dimension contiguous on both sides: runs per row (or per row chunk)
+//   ROWS       innermost dimension contiguous on both sides: runs per row (or per row chunk); short
+//              rows share a ring slot, one bulk load each
 //   TRANSPOSE  the tensor's unit-stride dimension is not the image's: sub-tiles of 32 elements by 256
 //              bytes through shared memory so both sides are touched along their contiguous direction,
 //              the loads of one sub-tile in flight while the previous one is written out
 //   GENERIC    anything else (stepped slices, expands): one element per thread
-// The image side has byte alignment only, because the object format is unpadded.
+// FLAT and ROWS tiles stream through a shared-memory ring fed by bulk copies (the streaming phase);
+// the table lists their segments first. The image side has byte alignment only, because the object
+// format is unpadded.
 #include <stdlib.h>
 #include <string.h>
 
