@@ -749,8 +749,7 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
 
     cpu = None
     if rank == 0 and world_size == 1 and not args.no_cpu_baseline:
-        del engine._staging
-        engine._staging = None
+        engine.release_device_memory()  # the CPU baseline stages from the same tensors; free the image arena first
         cpu = run_cpu_baseline(shard, workdir, int(args.cpu_sample_gb * 1e9), passes=3)
 
     if rank != 0:

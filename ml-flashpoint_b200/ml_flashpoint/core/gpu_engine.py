@@ -365,6 +365,19 @@ class CudaCopyEngine:
         self._cursor = 0
         return self._arena[:nbytes]
 
+    def release_device_memory(self) -> None:
+        """Gives the HBM arena back to the allocator (after the transfers out of it have finished);
+        the next save or restore allocates a new one."""
+        with self._lock:
+            if self._active_read is not None:
+                self._active_read.wait()
+                self._active_read = None
+            for image in self._images:
+                image.done.synchronize()
+            self._images = []
+            self._cursor = 0
+            self._arena = None
+
     def drop_resident_images(self) -> None:
         """Forgets the object images kept in HBM after their saves (they stay valid until reused)."""
         with self._lock:
