@@ -372,6 +372,7 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
     def _announce_save(self, write_buckets: list[ObjectWriteBucket]) -> None:
         """Plans every bucket's layout once and tells the engine how much HBM the images of this save
         take together, so that no bucket's pack kernel has to wait for another bucket's transfer."""
+        self._layouts.clear()  # entries of a save that failed before consuming them would pin its tensors
         if not write_buckets:
             return
         total = 0
