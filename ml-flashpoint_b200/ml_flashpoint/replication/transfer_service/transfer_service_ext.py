@@ -158,6 +158,7 @@ class TransferService:
         self._pending: Dict[str, concurrent.futures.Future] = {}
         self._inbound: Dict[int, _DeviceBuffer] = {}  # per source rank
         self._inbound_locks: Dict[int, threading.Lock] = {}
+        self._retired: list = []  # outgrown landing buffers, kept until shutdown
         self._opened_ipc: Dict[str, int] = {}
         self._bounce: Optional[_DeviceBuffer] = None
         self._stream = ctypes.c_void_p()
@@ -241,9 +242,10 @@ class TransferService:
         for ptr in self._opened_ipc.values():
             _native.lib().mlf_ipc_close(ctypes.c_void_p(ptr))
         self._opened_ipc.clear()
-        for buf in list(self._inbound.values()) + ([self._bounce] if self._bounce else []):
+        for buf in list(self._inbound.values()) + self._retired + ([self._bounce] if self._bounce else []):
             buf.free()
         self._inbound.clear()
+        self._retired = []
         self._bounce = None
         if self._stream:
             _native.lib().mlf_stream_destroy(self._stream)
@@ -309,12 +311,13 @@ class TransferService:
                 _native.check(_native.lib().mlf_enable_peer_access(reply["device"]))
             return int(reply["ptr"])
         key = reply["ipc"]
-        if key not in self._opened_ipc:
-            out = ctypes.c_void_p()
-            handle = (ctypes.c_uint8 * _native.MLF_IPC_HANDLE_BYTES).from_buffer_copy(bytes.fromhex(key))
-            _native.check(_native.lib().mlf_ipc_open(handle, ctypes.byref(out)))
-            self._opened_ipc[key] = int(out.value)
-        return self._opened_ipc[key]
+        with self._lock:  # several transfers to one peer may run at once; the handle is opened once
+            if key not in self._opened_ipc:
+                out = ctypes.c_void_p()
+                handle = (ctypes.c_uint8 * _native.MLF_IPC_HANDLE_BYTES).from_buffer_copy(bytes.fromhex(key))
+                _native.check(_native.lib().mlf_ipc_open(handle, ctypes.byref(out)))
+                self._opened_ipc[key] = int(out.value)
+            return self._opened_ipc[key]
 
     def _run_put(self, task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, exact_path: bool = False) -> None:
         from ml_flashpoint.core import gpu_engine
@@ -440,7 +443,9 @@ class TransferService:
             landing = self._inbound.get(source)
             if landing is None or landing.nbytes < size:
                 if landing:
-                    landing.free()
+                    # senders may still hold the old buffer open through its IPC handle: it is
+                    # freed at shutdown, after they have released it
+                    self._retired.append(landing)
                 landing = _DeviceBuffer(size)
                 self._inbound[source] = landing
             token = uuid.uuid4().hex
