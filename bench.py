@@ -721,9 +721,10 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
         }
         del targets
 
-    # ---- object bytes against the oracle on a bounded prefix (rank 0)
+    # ---- first part of the CPU-baseline leg (rank 0, one GPU): the CPU port as checker of the object
+    # just saved, on a bounded prefix; its timed part follows further down
     parity = None
-    if rank == 0:
+    if rank == 0 and world_size == 1 and not args.no_cpu_baseline:
         import mlf_oracle as oracle
 
         sample, _ = cpu_sample(shard, 64 << 20)
