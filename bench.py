@@ -1,13 +1,15 @@
 """Benchmark of the checkpoint save / restore data path on B200.
 
 One "step" is one full save of a rank's shard of a Llama-3-8B training state (bf16 weights, fp32
-master copy, fp32 Adam moments: 16 bytes per parameter, FSDP-sharded 8 ways on dimension 0, about
-16.06 GB per rank) into a memory-backed checkpoint object, followed (outside the save timing) by a
-restore of the same object. Every rank saves its own shard with no data-path collective, so the
-job scales weakly: ``value`` is the bytes all ranks saved divided by the slowest rank's time.
+master copy, fp32 Adam moments: 2 + 4 + 4 + 4 = 14 bytes per parameter, FSDP-sharded 8 ways on
+dimension 0, 14.05 GB per rank) into a memory-backed checkpoint object, followed (outside the save
+timing) by a restore of the same object. Every rank saves its own shard with no data-path
+collective, so the job scales weakly: ``value`` is the bytes all ranks saved divided by the slowest
+rank's time.
 
     python bench.py --gpus 1 --steps 3 --warmup 3            # this implementation
-    python bench.py --impl reference --steps 2 --warmup 1     # the reference's CPU path (oracle port)
+    python bench.py --impl reference --steps 2 --warmup 1     # the reference's own CPU path (oracle/_ref)
+    python bench.py --probe host-link                          # plain pinned copies, fresh process per rank
 
 Prints ONE JSON line on rank 0. Synthetic data only: random-initialised tensors with the shapes,
 dtypes and value distributions of the named configuration.
@@ -240,7 +242,8 @@ def calibrate_host_link(device, nbytes: int = 2 << 30) -> dict:
 
 
 # --------------------------------------------------------------------------------------
-# CPU baseline (the reference's host path, restated in oracle/cpu_path.py)
+# CPU baseline: the reference's own saver / loader (oracle/_ref driven by oracle/ref_arm.py),
+# or, where that build is absent, its restatement in oracle/cpu_path.py
 # --------------------------------------------------------------------------------------
 def cpu_sample(shard, budget_bytes: int):
     picked, total = [], 0
@@ -253,7 +256,45 @@ def cpu_sample(shard, budget_bytes: int):
     return picked, total
 
 
-def run_cpu_baseline(shard, workdir: str, budget_bytes: int, passes: int, ranks_on_host: int = 1) -> dict:
+def reference_arm_unavailable():
+    """None when the byte-compiled reference under oracle/_ref can run here, else the reason."""
+    import ref_arm
+
+    return ref_arm.unavailable_reason()
+
+
+def run_reference_ranks(world_size: int, steps: int, warmup: int, workdir: str, layers: int, budget_s: float,
+                        digest: bool = False, max_sample_bytes=None) -> dict:
+    """``world_size`` ranks of the reference implementation saving at once on this host's cores
+    (one fresh process per rank; see oracle/ref_arm.py). Returns the aggregate as a cpu_baseline dict."""
+    import ref_arm
+
+    r = ref_arm.run(world_size, steps, warmup, os.path.join(workdir, "reference_arm"), layers=layers,
+                    budget_s=budget_s, digest=digest, max_sample_bytes=max_sample_bytes)
+    out = {
+        "value": r["value"],
+        "unit": UNIT,
+        "cores": r["cores"],
+        "host_cpus": r["host_cpus"],
+        "kind": "reference",
+        "sample": r["sample"],
+        "ranks": r["ranks"],
+        "ms_per_step": r["ms_per_step"],
+        "bytes_per_step_per_rank": r["bytes_per_step_per_rank"],
+        "whole_shard": r["bytes_per_step_per_rank"] >= r["full_bytes_per_rank"],
+        "blocking_stage_ms": r["blocking_stage_ms"],
+        "write_ms": r["write_ms"],
+        "restore_value": r.get("restore_value"),
+        "restore_verified": r.get("restore_verified"),
+    }
+    if digest:
+        out["objects"] = r["objects"]
+    return out
+
+
+def run_cpu_port(shard, workdir: str, budget_bytes: int, passes: int, ranks_on_host: int = 1) -> dict:
+    """Fallback CPU baseline where oracle/_ref is absent: the restated host path of oracle/cpu_path.py
+    (no buffer pool, one rank)."""
     import cpu_path
 
     tensors, nbytes = cpu_sample(shard, budget_bytes)
@@ -281,7 +322,7 @@ def run_cpu_baseline(shard, workdir: str, budget_bytes: int, passes: int, ranks_
         "cores": cpu_path.reference_thread_count(ranks_on_host),
         "host_cpus": os.cpu_count(),
         "kind": "port",
-        "sample": f"first {len(tensors)} tensors of the shard, {nbytes / 1e9:.2f} GB, GPU-sourced: stage to pageable host memory + copy_ into a tmpfs mapping; best of {passes} passes",
+        "sample": f"first {len(tensors)} tensors of the shard, {nbytes / 1e9:.2f} GB, GPU-sourced: stage to pageable host memory + copy_ into a fresh tmpfs mapping (no buffer pool); best of {passes} passes",
         "blocking_stage_ms": min(stage) * 1e3,
         "restore_value": nbytes / 1e9 / restore_s,
         "restore_verified": bool(ok),
@@ -303,7 +344,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replication", action="store_true")
     ap.add_argument("--no-overlap-probe", action="store_true")
-    ap.add_argument("--cpu-sample-gb", type=float, default=2.0)
+    ap.add_argument("--cpu-sample-gb", type=float, default=2.0, help="sample of the fallback CPU port (only without oracle/_ref)")
+    ap.add_argument("--ref-budget-s", type=float, default=150.0, help="time budget of the reference arm's warm-up + timed saves")
+    ap.add_argument("--cpu-baseline-budget-s", type=float, default=20.0, help="time budget of the CPU-baseline leg's saves")
     ap.add_argument("--workdir", default=None)
     ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
     args = ap.parse_args()
@@ -358,28 +401,44 @@ def main() -> None:
 
 
 def run_reference_arm(args, device, workdir: str) -> None:
-    import cpu_path
+    """The reference's own CPU implementation of the save, on this host's cores: ``--gpus`` ranks
+    saving at once, each a process of its own with its own buffer pool, staged from its own GPU,
+    as the reference runs them (rank 0 of the launch drives all of them and prints the line)."""
+    world_size = max(1, args.gpus)
+    payload_full = shard_payload_bytes(args.layers)
+    why = reference_arm_unavailable()
+    if why is None:
+        cpu = run_reference_ranks(world_size, args.steps, max(args.warmup, 2), workdir, args.layers, args.ref_budget_s)
+        value, ms_per_step = cpu["value"], cpu["ms_per_step"]
+        warmup = max(args.warmup, 2)
+    else:
+        # no oracle/_ref on this machine: the restated host path, one rank, bounded sample
+        import cpu_path
 
-    shard = build_shard(0, device, layers=args.layers)
-    payload_full = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
-    tensors, nbytes = cpu_sample(shard, int(args.cpu_sample_gb * 1e9))
-    path = os.path.join(workdir, "reference.distcp")
-    def sync():
+        shard = build_shard(0, device, layers=args.layers)
+        tensors, nbytes = cpu_sample(shard, int(args.cpu_sample_gb * 1e9))
+        path = os.path.join(workdir, "reference.distcp")
+        warmup = max(args.warmup, 1)
+        for _ in range(warmup):
+            cpu_path.timed_save(tensors, path)
         if torch.cuda.is_available():
             torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 1)):
-        cpu_path.timed_save(tensors, path)
-    sync()
-    t0 = time.perf_counter()
-    stage_ms = []
-    for _ in range(args.steps):
-        r = cpu_path.timed_save(tensors, path)
-        stage_ms.append(r["stage_s"] * 1e3)
-    sync()
-    elapsed = time.perf_counter() - t0
-    value = nbytes * args.steps / 1e9 / elapsed
-    sample = f"first {len(tensors)} tensors of one rank's shard ({nbytes / 1e9:.2f} of {payload_full / 1e9:.2f} GB) per step"
+        t0 = time.perf_counter()
+        stage_ms = [cpu_path.timed_save(tensors, path)["stage_s"] * 1e3 for _ in range(args.steps)]
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+        value, ms_per_step = nbytes * args.steps / 1e9 / elapsed, elapsed / args.steps * 1e3
+        cpu = {
+            "value": value,
+            "unit": UNIT,
+            "cores": cpu_path.reference_thread_count(1),
+            "host_cpus": os.cpu_count(),
+            "kind": "port",
+            "sample": f"{why}; restated host path instead: first {len(tensors)} tensors of one rank's shard "
+            f"({nbytes / 1e9:.2f} of {payload_full / 1e9:.2f} GB) per step, one rank, no buffer pool",
+            "blocking_stage_ms": statistics.median(stage_ms),
+        }
     line = {
         "impl": "reference",
         "metric": METRIC,
@@ -387,27 +446,31 @@ def run_reference_arm(args, device, workdir: str) -> None:
         "unit": UNIT,
         "n_gpus": args.gpus,
         "steps": args.steps,
-        "warmup": args.warmup,
-        "ms_per_step": elapsed / args.steps * 1e3,
+        "warmup": warmup,
+        "ms_per_step": ms_per_step,
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "u8",
         "data": "synthetic",
         "config": workload_config(args, payload_full),
-        "cpu_baseline": {
-            "value": value,
-            "unit": UNIT,
-            "cores": cpu_path.reference_thread_count(1),
-            "host_cpus": os.cpu_count(),
-            "kind": "port",
-            "sample": sample,
-            "blocking_stage_ms": statistics.median(stage_ms),
-        },
+        "per_gpu_value": value / world_size if cpu["kind"] == "reference" else value,
+        "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def shard_payload_bytes(layers: int = 32) -> int:
+    """Payload bytes of one rank's shard (14 bytes per parameter), from the shapes alone."""
+    total = 0
+    for _, shape in llama3_8b_params(layers):
+        numel = shape[0] // FSDP_WORLD
+        for d in shape[1:]:
+            numel *= d
+        total += numel * 14
+    return total
 
 
 def workload_config(args, payload_bytes: int) -> dict:
@@ -416,18 +479,35 @@ def workload_config(args, payload_bytes: int) -> dict:
         + ("" if args.layers == 32 else f" (reduced to {args.layers} layers)"),
         "payload_bytes_per_rank": payload_bytes,
         "pack_mode": args.mode or "staged",
-        "cache": "inputs larger than L2 (16 GB per rank vs 126 MB)",
+        "cache": "inputs larger than L2 (14.05 GB per rank vs 126 MB)",
         "objects_per_rank": 1,
     }
 
 
-def run_replication(args, rank, world_size, device, workdir, com, saver, engine, items, resolver, shard, one_save, state):
-    """Replicates the last saved object of every rank to rank (r + 1) mod N, all ranks at once.
+def file_sha256(path: str) -> str:
+    import hashlib
+
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for block in iter(lambda: f.read(1 << 24), b""):
+            h.update(block)
+    return h.hexdigest()
+
+
+def run_replication(args, rank, world_size, device, workdir, com, engine, items, resolver, shard, state):
+    """Replicates every rank's object to rank (r + 1) mod N, all ranks at once, two ways:
+
+    * ``after_save``: the object is saved first, then ``ReplicationManager.async_replicate`` is timed
+      alone (object in the partner's file when the future resolves);
+    * ``with_save``: ``write_data_async(replicate_after_write=True)``: the push over NVLink is queued
+      with the pack kernel and reads the HBM image while the copy engine drains it to the host.
 
     Uses the full object when /dev/shm can hold a second copy per rank, otherwise a prefix of the
-    shard saved as an object of its own (and says so). Returns throughput of the whole replication
-    (object in the partner's file) and of the GPU-to-GPU hop alone (NVLink roofline)."""
+    shard saved as an object of its own (and says so). After the last round every rank hashes the
+    replica it received and compares it with the digest of the sender's primary object."""
+    from ml_flashpoint.core.buffer_pool import BufferPool
     from ml_flashpoint.core.checkpoint_id_types import CheckpointContainerId
+    from ml_flashpoint.core.checkpoint_saver import DefaultMLFlashpointCheckpointSaver
     from ml_flashpoint.replication import replication_manager as rm
     from ml_flashpoint.replication.transfer_service.transfer_service_ext import TransferService
 
@@ -441,7 +521,6 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
     free = stat.f_bavail * stat.f_frsize
     full = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
     budget = int(0.8 * free / world_size)
-    from ml_flashpoint.core.buffer_pool import BufferPool
 
     # replicas land in a page-locked pool file of their own, like primaries do
     landing_pool = BufferPool(os.path.join(workdir, "replica_pool"), rank, 1, min(full, budget) + (1 << 20), register_cuda=True)
@@ -452,6 +531,15 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
     dist.all_gather_object(addresses, service.address)
     manager = rm.ReplicationManager()
     manager.initialize(com, replication_transfer_service=service, repl_strategy=rm.RingReplicationStrategy(addresses))
+    saver = DefaultMLFlashpointCheckpointSaver(
+        global_rank_getter=lambda: rank,
+        local_rank_getter=lambda: rank,
+        global_barrier_func=barrier,
+        ckpt_obj_manager=com,
+        replication_manager=manager,
+        initial_buffer_size_bytes=full + (1 << 20),
+        copy_engine=engine,
+    )
 
     note = "full object"
     sub_items = items
@@ -466,45 +554,93 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
             total += n
         sub_items = picked
         note = f"prefix of the shard ({total / 1e9:.2f} of {full / 1e9:.2f} GB): tmpfs cannot hold a second full copy per rank"
-    times, hops = [], []
-    error = None
-    for i in range(3):
+
+    def new_checkpoint():
         if state["prev"] is not None:
             com.delete_container(state["prev"])
         ckpt = CheckpointContainerId(os.path.join(workdir, "ckpt", f"step-{state['step']}_ckpt"))
         state["step"] += 1
         state["prev"] = ckpt
         saver.initialize_checkpoint(ckpt)
-        buckets = saver.prepare_write_data(ckpt, sub_items, resolver, f"__{rank}_", bucket_count=1)
-        saver.write_data(ckpt, buckets, replicate_after_write=False, thread_count=1)
-        barrier()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
+        return ckpt, saver.prepare_write_data(ckpt, sub_items, resolver, f"__{rank}_", bucket_count=1)
+
+    times, hops = [], []
+    both_s, to_hbm_wall_ms, to_hbm_dev_ms = [], [], []
+    error = None
+    held = 0
+    buckets = None
+    rounds = [("after_save", 0), ("after_save", 1), ("after_save", 2), ("with_save", 0), ("with_save", 1)]
+    for k, (how, i) in enumerate(rounds):
+        ckpt, buckets = new_checkpoint()
         try:
-            futures = manager.async_replicate(com.get_buffer(buckets[0].object_id))
-            for f in futures:
-                f.result(timeout=200)
+            if how == "after_save":
+                saver.write_data(ckpt, buckets, replicate_after_write=False, thread_count=1)
+                barrier()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                futures = manager.async_replicate(com.get_buffer(buckets[0].object_id))
+                for f in futures:
+                    f.result(timeout=200)
+                dt = time.perf_counter() - t0
+                if i:  # the first round opens IPC handles and allocates landing buffers
+                    times.append(dt)
+                    hops.append(service.last_put_stats)
+            else:
+                barrier()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                pending = saver.write_data_async(ckpt, buckets, replicate_after_write=True)
+                pending.result()
+                for f in pending.replication_futures:
+                    f.result(timeout=200)
+                dt = time.perf_counter() - t0
+                stats = service.last_put_stats
+                if i:
+                    both_s.append(dt)
+                    to_hbm_wall_ms.append((stats["in_peer_hbm_at"] - t0) * 1e3)
+                    if stats.get("since_save_start_ms") is not None:
+                        to_hbm_dev_ms.append(stats["since_save_start_ms"])
         except Exception as e:  # keep the collectives below symmetric; report instead of dying
-            error = f"{type(e).__name__}: {e}"
-        dt = time.perf_counter() - t0
+            error = error or f"{type(e).__name__}: {e}"
+        held = max(held, engine.held_device_bytes() + service.held_device_bytes())
         barrier()
-        if i and error is None:  # first round opens IPC handles and allocates landing buffers
-            times.append(dt)
-            hops.append(service.last_put_stats)
-        shutil.rmtree(replica_root, ignore_errors=True)  # the partner's copy of the previous round
-        barrier()
-    object_bytes = os.path.getsize(str(buckets[0].object_id))
+        if k + 1 < len(rounds):
+            shutil.rmtree(replica_root, ignore_errors=True)  # the partner's copy of this round
+            barrier()
+
+    # ---- are the replicas the primaries, byte for byte? (digests travel, files stay where they are)
+    object_path = str(buckets[0].object_id)
+    object_bytes = os.path.getsize(object_path)
+    source = (rank - 1) % world_size
+    mine = [None] * world_size
+    digest_error = None
+    try:
+        box = {}
+        worker = threading.Thread(target=lambda: box.__setitem__("primary", file_sha256(object_path)))
+        worker.start()
+        dist.all_gather_object(mine, (object_path, None))  # object ids first: the replica's path depends on the sender's
+        replica_digest = file_sha256(mapper(mine[source][0], source))
+        worker.join()
+        digests = [None] * world_size
+        dist.all_gather_object(digests, box["primary"])
+        ok = replica_digest == digests[source]
+    except Exception as e:
+        digest_error = f"{type(e).__name__}: {e}"
+        ok = False
+    all_ok = all_max(0.0 if ok else 1.0, device) == 0.0
+
     failed = all_max(0.0 if error is None else 1.0, device)
     service.release_peers()  # importers close first ...
     barrier()
     manager.shutdown()  # ... then exporters free their landing buffers
     landing_pool.teardown()
+    shutil.rmtree(replica_root, ignore_errors=True)
     if failed:
         return {"error": error or "a peer rank failed", "what": note}
     slow = all_max(statistics.mean(times), device)
     hop_ms = all_max(statistics.mean(h["hop_ms"] for h in hops), device)
     total_bytes = all_sum(object_bytes, device)
-    return {
+    out = {
         "e2e_value": total_bytes / 1e9 / slow,
         "unit": UNIT,
         "ms": slow * 1e3,
@@ -516,7 +652,22 @@ def run_replication(args, rank, world_size, device, workdir, com, saver, engine,
         "nvlink_frac_of_measured_770": object_bytes / 1e9 / (hop_ms / 1e3) / 770.0,
         "source": "HBM image of the save" if hops[-1]["from_hbm_image"] else "host mapping via bounce ring",
         "partner": "(rank + 1) mod N",
+        "bit_exact": bool(all_ok),
+        "bit_exact_how": "SHA-256 of the replica each rank received vs the digest of the sender's primary object (all_gather_object)",
+        "hbm_held_bytes": int(all_max(float(held), device)),
     }
+    if digest_error:
+        out["bit_exact_error"] = digest_error
+    if both_s:
+        out["with_save"] = {
+            "what": "write_data_async(replicate_after_write=True): push queued with the pack kernel, NVLink hop overlaps the drain",
+            "save_and_replica_on_partner_host_ms": all_max(statistics.mean(both_s), device) * 1e3,
+            "ms_to_partner_hbm": all_max(statistics.mean(to_hbm_wall_ms), device),
+            "ms_to_partner_hbm_device": all_max(statistics.mean(to_hbm_dev_ms), device) if to_hbm_dev_ms else None,
+            "note": "ms_to_partner_hbm = wall time from the call to the last byte of the replica in the partner's HBM; "
+            "the _device figure runs from the pack kernel's start event to the end of the copy kernel",
+        }
+    return out
 
 
 def overlap_probe(saver, com, base, state, items, resolver, rank, device) -> dict:
@@ -721,24 +872,42 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
         }
         del targets
 
-    # ---- first part of the CPU-baseline leg (rank 0, one GPU): the CPU port as checker of the object
-    # just saved, on a bounded prefix; its timed part follows further down
+    # ---- parity of the object just saved with the CPU oracle (its checker role): the whole shard
+    # through a streaming SHA-256 on one GPU, a 64 MB prefix on every rank otherwise
     parity = None
-    if rank == 0 and world_size == 1 and not args.no_cpu_baseline:
+    parity_prefix = None
+    object_path = str(buckets[0].object_id)
+    if not args.no_cpu_baseline:
         import mlf_oracle as oracle
 
         sample, _ = cpu_sample(shard, 64 << 20)
         want, _ = oracle.pack_object([(str(i), t.cpu()) for i, t in enumerate(sample)], [])
-        with open(str(buckets[0].object_id), "rb") as f:
+        with open(object_path, "rb") as f:
             got = f.read(len(want))
         # the oracle's metadata block carries the sample's length; compare the data section prefix
-        parity = got[METADATA_SIZE:] == want[METADATA_SIZE:]
+        mine_ok = got[METADATA_SIZE:] == want[METADATA_SIZE:]
+        parity_prefix = all_max(0.0 if mine_ok else 1.0, device) == 0.0
+        if world_size == 1:
+            box = {}
+            worker = threading.Thread(target=lambda: box.__setitem__("file", file_sha256(object_path)))
+            worker.start()
+            # tensors stay on the GPU; the oracle brings one at a time to the host while it hashes it
+            want_sha, want_size = oracle.object_sha256([(str(i), t) for i, (_, t, _, _) in enumerate(shard)])
+            worker.join()
+            parity = {
+                "whole_object_sha256_equal": box["file"] == want_sha and os.path.getsize(object_path) == want_size,
+                "object_bytes": want_size,
+                "file_sha256": box["file"],
+                "oracle_sha256": want_sha,
+                "how": "oracle.object_sha256 (headers and payloads hashed tensor by tensor) vs SHA-256 of the saved object file",
+            }
 
     # ---- replication to the ring partner (only where there is a partner)
     replication = None
     if world_size > 1 and not args.no_replication:
-        replication = run_replication(args, rank, world_size, device, workdir, com, saver, engine, items, resolver, shard, one_save, state)
+        replication = run_replication(args, rank, world_size, device, workdir, com, engine, items, resolver, shard, state)
 
+    hbm_held = int(all_max(float(engine.held_device_bytes()), device))
     pinned_peak = calibrate_host_link(device)
 
     total_payload = all_sum(payload, device)
@@ -750,12 +919,38 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
 
     cpu = None
     if rank == 0 and world_size == 1 and not args.no_cpu_baseline:
-        engine.release_device_memory()  # the CPU baseline stages from the same tensors; free the image arena first
-        cpu = run_cpu_baseline(shard, workdir, int(args.cpu_sample_gb * 1e9), passes=3)
+        engine.release_device_memory()  # the CPU baseline stages the same state from this GPU; free the image arena first
+        if reference_arm_unavailable() is None:
+            # the reference's own saver and loader, one rank, in a process of its own (its package has
+            # the same name as this one); it also reports the SHA-256 of the object IT wrote
+            cpu = run_reference_ranks(1, 2, 2, workdir, args.layers, args.cpu_baseline_budget_s, digest=True)
+            theirs = cpu.pop("objects")[0]
+            if parity is not None and cpu["whole_shard"]:
+                parity["equal_to_reference_object"] = theirs["sha256"] == parity["file_sha256"] and theirs["size"] == parity["object_bytes"]
+                parity["reference_how"] = "SHA-256 of the object the reference's own saver wrote for the same seeded shard (oracle/_ref)"
+        else:
+            cpu = run_cpu_port(shard, workdir, int(args.cpu_sample_gb * 1e9), passes=3)
+            cpu["sample"] = reference_arm_unavailable() + "; " + cpu["sample"]
 
     if rank != 0:
         return
     achieved = 2 * payload / 1e9 / kernel_s
+    d2h_gbs = (
+        layout.total_bytes / 1e9 / ((statistics.mean(device_ms) - statistics.mean(kernel_ms)) / 1e3)
+        if statistics.mean(device_ms) > statistics.mean(kernel_ms)
+        else achieved / 2
+    )
+    if restore is not None:
+        per_gpu = restore["e2e_value"] / world_size
+        restore["roofline"] = {
+            "bound": "host_link",
+            "achieved": per_gpu,
+            "peak": pinned_peak["h2d"],
+            "unit": "GB/s",
+            "frac": per_gpu / pinned_peak["h2d"],
+            "peak_source": "plain pinned host-to-device copies, all ranks at once, slowest rank (this run)",
+            "what": "end-to-end restore per GPU: object file -> HBM image -> unpack kernel -> target tensors",
+        }
     line = {
         "metric": METRIC,
         "value": total_payload * args.steps / 1e9 / slow_device_s,
@@ -786,6 +981,9 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
             "api": "DefaultMLFlashpointCheckpointSaver.write_data (object closed on return)",
         },
         "restore": restore,
+        "hbm_held_bytes": hbm_held,
+        "hbm_held_note": "HBM the data path holds beyond the caller's tensors during a save (the image arena); "
+        "replication adds landing and bounce buffers, see replication.hbm_held_bytes",
         "overlap": overlap,
         "replication": replication,
         "roofline": {
@@ -802,21 +1000,20 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
             "traffic_source": "ncu capture of a 2.6 GB case scaled by payload bytes",
         },
         "host_link": {
-            "d2h_gbs": (
-                layout.total_bytes / 1e9 / ((statistics.mean(device_ms) - statistics.mean(kernel_ms)) / 1e3)
-                if statistics.mean(device_ms) > statistics.mean(kernel_ms)
-                else achieved / 2
-            ),
+            "d2h_gbs": d2h_gbs,
             "note": "copy-engine drain of the HBM image into the page-locked object mapping (staged), "
             "or the kernel's own stores into it (direct)",
             "pinned_copy_peak_d2h_gbs": pinned_peak["d2h"],
             "pinned_copy_peak_h2d_gbs": pinned_peak["h2d"],
             "peak_note": "plain copies to/from driver-allocated pinned memory, all ranks at once, slowest rank",
+            "frac_of_pinned_peak": d2h_gbs / pinned_peak["d2h"],
+            "frac_of_pcie_gen5_x16_63gbs": d2h_gbs / 63.0,
         },
         "cpu_baseline": cpu,
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "parity_vs_oracle_prefix": parity,
+        "parity_vs_oracle": parity,
+        "parity_vs_oracle_prefix": parity_prefix,
         "pool_register_s": register_s,
     }
     print(json.dumps(line))

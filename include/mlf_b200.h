@@ -140,10 +140,15 @@ int32_t mlf_plan_status(mlf_plan* p);
  * until the process exits.
  *
  * The first call on a device, with that device current, looks up the array's device address;
- * make that first call outside any stream capture. All calls on a device share the one array,
- * and it keeps the last call's tables: two calls whose kernels can overlap on the GPU (different
- * streams, or several threads) race on it, so finish one (or order them on one stream) before
- * starting the next. The launch is asynchronous on `stream`, like mlf_plan_launch. */
+ * make that first call outside any stream capture. Better still, make one small real call (a
+ * single descriptor) per device at start-up: it brings the library's module, the array and the
+ * kernel onto the device while memory is still to be had, which a later call in a tight spot
+ * would otherwise have to do itself. All calls on a device share the one array, and it keeps the
+ * last call's tables: two calls whose kernels can overlap on the GPU (different streams, or
+ * several threads) race on it, so finish one (or order them on one stream) before starting the
+ * next. Do not call it while `stream` is being captured: the tables are uploaded from host
+ * arrays that the next call overwrites. The kernel runs asynchronously on `stream`, but the call
+ * itself may wait for work queued earlier on that stream (the upload is from pageable memory). */
 #define MLF_NOALLOC_MAX_DESCS 1024
 int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_base, uint64_t image_capacity, void* stream);
 /* Kernel launches issued by this library since load (for launch accounting in benchmarks). */

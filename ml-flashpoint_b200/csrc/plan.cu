@@ -921,18 +921,41 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg*
     if (d.ndim > MLF_MAX_DIMS) return mlf::fail(MLF_ERR_INVALID, where + ": ndim exceeds MLF_MAX_DIMS");
     if (d.elem_size != 1 && d.elem_size != 2 && d.elem_size != 4 && d.elem_size != 8 && d.elem_size != 16)
       return mlf::fail(MLF_ERR_INVALID, where + ": elem_size must be 1, 2, 4, 8 or 16");
+    // Shapes and strides come from the caller: every product and sum below is checked, so that a
+    // wrapped extent can never slip under the image-capacity guard of the launch.
     uint64_t numel = 1;
-    uint64_t span = 0;  // highest element index touched on the image side
+    uint64_t span = 0;   // highest element index touched on the image side
+    uint64_t tspan = 0;  // the same on the tensor side
+    bool empty = false, overflow = false;
     for (uint32_t k = 0; k < d.ndim; ++k) {
       if (d.shape[k] < 0 || d.tensor_stride[k] < 0 || d.image_stride[k] < 0)
         return mlf::fail(MLF_ERR_INVALID, where + ": negative extent or stride");
-      numel *= (uint64_t)d.shape[k];
-      if (d.shape[k] > 0) span += (uint64_t)(d.shape[k] - 1) * (uint64_t)d.image_stride[k];
+      if (d.shape[k] == 0) empty = true;
     }
-    if (numel == 0) return MLF_OK;  // nothing to move; the format stores no payload for it either
+    if (empty) return MLF_OK;  // nothing to move; the format stores no payload for it either
+    for (uint32_t k = 0; k < d.ndim; ++k) {
+      uint64_t step = 0;
+      overflow |= __builtin_mul_overflow(numel, (uint64_t)d.shape[k], &numel);
+      overflow |= __builtin_mul_overflow((uint64_t)(d.shape[k] - 1), (uint64_t)d.image_stride[k], &step);
+      overflow |= __builtin_add_overflow(span, step, &span);
+      overflow |= __builtin_mul_overflow((uint64_t)(d.shape[k] - 1), (uint64_t)d.tensor_stride[k], &step);
+      overflow |= __builtin_add_overflow(tspan, step, &tspan);
+    }
     if (d.tensor_ptr == 0) return mlf::fail(MLF_ERR_INVALID, where + ": null tensor pointer");
-    *payload_out = numel * d.elem_size;
-    *extent_out = d.image_off + (span + 1) * d.elem_size;
+    uint64_t payload = 0, extent = 0, tensor_end = 0;
+    overflow |= __builtin_mul_overflow(numel, (uint64_t)d.elem_size, &payload);
+    overflow |= __builtin_add_overflow(span, (uint64_t)1, &extent);
+    overflow |= __builtin_mul_overflow(extent, (uint64_t)d.elem_size, &extent);
+    overflow |= __builtin_add_overflow(extent, d.image_off, &extent);
+    overflow |= __builtin_add_overflow(tspan, (uint64_t)1, &tensor_end);
+    overflow |= __builtin_mul_overflow(tensor_end, (uint64_t)d.elem_size, &tensor_end);
+    overflow |= __builtin_add_overflow(tensor_end, d.tensor_ptr, &tensor_end);
+    // byte strides are kept as int64 further down; 2^62 leaves room for the x2 of 16-byte elements
+    overflow |= payload >> 62 || extent >> 62 || (tensor_end - d.tensor_ptr) >> 62;
+    if (overflow)
+      return mlf::fail(MLF_ERR_INVALID, where + ": shape and strides overflow 64-bit byte arithmetic");
+    *payload_out = payload;
+    *extent_out = extent;
 
     // 16-byte elements are moved as pairs of 8-byte halves (an extra innermost dimension of 2)
     int64_t shp[MLF_MAX_DIMS + 1], ts[MLF_MAX_DIMS + 1], is[MLF_MAX_DIMS + 1];
@@ -1167,14 +1190,22 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
         {mlf_plan_kernel_stream<MLF_PACK>, mlf_plan_kernel_bulk<MLF_PACK>},
         {mlf_plan_kernel_stream<MLF_UNPACK>, mlf_plan_kernel_bulk<MLF_UNPACK>},
     };
-    static std::once_flag opted_in;
-    static cudaError_t opt_status = cudaSuccess;
-    std::call_once(opted_in, [&]() {
-      for (int d = 0; d < 2 && opt_status == cudaSuccess; ++d)
-        for (int v = 0; v < 2 && opt_status == cudaSuccess; ++v)
-          opt_status = cudaFuncSetAttribute(kernels[d][v], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem);
-    });
-    MLF_CUDA(opt_status);
+    // The opt-in to more than 48 KiB of dynamic shared memory is a per-device function attribute:
+    // a process that drives several GPUs has to set it once on each of them.
+    static std::mutex opt_mu;
+    static bool opted_in[kMaxDevices] = {false};
+    int dev = 0;
+    MLF_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return mlf::fail(MLF_ERR_INVALID, "mlf_plan_launch: device index out of range");
+    {
+      std::lock_guard<std::mutex> hold(opt_mu);
+      if (!opted_in[dev]) {
+        for (int d = 0; d < 2; ++d)
+          for (int v = 0; v < 2; ++v)
+            MLF_CUDA(cudaFuncSetAttribute(kernels[d][v], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkDynSmem));
+        opted_in[dev] = true;
+      }
+    }
     const bool staged = p->nlinear < p->ntiles;
     const BulkKernel kernel = kernels[p->direction == MLF_PACK ? 0 : 1][staged ? 1 : 0];
     const int32_t rc = wave_grid(kernel, max_ctas, p->ntiles, &grid, kBulkDynSmem);

@@ -91,9 +91,14 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
         all_gather_object_func: Callable[..., None],
         world_size_getter: Callable[[], int],
         copy_engine: Optional["gpu_engine.CudaCopyEngine"] = None,
+        replica_namespace=None,
     ):
         """``copy_engine`` moves the bytes (default: the process-wide CUDA engine, created on first
-        use); the other arguments are as in the reference (:126-160)."""
+        use). ``replica_namespace`` (a ``transfer_service_ext.ReplicaNamespace``) is for ranks whose
+        replication partners share their filesystem: the replicas this rank holds for others are then
+        reported during recovery as objects it can serve. The other arguments are as in the reference
+        (:126-160)."""
+        self._replica_namespace = replica_namespace
         self._checkpoint_object_manager = checkpoint_object_manager
         self._replication_manager = replication_manager
         self._global_rank_getter = global_rank_getter
@@ -193,6 +198,7 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
             optimized = stream.format_signature == CheckpointFormat.MLF_FORMAT
             scatter = []  # (target, payload offset, stored shape, storage offsets)
             commits = []  # (req, target)
+            converts = []  # (target, temporary in the stored dtype)
             # The bytes start moving into HBM now; headers are parsed and the plan is built meanwhile.
             prefetched = None
             tensor_items = [storage_data[req.storage_index] for req in read_items if req.type != LoadItemType.BYTE_IO]
@@ -222,18 +228,24 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
                 assert tuple(target.size()) == tuple(req.lengths), (
                     f"req {req.storage_index} mismatch sizes {target.size()} vs {torch.Size(req.lengths)}"
                 )
-                if target.dtype != dtype:
-                    raise TypeError(f"req {req.storage_index}: stored dtype {dtype} but target is {target.dtype}")
                 for off, n, full in zip(req.storage_offsets, req.lengths, shape):
                     if off < 0 or off + n > full:
                         raise IndexError(f"req {req.storage_index}: block [{off}, {off + n}) outside stored extent {full}")
-                scatter.append((target, item_md.offset + header_bytes, tuple(shape), tuple(req.storage_offsets)))
+                landing = target
+                if target.dtype != dtype:
+                    # the reference ends in ``target.copy_(tensor)`` (:331-336), which converts: the block
+                    # is unpacked in its stored dtype into a device temporary and converted from there
+                    landing = torch.empty(tuple(req.lengths), dtype=dtype, device=getattr(self._engine(), "device", target.device))
+                    converts.append((target, landing))
+                scatter.append((landing, item_md.offset + header_bytes, tuple(shape), tuple(req.storage_offsets)))
                 commits.append((req, target))
             if scatter:
                 if prefetched is not None:
                     self._engine().unpack(scatter, stream, prefetched=prefetched)
                 else:
                     self._engine().unpack(scatter, stream)
+            for target, landing in converts:
+                target.copy_(landing)
             for req, target in commits:
                 planner.commit_tensor(req, target)
 
@@ -432,8 +444,12 @@ class DefaultMLFlashpointCheckpointLoader(MLFlashpointCheckpointLoader):
         return all(verdicts)
 
     def _get_extra_local_objects(self, container_path: Path) -> List[CheckpointObjectId]:
-        """Hook: further objects this rank can serve (e.g. framework context files)."""
-        return []
+        """Hook: further objects this rank can serve (e.g. framework context files). Here: the replicas
+        it holds for other ranks, under their original paths, when a replica namespace is configured."""
+        namespace = getattr(self, "_replica_namespace", None)
+        if namespace is None:
+            return []
+        return [CheckpointObjectId(path) for path in namespace.held_objects(str(container_path))]
 
     def _get_extra_needed_objects(
         self,

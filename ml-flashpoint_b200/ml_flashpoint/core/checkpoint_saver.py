@@ -65,6 +65,12 @@ class PendingSave:
     ``safe_to_mutate_event`` is the CUDA event for the same moment, for
     ``stream.wait_event`` without blocking the host. ``result`` blocks until every object is
     complete in its buffer, closes the buffers and returns the write results.
+
+    With ``replicate_after_write`` the push of an object to its replication partners is queued as
+    soon as its pack kernel is, when the object's file already has its final size (pool buffers):
+    the copy over NVLink reads the finished HBM image while the copy engine still drains the same
+    image to the host. Objects in standalone files are replicated from ``result``, after the close
+    that trims them. ``replication_futures`` collects the transfer futures either way.
     """
 
     def __init__(self, saver: "DefaultMLFlashpointCheckpointSaver", replicate_after_write: bool):
@@ -72,9 +78,15 @@ class PendingSave:
         self._replicate = replicate_after_write
         self._parts: list = []  # (bucket, writer, records, ticket)
         self._results: Optional[list[WriteResult]] = None
+        self._replicated_early: set = set()  # object names whose replication started with the pack kernel
+        self.replication_futures: list = []  # transfer futures of replications started so far
 
     def _add(self, bucket, writer, records, ticket) -> None:
         self._parts.append((bucket, writer, records, ticket))
+
+    def _note_early_replication(self, bucket, futures) -> None:
+        self._replicated_early.add(bucket.object_name)
+        self.replication_futures.extend(futures or [])
 
     @property
     def safe_to_mutate_event(self):
@@ -104,7 +116,8 @@ class PendingSave:
             raise first_error
         if self._replicate:
             for bucket, _, _, _ in self._parts:
-                self._saver.async_replicate_object(bucket.object_id)
+                if bucket.object_name not in self._replicated_early:
+                    self.replication_futures.extend(self._saver.async_replicate_object(bucket.object_id) or [])
         self._results = results
         return results
 
@@ -338,7 +351,24 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
                         open_writer.close()
                 raise
             pending._add(bucket, writer, records, ticket)
+            if replicate_after_write and self._can_replicate_early(writer):
+                try:
+                    pending._note_early_replication(bucket, self.async_replicate_object(bucket.object_id))
+                except Exception:
+                    _LOGGER.exception("Could not start replication of '%s' early; it will follow the write", bucket.object_id)
         return pending
+
+    def _can_replicate_early(self, writer) -> bool:
+        """True when replication of the object behind ``writer`` may start before its bytes have
+        reached the host mapping: the file must already have its final size (a pool buffer sized by
+        ``ensure_total_size``), because the receiver is told the object's size up front, and a
+        replication manager must be present. The transfer service then either sends the finished HBM
+        image or waits for the drain itself."""
+        return (
+            self._replication_manager is not None
+            and hasattr(writer, "ensure_total_size")
+            and hasattr(self._engine(), "wait_object_on_host")
+        )
 
     @log_execution_time(logger=_LOGGER, name="_write_to_buffer_from_queue_worker")
     def _write_to_buffer_from_queue_worker(
@@ -358,10 +388,18 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
                 # existing objects are overwritten: a restarted job may rewrite steps it abandoned
                 with self._chkpt_obj_manager.acquire_buffer(bucket.object_id, self._initial_buffer_size_bytes) as writer:
                     records, ticket = self._write_bucket(bucket, writer, use_optimized_write, wait=False)
+                    early = False
+                    if replicate_after_write and self._can_replicate_early(writer):
+                        # the NVLink hop reads the HBM image while the copy engine drains it to the host
+                        try:
+                            self.async_replicate_object(bucket.object_id)
+                            early = True
+                        except Exception:
+                            _LOGGER.exception("Could not start replication of '%s' early", bucket.object_id)
                     results = self._to_write_results(bucket.object_name, records)  # while the bytes move
                     ticket.wait()
                 results_from_threads.put((results, None))
-                if replicate_after_write:
+                if replicate_after_write and not early:
                     self.async_replicate_object(bucket.object_id)
             except Exception as e:
                 _LOGGER.exception("Error in writer thread for object '%s'", bucket.object_id)

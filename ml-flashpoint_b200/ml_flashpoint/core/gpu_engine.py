@@ -227,6 +227,8 @@ class _Image:
     nbytes: int
     done: "torch.cuda.Event"  # fires when the transfer out of the region has finished
     object_id: Optional[str]
+    ready: Optional["torch.cuda.Event"] = None  # fires when the pack kernel has written the whole image
+    start: Optional["torch.cuda.Event"] = None  # recorded right before the pack kernel (timing)
 
     def overlaps(self, offset: int, nbytes: int) -> bool:
         return self.offset < offset + nbytes and offset < self.offset + self.nbytes
@@ -296,6 +298,8 @@ class CudaCopyEngine:
         self._arena_goal = 0  # bytes the arena should hold: the largest save announced so far
         self._cursor = 0
         self._images: List[_Image] = []  # regions whose contents are still valid, oldest first
+        # object id -> event of the latest transfer into that object's mapping (kept after the image is reused)
+        self._drains: "OrderedDict[str, torch.cuda.Event]" = OrderedDict()
         self._active_read: Optional["_ObjectRead"] = None  # a restore's image being filled right now
         self.last_ticket: Optional[PackTicket] = None  # most recent save, for timing queries
         self.last_unpack_ms: Optional[Tuple[float, float]] = None  # (host-to-HBM ms, kernel ms) of the last restore
@@ -497,7 +501,12 @@ class CudaCopyEngine:
                     )
                     done_event.record(self.pack_stream)
                 resident_id = str(object_id) if object_id is not None and start_pos == 0 else None
-                self._images.append(_Image(offset, total, done_event, resident_id))
+                self._images.append(_Image(offset, total, done_event, resident_id, mutate_event, start_event))
+            if object_id is not None:
+                self._drains[str(object_id)] = done_event
+                self._drains.move_to_end(str(object_id))
+                while len(self._drains) > 64:
+                    self._drains.popitem(last=False)
             entry.last_kernel = mutate_event
             self.last_ticket = PackTicket(self, entry, start_event, mutate_event, done_event, total)
             return self.last_ticket
@@ -514,6 +523,20 @@ class CudaCopyEngine:
                 if image.object_id == str(object_id) and image.nbytes == nbytes:
                     return _ResidentLease(self, image)
         return None
+
+    def wait_object_on_host(self, object_id: str) -> None:
+        """Blocks until every save of ``object_id`` that this engine still knows of has reached the
+        object's host mapping. Callers that read the mapping while a save may still be draining
+        (replication started right after the pack kernel) call this first."""
+        with self._lock:
+            event = self._drains.get(str(object_id))
+        if event is not None:
+            event.synchronize()
+
+    def held_device_bytes(self) -> int:
+        """HBM this engine holds beyond the caller's tensors: the image arena."""
+        with self._lock:
+            return 0 if self._arena is None else int(self._arena.numel())
 
     def _fill_image(self, image: torch.Tensor, buffer_io, lo: int, nbytes: int, stream: "torch.cuda.Stream") -> None:
         """Brings data-section bytes ``[lo, lo + nbytes)`` of ``buffer_io`` into ``image``. Asynchronous on
@@ -727,11 +750,20 @@ class _ObjectRead:
 
 
 class _ResidentLease:
-    """Context manager yielding the device address of a resident object image (see ``resident_image``)."""
+    """Context manager yielding the device address of a resident object image (see ``resident_image``).
+
+    Entering waits for the pack kernel that writes the image, not for the transfer that drains it to
+    the host: the image is complete from the "safe to mutate" moment on, so a replication hop can
+    run over NVLink while the copy engine is still moving the same bytes over PCIe."""
 
     def __init__(self, engine: CudaCopyEngine, image: _Image):
         self._engine = engine
         self._image = image
+
+    @property
+    def start_event(self):
+        """CUDA event recorded right before the pack kernel of this image (None if unknown)."""
+        return self._image.start
 
     def __enter__(self) -> int:
         engine = self._engine
@@ -739,7 +771,7 @@ class _ResidentLease:
         if not any(held is self._image for held in engine._images) or self._image.object_id is None:
             engine._lock.release()
             raise RuntimeError("the resident image was overwritten before it could be leased")
-        self._image.done.synchronize()  # the image is complete once its drain to the host has finished
+        (self._image.ready or self._image.done).synchronize()
         return engine._arena.data_ptr() + self._image.offset
 
     def __exit__(self, *exc) -> None:
@@ -789,3 +821,10 @@ def resident_image(object_id: str, nbytes: int) -> Optional[_ResidentLease]:
     """``CudaCopyEngine.resident_image`` of the process-wide engine, or None if there is no engine yet."""
     engine = _default_engine
     return None if engine is None else engine.resident_image(object_id, nbytes)
+
+
+def wait_object_on_host(object_id: str) -> None:
+    """``CudaCopyEngine.wait_object_on_host`` of the process-wide engine (no-op without one)."""
+    engine = _default_engine
+    if engine is not None:
+        engine.wait_object_on_host(object_id)

@@ -27,12 +27,14 @@ for every transfer. ``MLFLASHPOINT_REPL_TRANSPORT`` = ``auto`` (default) | ``nvl
 from __future__ import annotations
 
 import concurrent.futures
+import contextlib
 import ctypes
 import json
 import os
 import socket
 import struct
 import threading
+import time
 import uuid
 from typing import Callable, Dict, Optional, Tuple
 
@@ -114,6 +116,40 @@ def _recv_into(sock: socket.socket, view: memoryview) -> None:
         if n == 0:
             raise ConnectionError("peer closed the connection in the middle of an object")
         got += n
+
+
+class ReplicaNamespace:
+    """Where replicas live when replication partners share one filesystem (the ranks of one box).
+
+    The reference stores a replica under the sender's own path on another host
+    (transfer_service.cpp:702-780). On one box that path is the primary itself, so replicas go to
+    ``<root>/src<sender rank>/<object path>`` instead. An instance is callable as the
+    ``replica_path_mapper`` of ``TransferService``; ``held_objects`` is the reverse view a loader
+    needs during recovery: which objects of a container this rank can serve from its replicas."""
+
+    def __init__(self, root: str):
+        self.root = str(root)
+
+    def __call__(self, object_id: str, source_rank: int) -> str:
+        return os.path.join(self.root, f"src{source_rank}", str(object_id).lstrip("/"))
+
+    def held_objects(self, container_path: str) -> list:
+        """Original object paths of the replicas held here for ``container_path`` (any sender)."""
+        found = []
+        try:
+            senders = sorted(os.listdir(self.root))
+        except OSError:
+            return found
+        for sender in senders:
+            if not sender.startswith("src"):
+                continue
+            mirrored = os.path.join(self.root, sender, str(container_path).lstrip("/"))
+            try:
+                names = os.listdir(mirrored)
+            except OSError:
+                continue
+            found.extend(os.path.join(str(container_path), n) for n in names if not n.endswith(".tmp"))
+        return found
 
 
 class _DeviceBuffer:
@@ -207,6 +243,13 @@ class TransferService:
     @property
     def address(self) -> str:
         return f"{self._host}:{self._port}"
+
+    def held_device_bytes(self) -> int:
+        """HBM this service holds right now: landing buffers (one per source rank), outgrown ones kept
+        until shutdown, and the sender-side bounce buffer."""
+        with self._lock:
+            buffers = list(self._inbound.values()) + list(self._retired) + ([self._bounce] if self._bounce else [])
+        return sum(b.nbytes for b in buffers if b.ptr)
 
     def release_peers(self) -> None:
         """Closes the landing buffers of other processes that this service has opened.
@@ -339,6 +382,7 @@ class TransferService:
             if not reply.get("ok"):
                 raise RuntimeError(f"peer refused put of '{dest_object_id}': {reply.get('error')}")
             if reply.get("transport") == "tcp":
+                gpu_engine.wait_object_on_host(dest_object_id)  # a save of it may still be draining
                 source = (ctypes.c_ubyte * data_size).from_address(data_ptr)
                 sock.sendall(memoryview(source).cast("B"))
                 self.last_put_stats = {"bytes": data_size, "hop_ms": None, "from_hbm_image": False, "transport": "tcp"}
@@ -353,29 +397,53 @@ class TransferService:
             _native.check(lib.mlf_event_create(ctypes.byref(t0)))
             _native.check(lib.mlf_event_create(ctypes.byref(t1)))
             try:
-                if twin is not None:
-                    # metadata block from the host mapping, data section from the HBM image of the save
-                    with twin as image_ptr:
+                with contextlib.ExitStack() as lease:
+                    image_ptr = None
+                    if twin is not None:
+                        try:
+                            # waits for the pack kernel only: the hop overlaps the drain to the host
+                            image_ptr = lease.enter_context(twin)
+                        except RuntimeError:
+                            # a newer save or a restore took the arena between lookup and lease: the
+                            # object itself is complete in the host mapping, send it from there
+                            twin = None
+                    since_save_ms = None
+                    if image_ptr is not None:
+                        # metadata block from the host mapping (final since the bytes were claimed),
+                        # data section from the HBM image of the save
                         _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(peer), ctypes.c_void_p(data_ptr), METADATA_SIZE, _native.MLF_COPY_H2D, stream))
                         _native.check(lib.mlf_event_record(t0, stream))
                         _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer + METADATA_SIZE), ctypes.c_void_p(image_ptr), data_size - METADATA_SIZE, stream, 0))
                         _native.check(lib.mlf_event_record(t1, stream))
                         _native.check(lib.mlf_stream_sync(stream))
-                else:
-                    with self._lock:
-                        if self._bounce is None or self._bounce.nbytes < data_size:
-                            if self._bounce:
-                                self._bounce.free()
-                            self._bounce = _DeviceBuffer(data_size)
-                        bounce = self._bounce
-                    _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(bounce.ptr), ctypes.c_void_p(data_ptr), data_size, 1, 0))
-                    _native.check(lib.mlf_event_record(t0, stream))
-                    _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer), ctypes.c_void_p(bounce.ptr), data_size, stream, 0))
-                    _native.check(lib.mlf_event_record(t1, stream))
-                    _native.check(lib.mlf_stream_sync(stream))
+                        began = twin.start_event
+                        if began is not None:
+                            ms = ctypes.c_float()
+                            if lib.mlf_event_elapsed_ms(ctypes.c_void_p(began.cuda_event), t1, ctypes.byref(ms)) == 0:
+                                since_save_ms = float(ms.value)
+                    else:
+                        gpu_engine.wait_object_on_host(dest_object_id)
+                        with self._lock:
+                            if self._bounce is None or self._bounce.nbytes < data_size:
+                                if self._bounce:
+                                    self._bounce.free()
+                                self._bounce = _DeviceBuffer(data_size)
+                            bounce = self._bounce
+                        _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(bounce.ptr), ctypes.c_void_p(data_ptr), data_size, 1, 0))
+                        _native.check(lib.mlf_event_record(t0, stream))
+                        _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer), ctypes.c_void_p(bounce.ptr), data_size, stream, 0))
+                        _native.check(lib.mlf_event_record(t1, stream))
+                        _native.check(lib.mlf_stream_sync(stream))
                 ms = ctypes.c_float()
                 _native.check(lib.mlf_event_elapsed_ms(t0, t1, ctypes.byref(ms)))
-                self.last_put_stats = {"bytes": data_size, "hop_ms": float(ms.value), "from_hbm_image": twin is not None}
+                self.last_put_stats = {
+                    "bytes": data_size,
+                    "hop_ms": float(ms.value),
+                    "from_hbm_image": image_ptr is not None,
+                    # device time from the start of the save's pack kernel to the last byte in the peer's HBM
+                    "since_save_start_ms": since_save_ms,
+                    "in_peer_hbm_at": time.perf_counter(),
+                }
             finally:
                 lib.mlf_event_destroy(t0)
                 lib.mlf_event_destroy(t1)

@@ -228,6 +228,34 @@ def pack_object(tensors: Iterable[Tuple[str, object]], blobs: Iterable[Tuple[str
     return bytes(meta) + bytes(data), records
 
 
+def object_sha256(tensors: Sequence[Tuple[str, object]], blobs: Sequence[Tuple[str, bytes]] = ()) -> Tuple[str, int]:
+    """SHA-256 and size of the object ``pack_object`` would produce, without building it.
+
+    Meant for objects too large to hold in host memory a second time. The metadata block at offset 0
+    carries the length of the data section, so a first pass adds that length up from shapes and
+    dtypes alone; the second pass feeds the hash piece by piece: metadata block, then header and
+    payload of every tensor in bucket order, then the blobs. Tensors may live on any device; each
+    is brought to the host only while its payload is hashed.
+    """
+    import hashlib
+
+    length = 0
+    for _, tensor in tensors:
+        length += len(header_bytes(str(tensor.dtype).split(".")[-1], tuple(tensor.shape)))
+        length += tensor.numel() * tensor.element_size()
+    length += sum(len(b) for _, b in blobs)
+    digest = hashlib.sha256()
+    digest.update(struct.pack("<Q", length) + SIGNATURE_MLF + bytes(METADATA_SIZE - 16))
+    for _, tensor in tensors:
+        digest.update(header_bytes(str(tensor.dtype).split(".")[-1], tuple(tensor.shape)))
+        host = tensor if tensor.device.type == "cpu" else tensor.cpu()
+        digest.update(tensor_payload(host))
+        del host
+    for _, blob in blobs:
+        digest.update(blob)
+    return digest.hexdigest(), METADATA_SIZE + length
+
+
 def save_case(case: dict, prefix: str = "__0_", rank: int = 0):
     """Runs bucketing + naming + packing for a ``tests/golden/cases.py`` case.
 

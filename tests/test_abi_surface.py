@@ -67,6 +67,41 @@ def test_plan_validation_happens_before_any_device_work():
     assert lib.mlf_plan_image_extent(None) == 0
 
 
+def test_plan_rejects_shapes_whose_byte_arithmetic_overflows():
+    """Caller-supplied shapes and strides are multiplied with overflow checks: an extent that wraps
+    around 2^64 must never pass the image-capacity guard of a launch."""
+    from ml_flashpoint import _native
+
+    lib = _native.lib()
+    plan = ctypes.c_void_p()
+
+    def desc(shape, tstride, istride, esize=8, image_off=0):
+        d = (_native.CopyDesc * 1)()
+        d[0].tensor_ptr = 1 << 20
+        d[0].image_off = image_off
+        d[0].elem_size = esize
+        d[0].ndim = len(shape)
+        for k, (n, ts, st) in enumerate(zip(shape, tstride, istride)):
+            d[0].shape[k], d[0].tensor_stride[k], d[0].image_stride[k] = n, ts, st
+        return d
+
+    big = (1 << 62) + 1
+    cases = [
+        desc((1 << 31, 1 << 31, 4), (1 << 33, 4, 1), (1 << 33, 4, 1)),        # numel * elem_size wraps
+        desc((2, 2), (1, 1), (big, 1)),                                          # image span wraps
+        desc((2, 2), (big, 1), (2, 1)),                                          # tensor span wraps
+        desc((4,), (1,), (1,), esize=4, image_off=(1 << 64) - 8),               # image_off + extent wraps
+        desc((1 << 40, 1 << 21), (1 << 21, 1), (1 << 21, 1), esize=16),         # beyond the 2^62 byte bound
+    ]
+    for d in cases:
+        assert lib.mlf_plan_create(d, 1, _native.MLF_PACK, ctypes.byref(plan)) == _native.MLF_ERR_INVALID
+        assert b"overflow" in lib.mlf_last_error()
+    # an empty box is still fine whatever its other extents are
+    empty = desc((0, 1 << 62), (1, 1), (1, 1))
+    assert lib.mlf_plan_create(empty, 1, _native.MLF_PACK, ctypes.byref(plan)) == 0  # no tables, no device call
+    lib.mlf_plan_destroy(plan)
+
+
 def test_copy_desc_layout_matches_header():
     from ml_flashpoint import _native
 

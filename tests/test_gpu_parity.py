@@ -643,3 +643,77 @@ def test_single_tensor_larger_than_4_gib(shm_path, engine):
     make_loader(com, copy_engine=engine).read_data(buckets[0].object_id, [req], _Planner(), {idx: info})
     torch.cuda.synchronize()
     assert torch.equal(back, huge)
+
+
+def test_legacy_torch_save_format_on_the_gpu(shm_path, engine):
+    """``use_optimized_save=False``: every tensor travels as a ``torch.save`` stream under the
+    ``TORCH___`` signature, moved by the same pack kernel as byte items; the loader reads the streams
+    back (reference: core/checkpoint_saver.py:665-673, core/checkpoint_loader.py:212-218)."""
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    case = case_to_device(cases.CASES["mixed"](), "cuda")
+    _, com, ckpt, buckets, results = _save(case, shm_path, engine, use_optimized_save=False)
+    raw = open(str(buckets[0].object_id), "rb").read()
+    assert raw[8:16] == b"TORCH___"
+    assert int.from_bytes(raw[:8], "little") == len(raw) - 4096
+    # every tensor item is a self-contained torch.save stream holding the tensor's values
+    import io
+
+    by_fqn = {r.index.fqn: r for r in results}
+    for fqn, t in case["tensors"].items():
+        info = by_fqn[fqn].storage_data
+        stored = torch.load(io.BytesIO(raw[4096 + info.offset : 4096 + info.offset + info.length]), map_location="cpu", weights_only=True)
+        assert tensor_bytes(stored) == tensor_bytes(t), fqn
+    loader = make_loader(com, copy_engine=engine)
+    storage = {r.index: r.storage_data for r in results}
+    targets, blobs, reqs = {}, {}, []
+    for r in results:
+        fqn = r.index.fqn
+        if fqn in case["blobs"]:
+            reqs.append(ReadItem(LoadItemType.BYTE_IO, r.index, None, r.index, None, None))
+            continue
+        t = case["tensors"][fqn]
+        if t.numel() == 0:
+            continue
+        targets[fqn] = torch.zeros(t.shape, dtype=t.dtype, device="cuda")
+        reqs.append(ReadItem(LoadItemType.TENSOR, r.index, torch.Size([0] * t.dim()), r.index, torch.Size([0] * t.dim()), torch.Size(t.shape)))
+
+    class _Planner:
+        def resolve_tensor(self, req):
+            return targets[req.dest_index.fqn]
+
+        def commit_tensor(self, req, tensor):
+            pass
+
+        def load_bytes(self, req, value):
+            blobs[req.dest_index.fqn] = value.read()
+
+    loader.read_data(buckets[0].object_id, reqs, _Planner(), storage)
+    torch.cuda.synchronize()
+    for fqn, target in targets.items():
+        assert tensor_bytes(target) == tensor_bytes(case["tensors"][fqn]), fqn
+    assert blobs == dict(case["blobs"])
+
+
+def test_restore_converts_when_the_target_dtype_differs(tmp_path, engine):
+    """An fp32 checkpoint loaded into bf16 parameters: the reference's ``target.copy_(tensor)`` converts
+    (core/checkpoint_loader.py:331-336); here the block is unpacked in its stored dtype and converted."""
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    src = torch.randn(37, 53, device="cuda")
+    _, com, ckpt, buckets, results = _save({"tensors": {"w": src}, "blobs": {}, "bucket_count": 1}, tmp_path, engine)
+    loader = make_loader(com, copy_engine=engine)
+    idx = results[0].index
+    for device in ("cuda", "cpu"):
+        target = torch.zeros(5, 53, dtype=torch.bfloat16, device=device)
+        req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0, 0]), idx, torch.Size([3, 0]), torch.Size([5, 53]))
+
+        class _Planner:
+            def resolve_tensor(self, r):
+                return target
+
+            def commit_tensor(self, r, t):
+                pass
+
+        loader.read_data(buckets[0].object_id, [req], _Planner(), {idx: results[0].storage_data})
+        assert torch.equal(target.cpu(), src[3:8].to(torch.bfloat16).cpu())

@@ -257,3 +257,26 @@ def test_missing_object_is_fetched_from_the_rank_that_holds_it(tmp_path):
     assert loader._try_retrieve_object_if_missing(oid) is True
     assert fetched == [(3, [str(oid)])]
     assert loader._try_retrieve_object_if_missing(oid) is True and len(fetched) == 1  # present now
+
+
+def test_replica_namespace_maps_and_lists_back(tmp_path):
+    """Replicas of ranks that share a filesystem live under ``<root>/src<sender>/<object path>``; the
+    reverse listing reports them under their original paths (what a loader advertises in recovery)."""
+    from ml_flashpoint.replication.transfer_service.transfer_service_ext import ReplicaNamespace
+
+    space = ReplicaNamespace(str(tmp_path / "replicas"))
+    container = "/job/ckpt/step-5_ckpt"
+    assert space.held_objects(container) == []  # nothing received yet, the root does not even exist
+    a = space(f"{container}/__0__0_src0.distcp", 0)
+    b = space(f"{container}/__3__0_src3.distcp", 3)
+    assert a == str(tmp_path / "replicas" / "src0" / "job/ckpt/step-5_ckpt/__0__0_src0.distcp")
+    for path in (a, b, b + ".tmp", space("/job/ckpt/step-4_ckpt/__0__0_src0.distcp", 0)):
+        _touch(path)
+    assert sorted(space.held_objects(container)) == [f"{container}/__0__0_src0.distcp", f"{container}/__3__0_src3.distcp"]
+
+    loader = make_loader(CheckpointObjectManager(), copy_engine=NumpyCopyEngine(), rank=1, world=2)
+    loader._replica_namespace = space
+    import pathlib
+
+    extra = loader._get_extra_local_objects(pathlib.Path(container))
+    assert sorted(str(o) for o in extra) == sorted(space.held_objects(container))

@@ -228,3 +228,26 @@ def test_overlapped_save_api_publishes_the_same_objects(tmp_path, golden_dir):
         assert open(str(bucket.object_id), "rb").read() == golden_object_bytes(golden_dir, g)
     got = sorted((r.storage_data.relative_path, r.storage_data.offset, r.storage_data.length) for r in results)
     assert got == [(w["relative_path"], w["offset"], w["length"]) for w in gold["write_results"]]
+
+
+def test_load_converts_to_the_target_dtype(tmp_path):
+    """The reference ends a read in ``target.copy_(tensor)``, which converts dtypes (fp32 checkpoint
+    into bf16 parameters): the loader unpacks in the stored dtype and converts afterwards."""
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    src = torch.randn(6, 10)
+    _, com, ckpt, buckets, results = _save({"tensors": {"w": src}, "blobs": {}, "bucket_count": 1}, tmp_path)
+    loader = make_loader(com, copy_engine=NumpyCopyEngine())
+    idx = results[0].index
+    target = torch.zeros(2, 10, dtype=torch.bfloat16)
+    req = ReadItem(LoadItemType.TENSOR, idx, torch.Size([0, 0]), idx, torch.Size([1, 0]), torch.Size([2, 10]))
+
+    class _P:
+        def resolve_tensor(self, r):
+            return target
+
+        def commit_tensor(self, r, t):
+            pass
+
+    loader.read_data(buckets[0].object_id, [req], _P(), {idx: results[0].storage_data})
+    assert torch.equal(target, src[1:3].to(torch.bfloat16))

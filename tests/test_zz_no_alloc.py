@@ -16,6 +16,8 @@ import ctypes
 import pytest
 import torch
 
+import mlf_oracle as oracle
+
 pytestmark = pytest.mark.gpu
 
 
@@ -87,6 +89,33 @@ def test_noalloc_pack_matches_plan_pack_on_consecutive_calls():
         torch.cuda.synchronize()
         assert torch.equal(got, want)
         assert int((want != 0x5A).sum()) > 0  # the reference image was actually written
+        # and directly against the CPU oracle: every payload is the tensor's logical C-order bytes
+        image = bytes(got.cpu().numpy())
+        for t, off in zip(tensors, offsets):
+            raw = oracle.tensor_payload(t.cpu())
+            assert image[off : off + len(raw)] == raw
+
+
+def test_noalloc_pack_on_a_stream_of_the_callers():
+    """The tables are uploaded on the caller's stream ahead of the kernel, so a non-default stream
+    works the same; the call may wait for earlier work on that stream (pageable upload)."""
+    from ml_flashpoint import _native
+
+    lib = _native.lib()
+    side = torch.cuda.Stream()
+    tensors, _ = _tensor_sets()
+    offsets, total = _layout(tensors, 9)
+    descs = _descs_for(tensors, offsets)
+    want = torch.zeros(total + 64, dtype=torch.uint8, device="cuda")
+    got = torch.zeros(total + 64, dtype=torch.uint8, device="cuda")
+    _pack_with_plan(descs, len(tensors), want)
+    torch.cuda.synchronize()  # the inputs were produced on the default stream
+    for _ in range(2):
+        got.zero_()
+        torch.cuda.synchronize()
+        _native.check(lib.mlf_pack_noalloc(descs, len(tensors), ctypes.c_void_p(got.data_ptr()), got.numel(), ctypes.c_void_p(side.cuda_stream)))
+        side.synchronize()
+        assert torch.equal(got, want)
 
 
 def test_noalloc_pack_rejects_oversized_and_out_of_window_requests():

@@ -148,3 +148,34 @@ def moe_expert_parallel_rank_full_size(device, rank=0, layers=32, d_model=4096, 
         if t.device.type == "cpu":
             tensors[name] = t
     return {"tensors": tensors, "blobs": small["blobs"], "bucket_count": 1}
+
+
+def gpt2_small_adam(device, seed=0, layers=12, d_model=768, d_ff=3072, vocab=50257, ctx=1024):
+    """GPT-2 small (tied embeddings, 124 439 808 parameters) with Adam state, all fp32: weights
+    N(0, 0.02) with LayerNorm gains 1.0, ``exp_avg`` N(0, 1e-3), ``exp_avg_sq`` its square-law
+    counterpart, and one int64 ``step`` scalar (1000) per parameter: 12 bytes per parameter, 1.49 GB.
+    Values are drawn on ``device`` from a generator seeded with ``seed`` alone, so every rank of a
+    data-parallel job (same device type) holds the same replica."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    shapes = [("transformer.wte.weight", (vocab, d_model)), ("transformer.wpe.weight", (ctx, d_model))]
+    for i in range(layers):
+        p = f"transformer.h.{i}."
+        shapes += [
+            (p + "ln_1.weight", (d_model,)), (p + "ln_1.bias", (d_model,)),
+            (p + "attn.c_attn.weight", (d_model, 3 * d_model)), (p + "attn.c_attn.bias", (3 * d_model,)),
+            (p + "attn.c_proj.weight", (d_model, d_model)), (p + "attn.c_proj.bias", (d_model,)),
+            (p + "ln_2.weight", (d_model,)), (p + "ln_2.bias", (d_model,)),
+            (p + "mlp.c_fc.weight", (d_model, d_ff)), (p + "mlp.c_fc.bias", (d_ff,)),
+            (p + "mlp.c_proj.weight", (d_ff, d_model)), (p + "mlp.c_proj.bias", (d_model,)),
+        ]
+    shapes += [("transformer.ln_f.weight", (d_model,)), ("transformer.ln_f.bias", (d_model,))]
+    state = {}
+    for name, shape in shapes:
+        w = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02
+        if ".ln_" in name and name.endswith("weight"):
+            w.fill_(1.0)
+        state["model." + name] = w
+        state["optim.exp_avg." + name] = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 1e-3
+        state["optim.exp_avg_sq." + name] = (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 1e-3) ** 2
+        state["optim.step." + name] = torch.tensor(1000, dtype=torch.int64, device=device)
+    return state
