@@ -77,6 +77,21 @@ int32_t mlf_buf_is_registered(const mlf_buf* b);
  * through the descriptor avoids faulting the whole object into the mapping. `nthreads` 0 = half
  * the cores. */
 int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads);
+/* The same read with a second kind of worker beside the pread() threads: one "lock lane" that maps
+ * the object's file writable, page-locks `lock_run_mib` MiB of it at a time (cudaHostRegister), lets
+ * a copy engine read that piece in place, and unlocks it, one piece ahead of the previous piece's
+ * transfer. Both kinds of worker draw from the same range (the threads from its front, the lane
+ * from its back) until they meet, so the split follows their speeds. Page-locking moves several
+ * times more bytes per CPU core than pread(), but the driver serialises it within a process, so
+ * there is one lane; it pays off where the cores, not the host link, bound a restore (several
+ * ranks restoring at once on one host). Needs write permission on the file (nothing is written);
+ * without it, or if locking fails, the threads move everything. lock_run_mib = 0 is
+ * mlf_buf_read_to_device. Same reference counterpart: the loader's per-tensor host reads
+ * (core/checkpoint_loader.py:177-219). */
+int32_t mlf_buf_read_to_device_hybrid(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads,
+                                      int32_t lock_run_mib);
+/* Bytes the lock lane moved during the most recent read in this process (0 if it did not run). */
+uint64_t mlf_last_lock_lane_bytes(void);
 /* Device-visible address of byte 0 of the mapping (requires registration). */
 int32_t mlf_buf_dev_ptr(const mlf_buf* b, void** out);
 

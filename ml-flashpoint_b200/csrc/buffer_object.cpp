@@ -423,7 +423,8 @@ int32_t mlf_buf_unregister(mlf_buf* b) {
   return drop_registration(b);
 }
 
-int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads) {
+static int32_t read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads,
+                              int32_t lock_run_mib) {
   if (!b) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_read_to_device: null buffer");
   if (b->closed) return mlf::fail(MLF_ERR_CLOSED, "buffer is closed: " + b->id);
   if (offset > b->capacity || nbytes > b->capacity - offset)
@@ -442,7 +443,19 @@ int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr,
     MLF_CUDA(cudaStreamSynchronize(0));
     return MLF_OK;
   }
-  return mlf::bounce_transfer(dev_ptr, nullptr, b->fd, offset, nbytes, 1, nthreads);
+  // units of the bounce ring are 4 MiB unless tuned otherwise; a run is given in MiB to stay independent of that
+  const uint32_t run_units = lock_run_mib > 0 ? (uint32_t)std::max<int64_t>(1, (int64_t)lock_run_mib / 4) : 0;
+  return mlf::bounce_transfer(dev_ptr, nullptr, b->fd, offset, nbytes, 1, nthreads, run_units ? b->id.c_str() : nullptr, run_units);
+}
+
+int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads) {
+  return read_to_device(b, offset, dev_ptr, nbytes, nthreads, 0);
+}
+
+int32_t mlf_buf_read_to_device_hybrid(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads,
+                                      int32_t lock_run_mib) {
+  if (lock_run_mib < 0) return mlf::fail(MLF_ERR_INVALID, "mlf_buf_read_to_device_hybrid: negative run size");
+  return read_to_device(b, offset, dev_ptr, nbytes, nthreads, lock_run_mib);
 }
 
 int32_t mlf_buf_dev_ptr(const mlf_buf* b, void** out) {

@@ -22,7 +22,7 @@ void clear_error();
 extern std::atomic<uint64_t> g_launches;
 
 int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off, uint64_t nbytes, int32_t to_device,
-                        int32_t nthreads);
+                        int32_t nthreads, const char* lock_path, uint32_t lock_run_units);
 
 // Calls fn(piece, length) for consecutive pieces of the host range [p, p + n), cut wherever a
 // range page-locked by this library starts or ends: a copy-engine transfer must stay inside one

@@ -1,8 +1,10 @@
 // Thin entry points around CUDA runtime services: copy-engine transfers, library-owned memory,
 // IPC handles for peer replication, streams and events. Kept free of any policy so that the
 // Python host code decides what overlaps with what.
+#include <fcntl.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -45,6 +47,7 @@ struct BounceRing {
   int device = -1;
 };
 BounceRing g_ring;
+std::atomic<uint64_t> g_last_lane_bytes{0};  // bytes the lock lane moved in the most recent transfer
 
 cudaError_t ensure_slots(int workers) {
   for (int i = 0; i < workers * 2; ++i) {
@@ -93,22 +96,62 @@ namespace mlf {
 // address (`host_ptr`) or, for host -> device only, a file descriptor read with pread() at
 // `file_off`: reading through the descriptor copies straight from the page cache into the
 // page-locked slot and never builds (or tears down) page tables for the object.
+//
+// The range is cut into units on a grid of chunk_bytes() in the source's own address space (file
+// offsets for a descriptor), so that unit boundaries fall on page boundaries of the file. Units are
+// handed out dynamically from one shared range: the bounce workers take single units from the
+// front; an optional "lock lane" (`lock_path` given, host -> device only) takes runs of units from
+// the back, page-locks that piece of a writable mapping of the file, lets a copy engine read it in
+// place and unlocks it again, one piece ahead of the transfer of the previous one. The two kinds of
+// worker meet wherever their speeds put the meeting point. Page-locking costs a core far less per
+// byte than pread() does, but the driver serialises it within a process, hence one lane.
 int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off, uint64_t nbytes, int32_t to_device,
-                        int32_t nthreads) {
+                        int32_t nthreads, const char* lock_path, uint32_t lock_run_units) {
   if (nbytes == 0) return MLF_OK;
   if (!dev_ptr || (!host_ptr && fd < 0)) return mlf::fail(MLF_ERR_INVALID, "bounce transfer: null pointer");
   int workers = nthreads > 0 ? nthreads : (int)std::max(1u, std::thread::hardware_concurrency() / 2);
   workers = std::min(workers, kMaxWorkers);
   const uint64_t chunk = chunk_bytes();
-  const uint64_t nchunks = (nbytes + chunk - 1) / chunk;
-  workers = (int)std::min<uint64_t>((uint64_t)workers, nchunks);
+  const uint64_t space0 = fd >= 0 ? file_off : 0;  // first byte in the source's address space
+  const uint64_t space1 = space0 + nbytes;
+  const uint64_t unit0 = space0 / chunk, unit1 = (space1 + chunk - 1) / chunk;
+  workers = (int)std::min<uint64_t>((uint64_t)workers, unit1 - unit0);
+  const bool lane_wanted = lock_path && to_device && fd >= 0 && lock_run_units > 0 && (unit1 - unit0) >= 4ull * lock_run_units;
   int dev = 0;
   MLF_CUDA(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> hold(g_ring.mu);
   MLF_CUDA(ensure_slots(workers));
 
+  std::mutex claim_mu;
+  uint64_t next_front = unit0, next_back = unit1;  // unclaimed units: [next_front, next_back)
+  auto claim_front = [&](uint64_t* u) {
+    std::lock_guard<std::mutex> g(claim_mu);
+    if (next_front >= next_back) return false;
+    *u = next_front++;
+    return true;
+  };
+  auto claim_back = [&](uint64_t* lo, uint64_t* hi) {
+    std::lock_guard<std::mutex> g(claim_mu);
+    if (next_front >= next_back) return false;
+    *hi = next_back;
+    *lo = next_back - std::min<uint64_t>(lock_run_units, next_back - next_front);
+    next_back = *lo;
+    return true;
+  };
+  auto unit_range = [&](uint64_t lo_unit, uint64_t hi_unit, uint64_t* begin, uint64_t* len) {
+    const uint64_t b = std::max(space0, lo_unit * chunk), e = std::min(space1, hi_unit * chunk);
+    *begin = b;
+    *len = e - b;
+  };
+
   std::atomic<int> first_error{(int)cudaSuccess};
   std::atomic<bool> io_failed{false};
+  std::atomic<uint64_t> lane_bytes{0};
+  auto note_error = [&](cudaError_t e) {
+    if (e == cudaSuccess) return;
+    int expected = (int)cudaSuccess;
+    first_error.compare_exchange_strong(expected, (int)e);
+  };
   auto run = [&](int w) {
     cudaError_t e = cudaSetDevice(dev);
     cudaStream_t stream = nullptr;
@@ -118,9 +161,11 @@ int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off
     bool used[2] = {false, false};
     uint64_t pending_off[2] = {0, 0}, pending_len[2] = {0, 0};
     int turn = 0;
-    for (uint64_t c = (uint64_t)w; c < nchunks && e == cudaSuccess; c += (uint64_t)workers, turn ^= 1) {
-      const uint64_t off = c * chunk;
-      const uint64_t len = std::min(chunk, nbytes - off);
+    uint64_t u = 0;
+    for (; e == cudaSuccess && claim_front(&u); turn ^= 1) {
+      uint64_t begin = 0, len = 0;
+      unit_range(u, u + 1, &begin, &len);
+      const uint64_t off = begin - space0;  // offset in the device range (and in host_ptr)
       char* slot = static_cast<char*>(g_ring.slots[w * 2 + turn]);
       if (used[turn]) {
         e = cudaEventSynchronize(done[turn]);  // the slot's previous transfer has left (or arrived)
@@ -131,7 +176,7 @@ int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off
         if (fd >= 0) {
           uint64_t got = 0;
           while (got < len) {
-            const ssize_t n = pread(fd, slot + got, len - got, (off_t)(file_off + off + got));
+            const ssize_t n = pread(fd, slot + got, len - got, (off_t)(begin + got));
             if (n <= 0) {
               io_failed.store(true);
               break;
@@ -165,15 +210,80 @@ int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off
     for (int k = 0; k < 2; ++k)
       if (done[k]) cudaEventDestroy(done[k]);
     if (stream) cudaStreamDestroy(stream);
-    if (e != cudaSuccess) {
-      int expected = (int)cudaSuccess;
-      first_error.compare_exchange_strong(expected, (int)e);
-    }
+    note_error(e);
   };
+
+  // The lock lane. Any failure to set it up (the file cannot be opened for writing, the mapping
+  // cannot be locked) simply ends the lane: the bounce workers take the rest of the range.
+  auto lane = [&]() {
+    if (cudaSetDevice(dev) != cudaSuccess) return;
+    const int wfd = open(lock_path, O_RDWR | O_CLOEXEC);
+    if (wfd < 0) return;
+    const uint64_t page = (uint64_t)sysconf(_SC_PAGESIZE);
+    const uint64_t map_len = (space1 + page - 1) / page * page;
+    void* map = mmap(nullptr, map_len, PROT_READ | PROT_WRITE, MAP_SHARED, wfd, 0);
+    close(wfd);
+    if (map == MAP_FAILED) return;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaError_t e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+    for (int k = 0; k < 2 && e == cudaSuccess; ++k) e = cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming);
+    char* locked[2] = {nullptr, nullptr};
+    int turn = 0;
+    bool give_up = false;
+    uint64_t lo = 0, hi = 0;
+    while (e == cudaSuccess && !give_up && claim_back(&lo, &hi)) {
+      uint64_t begin = 0, len = 0;
+      unit_range(lo, hi, &begin, &len);
+      if (locked[turn]) {  // two pieces in flight at most: finish and unlock the older one
+        e = cudaEventSynchronize(done[turn]);
+        if (e == cudaSuccess) e = cudaHostUnregister(locked[turn]);
+        locked[turn] = nullptr;
+        if (e != cudaSuccess) break;
+      }
+      // page-aligned outwards: inner boundaries lie on the unit grid, only the two ends of the whole
+      // transfer can be ragged, and no other piece shares their pages
+      const uint64_t lock_begin = begin / page * page, lock_end = std::min(map_len, (begin + len + page - 1) / page * page);
+      char* piece = static_cast<char*>(map) + lock_begin;
+      cudaError_t le = cudaHostRegister(piece, lock_end - lock_begin, cudaHostRegisterPortable);
+      if (le != cudaSuccess) {
+        // cannot lock (limits, or memory that cannot be pinned): move this piece the plain way and stop
+        (void)cudaGetLastError();
+        e = cudaMemcpyAsync(static_cast<char*>(dev_ptr) + (begin - space0), static_cast<char*>(map) + begin, len,
+                            cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        give_up = true;
+        break;
+      }
+      locked[turn] = piece;
+      e = cudaMemcpyAsync(static_cast<char*>(dev_ptr) + (begin - space0), static_cast<char*>(map) + begin, len,
+                          cudaMemcpyHostToDevice, stream);
+      if (e == cudaSuccess) e = cudaEventRecord(done[turn], stream);
+      lane_bytes.fetch_add(len);
+      turn ^= 1;
+    }
+    if (stream) {
+      cudaError_t se = cudaStreamSynchronize(stream);
+      if (e == cudaSuccess) e = se;
+    }
+    for (int k = 0; k < 2; ++k) {
+      if (locked[k]) {
+        cudaError_t ue = cudaHostUnregister(locked[k]);
+        if (e == cudaSuccess) e = ue;
+      }
+      if (done[k]) cudaEventDestroy(done[k]);
+    }
+    if (stream) cudaStreamDestroy(stream);
+    munmap(map, map_len);
+    note_error(e);
+  };
+
   std::vector<std::thread> pool;
+  if (lane_wanted) pool.emplace_back(lane);
   for (int w = 1; w < workers; ++w) pool.emplace_back(run, w);
   run(0);
   for (auto& t : pool) t.join();
+  g_last_lane_bytes.store(lane_bytes.load());
   if (first_error.load() != (int)cudaSuccess) {
     (void)cudaGetLastError();
     return mlf::cuda_fail((cudaError_t)first_error.load(), "pipelined bounce copy");
@@ -187,8 +297,10 @@ extern "C" {
 
 int32_t mlf_bounce_copy(void* dev_ptr, void* host_ptr, uint64_t nbytes, int32_t to_device, int32_t nthreads) {
   if (nbytes > 0 && !host_ptr) return mlf::fail(MLF_ERR_INVALID, "mlf_bounce_copy: null pointer");
-  return mlf::bounce_transfer(dev_ptr, host_ptr, -1, 0, nbytes, to_device, nthreads);
+  return mlf::bounce_transfer(dev_ptr, host_ptr, -1, 0, nbytes, to_device, nthreads, nullptr, 0);
 }
+
+uint64_t mlf_last_lock_lane_bytes(void) { return g_last_lane_bytes.load(); }
 
 int32_t mlf_dev_alloc(uint64_t nbytes, void** out) {
   if (!out) return mlf::fail(MLF_ERR_INVALID, "mlf_dev_alloc: null out");

@@ -78,6 +78,8 @@ _SIGNATURES = {
     "mlf_buf_unregister": (c_int32, [c_void_p]),
     "mlf_buf_is_registered": (c_int32, [c_void_p]),
     "mlf_buf_read_to_device": (c_int32, [c_void_p, c_uint64, c_void_p, c_uint64, c_int32]),
+    "mlf_buf_read_to_device_hybrid": (c_int32, [c_void_p, c_uint64, c_void_p, c_uint64, c_int32, c_int32]),
+    "mlf_last_lock_lane_bytes": (c_uint64, []),
     "mlf_buf_dev_ptr": (c_int32, [c_void_p, POINTER(c_void_p)]),
     "mlf_plan_create": (c_int32, [POINTER(CopyDesc), c_uint64, c_int32, POINTER(c_void_p)]),
     "mlf_plan_destroy": (None, [c_void_p]),

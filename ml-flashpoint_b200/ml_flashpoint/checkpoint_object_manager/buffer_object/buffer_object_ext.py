@@ -91,12 +91,18 @@ class BufferObject:
         _native.check(_native.lib().mlf_buf_dev_ptr(self._handle, ctypes.byref(out)))
         return int(out.value or 0)
 
-    def read_to_device(self, offset: int, device_ptr: int, nbytes: int, threads: int = 0) -> None:
+    def read_to_device(self, offset: int, device_ptr: int, nbytes: int, threads: int = 0, lock_run_mib: int = 0) -> int:
         """Blocking copy of object bytes ``[offset, offset + nbytes)`` into device memory through the
-        page-locked bounce ring, reading the file descriptor rather than the mapping."""
+        page-locked bounce ring, reading the file descriptor rather than the mapping. With
+        ``lock_run_mib`` > 0 a lock lane works beside the ring's threads: it page-locks that many MiB
+        of the file at a time and lets a copy engine read them in place. Returns the bytes the lane
+        moved (0 without one)."""
         _native.check(
-            _native.lib().mlf_buf_read_to_device(self._handle, int(offset), ctypes.c_void_p(device_ptr), int(nbytes), int(threads))
+            _native.lib().mlf_buf_read_to_device_hybrid(
+                self._handle, int(offset), ctypes.c_void_p(device_ptr), int(nbytes), int(threads), int(lock_run_mib)
+            )
         )
+        return int(_native.lib().mlf_last_lock_lane_bytes()) if lock_run_mib > 0 else 0
 
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None

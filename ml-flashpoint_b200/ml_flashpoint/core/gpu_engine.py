@@ -163,6 +163,15 @@ def default_host_threads(share: float = 0.5) -> int:
     return max(2, int((os.cpu_count() or 2) * share) // local_world)
 
 
+def default_restore_lock_run_mib() -> int:
+    """Whether a restore runs its lock lane, and with which run size. The lane relieves the CPU
+    threads of part of the object; it pays where several ranks share one host's cores."""
+    import os
+
+    local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))
+    return 256 if local_world > 1 else 0
+
+
 # ======================================================================================
 # CUDA engine
 # ======================================================================================
@@ -288,6 +297,12 @@ class CudaCopyEngine:
         self.host_threads = get_env_val_int("GPU_HOST_THREADS", default_host_threads())
         # a restore runs before training starts, with the host otherwise idle: it may use every core
         self.restore_threads = get_env_val_int("GPU_RESTORE_THREADS", default_host_threads(1.0))
+        # MiB the restore's lock lane page-locks at a time (0 = no lane, CPU threads only); see
+        # ``mlf_buf_read_to_device_hybrid``. -1 = decide from the ranks that share this host's cores.
+        self.restore_lock_run_mib = get_env_val_int("GPU_RESTORE_LOCK_RUN_MIB", -1)
+        if self.restore_lock_run_mib < 0:
+            self.restore_lock_run_mib = default_restore_lock_run_mib()
+        self.last_lock_lane_bytes = 0
         self._lock = threading.RLock()
         self._cache: "OrderedDict[tuple, _CachedPack]" = OrderedDict()
         self._cache_size = plan_cache_size
@@ -559,7 +574,9 @@ class CudaCopyEngine:
         if reader is not None:
             from ml_flashpoint.checkpoint_object_manager.buffer_metadata import METADATA_SIZE
 
-            reader(METADATA_SIZE + lo, image.data_ptr(), nbytes, self.restore_threads)
+            self.last_lock_lane_bytes = reader(
+                METADATA_SIZE + lo, image.data_ptr(), nbytes, self.restore_threads, self.restore_lock_run_mib
+            ) or 0
         else:
             _native.check(
                 _native.lib().mlf_bounce_copy(

@@ -3,9 +3,10 @@
     python oracle/build_ref.py /path/to/ml-flashpoint
 
 Every ``*.py`` under ``<reference root>/src/ml_flashpoint`` is compiled where it lies with
-``py_compile`` and only the resulting sourceless ``.pyc`` files are written, mirroring the package
-tree under ``oracle/_ref/ml_flashpoint``. No reference source is copied. ``oracle/_ref`` is a
-build output: it is ignored by git and rebuilt from a reference checkout by this recipe.
+``py_compile`` and only the resulting sourceless bytecode is kept, packed into one archive,
+``oracle/_ref/reference_bytecode.zip``, that mirrors the package tree (Python imports sourceless
+``.pyc`` files straight from a zip on ``sys.path``). No reference source is copied. ``oracle/_ref``
+is a build output: it is ignored by git and rebuilt from a reference checkout by this recipe.
 
 The two compiled extension modules of the reference (``buffer_object_ext``, ``transfer_service_ext``)
 cannot be built offline (their CMake build fetches abseil and googletest); ``ref_arm.py`` registers
@@ -61,35 +62,42 @@ def is_current(ref_root: str = DEFAULT_REFERENCE_ROOT) -> bool:
     return want == manifest.get("sources")
 
 
+ARCHIVE = os.path.join(OUT, "reference_bytecode.zip")
+
+
 def build(ref_root: str = DEFAULT_REFERENCE_ROOT, force: bool = False) -> str:
+    import tempfile
+    import zipfile
+
     if not reference_available(ref_root):
         raise FileNotFoundError(f"no reference checkout at {ref_root} (expected src/ml_flashpoint/__init__.py)")
-    if not force and is_current(ref_root):
+    if not force and is_current(ref_root) and os.path.isfile(ARCHIVE):
         return OUT
     shutil.rmtree(OUT, ignore_errors=True)
+    os.makedirs(OUT)
     hashes = {}
-    # directories that hold only compiled extensions are still packages the Python side imports from
-    # (namespace packages): mirror the directory tree, empty where there is no Python
-    base = os.path.join(ref_root, "src", "ml_flashpoint")
-    for folder, _, _ in os.walk(base):
-        mirrored = os.path.join(OUT, os.path.relpath(folder, os.path.join(ref_root, "src")))
-        os.makedirs(mirrored, exist_ok=True)
-        open(os.path.join(mirrored, ".keep"), "w").close()  # tools that copy trees may drop empty directories
-    for path, rel in _sources(ref_root):
-        target = os.path.join(OUT, rel + "c")  # pkg/mod.py -> pkg/mod.pyc, importable without the source
-        os.makedirs(os.path.dirname(target), exist_ok=True)
-        py_compile.compile(
-            path,
-            cfile=target,
-            dfile=os.path.join("<reference>", rel),
-            doraise=True,
-            invalidation_mode=py_compile.PycInvalidationMode.UNCHECKED_HASH,
-        )
-        hashes[rel] = _sha(path)
+    src_root = os.path.join(ref_root, "src")
+    with tempfile.TemporaryDirectory() as scratch, zipfile.ZipFile(ARCHIVE, "w", zipfile.ZIP_STORED) as archive:
+        # directories that hold only compiled extensions are still packages the Python side imports
+        # from (namespace packages): every directory of the tree gets an entry, Python or not
+        for folder, _, _ in sorted(os.walk(os.path.join(src_root, "ml_flashpoint"))):
+            archive.writestr(zipfile.ZipInfo(os.path.relpath(folder, src_root) + "/"), b"")
+        for path, rel in _sources(ref_root):
+            compiled = os.path.join(scratch, "module.pyc")
+            py_compile.compile(
+                path,
+                cfile=compiled,
+                dfile=os.path.join("<reference>", rel),
+                doraise=True,
+                invalidation_mode=py_compile.PycInvalidationMode.UNCHECKED_HASH,
+            )
+            archive.write(compiled, rel + "c")  # pkg/mod.py -> pkg/mod.pyc, importable without the source
+            hashes[rel] = _sha(path)
     import torch
 
     manifest = {
         "what": "byte-compiled reference package (ml_flashpoint), no sources",
+        "archive": os.path.basename(ARCHIVE),
         "magic": importlib.util.MAGIC_NUMBER.hex(),
         "python": sys.version.split()[0],
         "torch": torch.__version__,

@@ -1,8 +1,8 @@
 """Times the reference's own CPU save / restore path from ``oracle/_ref`` (TEST INFRASTRUCTURE).
 
 Only the benchmark's reference arm, its CPU-baseline leg and the tests may import this module.
-``oracle/_ref`` holds the reference package byte-compiled by ``build_ref.py``; this module makes it
-importable (two stand-in extension modules, see below) and drives, per emulated rank, exactly what
+``oracle/_ref`` holds the reference package byte-compiled by ``build_ref.py`` (one zip archive of
+sourceless ``.pyc`` files); this module makes it importable (two stand-in extension modules, see below) and drives, per emulated rank, exactly what
 the reference does for one save of GPU-resident state:
 
   stage    ``MemoryStorageWriter.stage_write_data_buckets`` (adapter/pytorch/memory_storage_writer.py:211-233):
@@ -39,6 +39,7 @@ import types
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")
+REF_ARCHIVE = os.path.join(REF_DIR, "reference_bytecode.zip")  # sourceless .pyc files, imported by zipimport
 POOL_BUFFERS = 2  # NUM_OF_BUFFERS_PER_OBJECT x write_thread_count (adapter/nemo/wrapper_util.py:47, 95)
 POOL_BUFFER_BYTES = 16 * 1024**3  # DEFAULT_INITIAL_BUFFER_SIZE_BYTES (core/checkpoint_saver.py)
 
@@ -52,6 +53,8 @@ def unavailable_reason() -> str | None:
         return "oracle/_ref is not built (run oracle/build_ref.py against a reference checkout)"
     if manifest.get("magic") != importlib.util.MAGIC_NUMBER.hex():
         return f"oracle/_ref was compiled by Python {manifest.get('python')}, not by this interpreter"
+    if not os.path.isfile(REF_ARCHIVE):
+        return "oracle/_ref holds a manifest but no bytecode archive (rebuild it with oracle/build_ref.py)"
     return None
 
 
@@ -121,7 +124,7 @@ def install() -> None:
     loaded = sys.modules.get("ml_flashpoint")
     if loaded is not None:
         origin = os.path.dirname(getattr(loaded, "__file__", "") or "")
-        if not origin.startswith(REF_DIR):
+        if not origin.startswith(REF_ARCHIVE):
             raise RuntimeError(f"another ml_flashpoint package is already imported from {origin}")
         return
     buf = types.ModuleType("ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext")
@@ -131,12 +134,12 @@ def install() -> None:
     xfer.TransferService = type("TransferService", (), {})
     xfer.TransferResult = type("TransferResult", (), {})
     sys.modules[xfer.__name__] = xfer
-    sys.path.insert(0, REF_DIR)
+    sys.path.insert(0, REF_ARCHIVE)
     os.environ.setdefault("MLFLASHPOINT_LOG_LEVEL", "ERROR")
     import ml_flashpoint
 
     origin = os.path.dirname(ml_flashpoint.__file__)
-    if not origin.startswith(REF_DIR):
+    if not origin.startswith(REF_ARCHIVE):
         raise RuntimeError(f"ml_flashpoint resolved to {origin}, not to the reference build")
 
 

@@ -717,3 +717,30 @@ def test_restore_converts_when_the_target_dtype_differs(tmp_path, engine):
 
         loader.read_data(buckets[0].object_id, [req], _Planner(), {idx: results[0].storage_data})
         assert torch.equal(target.cpu(), src[3:8].to(torch.bfloat16).cpu())
+
+
+@pytest.mark.parametrize("offset,trim", [(4096, 0), (4096 + 48, 12345)])
+def test_hybrid_restore_read_moves_exactly_the_files_bytes(shm_path, offset, trim):
+    """Restore feed with the lock lane beside the pread() threads: whatever share either side
+    takes, HBM ends up holding exactly the requested bytes of the object, for page-aligned and
+    ragged ends alike; with the file made read-only the lane cannot start and the threads move all."""
+    from ml_flashpoint import _native
+    from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+    nbytes = (192 << 20) + 4096 + 777
+    data = np.random.default_rng(5).integers(0, 256, nbytes, dtype=np.uint8)
+    path = str(shm_path / "object.bin")
+    data.tofile(path)
+    want = torch.from_numpy(data[offset : nbytes - trim])
+    for writable in (True, False):
+        os.chmod(path, 0o644 if writable else 0o444)
+        obj = BufferObject(path)
+        got = torch.zeros(want.numel(), dtype=torch.uint8, device="cuda")
+        lane = obj.read_to_device(offset, got.data_ptr(), want.numel(), threads=3, lock_run_mib=16)
+        torch.cuda.synchronize()
+        assert torch.equal(got.cpu(), want)
+        assert 0 <= lane <= want.numel()
+        if not writable and os.geteuid() != 0:
+            assert lane == 0
+        obj.close()
+    assert int(_native.lib().mlf_last_lock_lane_bytes()) >= 0

@@ -24,9 +24,12 @@ def test_build_recipe_outputs_bytecode_only():
         pytest.skip("no reference checkout on this machine")
     out = build_ref.build()
     assert build_ref.is_current()
-    kinds = {os.path.splitext(n)[1] for _, _, names in os.walk(out) for n in names}
-    assert kinds <= {".pyc", ".json", ".keep", ""} and ".py" not in kinds
-    assert os.path.isfile(os.path.join(out, "ml_flashpoint", "core", "checkpoint_saver.pyc"))
+    import zipfile
+
+    assert sorted(os.listdir(out)) == ["manifest.json", "reference_bytecode.zip"]
+    names = zipfile.ZipFile(os.path.join(out, "reference_bytecode.zip")).namelist()
+    assert "ml_flashpoint/core/checkpoint_saver.pyc" in names
+    assert all(n.endswith(".pyc") or n.endswith("/") for n in names)  # bytecode and directories, no sources
 
 
 @needs_ref
