@@ -349,7 +349,13 @@ def main() -> None:
     ap.add_argument("--cpu-baseline-budget-s", type=float, default=20.0, help="time budget of the CPU-baseline leg's saves")
     ap.add_argument("--workdir", default=None)
     ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
+    ap.add_argument("--probe", default=None, choices=[None, "host-link"],
+                    help="host-link: plain copies between HBM and driver-allocated pinned memory in a process that "
+                    "holds nothing else, rank by rank and all ranks at once; prints one JSON line and exits")
     args = ap.parse_args()
+    if args.probe == "host-link":
+        run_host_link_probe(args)
+        return
     if args.impl == "mlf_b200":
         args.warmup = max(args.warmup, 3)  # fewer warm-up saves would time plan creation and buffer sizing
 
@@ -460,6 +466,87 @@ def run_reference_arm(args, device, workdir: str) -> None:
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def run_host_link_probe(args) -> None:
+    """What the host link gives this set of GPUs, measured with nothing else in the process: no
+    pool files, no page-locked tmpfs, no arena. Per rank: copy-engine D2H and H2D between HBM and
+    ``cudaHostAlloc`` memory, and the copy kernel storing into / loading from the same memory
+    (``mlf_copy_kernel_launch``), first one rank at a time (the others idle), then all ranks at once.
+    Tells a limit of the host apart from a cost of this library's own registered mappings."""
+    import ctypes
+
+    from ml_flashpoint import _native
+
+    rank, local_rank, world_size = world()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world_size > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _native.lib()
+    nbytes = 2 << 30
+    host = ctypes.c_void_p()
+    _native.check(lib.mlf_host_alloc(nbytes, ctypes.byref(host)))
+    ctypes.memset(host, 1, nbytes)
+    dev = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    stream = torch.cuda.Stream()
+    raw = ctypes.c_void_p(stream.cuda_stream)
+
+    def timed(fn, reps=3):
+        best = 0.0
+        for _ in range(reps):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0.record(stream)
+            fn()
+            t1.record(stream)
+            stream.synchronize()
+            best = max(best, nbytes / 1e9 / (t0.elapsed_time(t1) / 1e3))
+        return best
+
+    ops = {
+        "copy_engine_d2h": lambda: _native.check(lib.mlf_memcpy_async(host, ctypes.c_void_p(dev.data_ptr()), nbytes, _native.MLF_COPY_D2H, raw)),
+        "copy_engine_h2d": lambda: _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(dev.data_ptr()), host, nbytes, _native.MLF_COPY_H2D, raw)),
+        "kernel_store_to_host": lambda: _native.check(lib.mlf_copy_kernel_launch(host, ctypes.c_void_p(dev.data_ptr()), nbytes, raw, 32)),
+        "kernel_load_from_host": lambda: _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(dev.data_ptr()), host, nbytes, raw, 32)),
+    }
+    for fn in ops.values():  # warm-up: first touch of the pinned pages by the device, kernel load
+        fn()
+    torch.cuda.synchronize()
+    result = {}
+    for name, fn in ops.items():
+        alone = 0.0
+        for turn in range(world_size):  # one rank at a time
+            barrier()
+            if turn == rank:
+                alone = timed(fn)
+            barrier()
+        barrier()
+        together = timed(fn)  # everybody at once
+        barrier()
+        gathered = [None] * world_size
+        if world_size > 1:
+            dist.all_gather_object(gathered, (alone, together))
+        else:
+            gathered = [(alone, together)]
+        result[name] = {
+            "alone_gbs_per_rank": [round(a, 2) for a, _ in gathered],
+            "all_at_once_gbs_per_rank": [round(t, 2) for _, t in gathered],
+            "all_at_once_aggregate_gbs": round(sum(t for _, t in gathered), 2),
+        }
+    lib.mlf_host_free(host)
+    if rank == 0:
+        print(json.dumps({
+            "probe": "host-link",
+            "n_gpus": world_size,
+            "visible_devices": os.environ.get("CUDA_VISIBLE_DEVICES"),
+            "bytes_per_copy": nbytes,
+            "host_cpus": os.cpu_count(),
+            "what": "fresh process per rank, nothing else page-locked; best of 3 per figure, CUDA events",
+            "results": result,
+        }))
+    if dist.is_initialized():
+        dist.destroy_process_group()
 
 
 def shard_payload_bytes(layers: int = 32) -> int:

@@ -222,29 +222,32 @@ def test_replication_starts_with_the_pack_kernel_when_the_object_is_pooled(shm_p
     saver, com = _pooled_saver(shm_path, engine, 0)
     mgr.initialize(com, replication_transfer_service=a, repl_strategy=rm.RingReplicationStrategy([a.address, b.address]))
     saver._replication_manager = mgr
-    case = case_to_device(cases.CASES["mixed"](), "cuda")
-    ckpt = CheckpointContainerId(str(shm_path / "step-3_ckpt"))
-    saver.initialize_checkpoint(ckpt)
-    items, resolver = cases.write_items_and_resolver(case)
-    buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=1)
-    started = []
-    real = mgr.async_replicate
-    monkeypatch.setattr(mgr, "async_replicate", lambda buf: started.append(real(buf)) or started[-1])
-    if overlapped:
-        pending = saver.write_data_async(ckpt, buckets, replicate_after_write=True)
-        assert len(started) == 1  # queued before result() is called
-        pending.result()
-        futures = pending.replication_futures
-    else:
-        saver.write_data(ckpt, buckets, replicate_after_write=True)
-        futures = started[0]
-    assert len(started) == 1 and len(futures) == 1 and futures[0].result(timeout=60).success
-    gold = load_golden(GOLDEN, "mixed.json")["objects"][0]
-    primary = open(str(buckets[0].object_id), "rb").read()
-    assert primary == golden_object_bytes(GOLDEN, gold)
-    assert open(mapper(str(buckets[0].object_id), 0), "rb").read() == primary
-    stats = a.last_put_stats
-    assert stats["from_hbm_image"] and stats["since_save_start_ms"] is not None and stats["since_save_start_ms"] > 0
+    try:
+        case = case_to_device(cases.CASES["mixed"](), "cuda")
+        ckpt = CheckpointContainerId(str(shm_path / "step-3_ckpt"))
+        saver.initialize_checkpoint(ckpt)
+        items, resolver = cases.write_items_and_resolver(case)
+        buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=1)
+        started = []
+        real = mgr.async_replicate
+        monkeypatch.setattr(mgr, "async_replicate", lambda buf: started.append(real(buf)) or started[-1])
+        if overlapped:
+            pending = saver.write_data_async(ckpt, buckets, replicate_after_write=True)
+            assert len(started) == 1  # queued before result() is called
+            pending.result()
+            futures = pending.replication_futures
+        else:
+            saver.write_data(ckpt, buckets, replicate_after_write=True)
+            futures = started[0]
+        assert len(started) == 1 and len(futures) == 1 and futures[0].result(timeout=60).success
+        gold = load_golden(GOLDEN, "mixed.json")["objects"][0]
+        primary = open(str(buckets[0].object_id), "rb").read()
+        assert primary == golden_object_bytes(GOLDEN, gold)
+        assert open(mapper(str(buckets[0].object_id), 0), "rb").read() == primary
+        stats = a.last_put_stats
+        assert stats["from_hbm_image"] and stats["since_save_start_ms"] is not None and stats["since_save_start_ms"] > 0
+    finally:
+        com.teardown_pool()  # the pool is process-wide: later tests must not inherit this one
 
 
 def test_put_falls_back_to_the_host_copy_when_the_image_is_gone(shm_path, services):
