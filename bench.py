@@ -340,6 +340,8 @@ def main() -> None:
     ap.add_argument("--impl", default="mlf_b200", choices=["mlf_b200", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="transformer layers in the synthetic state (32 = the named config)")
     ap.add_argument("--mode", default=None, choices=[None, "staged", "direct"], help="pack destination (default: staged)")
+    ap.add_argument("--arena-limit-gb", type=float, default=0.0,
+                    help="bound the HBM image arena (0 = hold the whole save): larger saves go through it piece by piece")
     ap.add_argument("--no-restore", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replication", action="store_true")
@@ -535,6 +537,70 @@ def run_host_link_probe(args) -> None:
             "all_at_once_aggregate_gbs": round(sum(t for _, t in gathered), 2),
         }
     lib.mlf_host_free(host)
+
+    # ---- the restore feed: an object file on tmpfs, opened read-only by a process that has never
+    # seen it (nothing page-locked), into HBM: pread() threads through the bounce ring, the same with
+    # the lock lane beside them, and the lock lane alone
+    from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+    from ml_flashpoint.core.gpu_engine import default_host_threads
+
+    shm_root = "/dev/shm" if os.path.isdir("/dev/shm") else "/tmp"
+    path = os.path.join(shm_root, f"mlf_probe_{os.getuid()}_{rank}.bin")
+    file_bytes = 4 << 30
+    with open(path, "wb") as f:
+        block = bytes(bytearray(os.urandom(1 << 20)) * 16)
+        for _ in range(file_bytes // len(block)):
+            f.write(block)
+    big = torch.empty(file_bytes, dtype=torch.uint8, device=device)
+    threads = default_host_threads(1.0)  # what a restore uses: all cores, divided between the ranks of the host
+    feeds = {
+        "pread_threads": (threads, 0),
+        "pread_threads_plus_lock_lane": (threads, 256),
+        "lock_lane_alone": (-1, 256),
+    }
+
+    def feed_once(nthreads, run_mib):
+        obj = BufferObject(path)  # a fresh read-only mapping each time
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        lane = obj.read_to_device(0, big.data_ptr(), file_bytes, threads=nthreads, lock_run_mib=run_mib)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        obj.close()
+        return file_bytes / 1e9 / dt, lane
+
+    feed_result = {}
+    try:
+        feed_once(threads, 0)  # warm-up: ring slots, streams
+        for name, (nthreads, run_mib) in feeds.items():
+            alone, lane_share = 0.0, 0.0
+            for turn in range(world_size):
+                barrier()
+                if turn == rank:
+                    alone, lane_bytes = feed_once(nthreads, run_mib)
+                    lane_share = lane_bytes / file_bytes
+                barrier()
+            barrier()
+            together, _ = feed_once(nthreads, run_mib)
+            barrier()
+            gathered = [None] * world_size
+            if world_size > 1:
+                dist.all_gather_object(gathered, (alone, together, lane_share))
+            else:
+                gathered = [(alone, together, lane_share)]
+            feed_result[name] = {
+                "alone_gbs_per_rank": [round(a, 2) for a, _, _ in gathered],
+                "all_at_once_gbs_per_rank": [round(t, 2) for _, t, _ in gathered],
+                "all_at_once_aggregate_gbs": round(sum(t for _, t, _ in gathered), 2),
+                "lane_share_alone": [round(s, 3) for _, _, s in gathered],
+                "pread_threads_per_rank": threads if nthreads > 0 else 0,
+            }
+    finally:
+        os.remove(path)
+    result["restore_feed"] = {
+        "what": "4 GiB object file on tmpfs opened read-only into HBM (wall clock of the blocking call), page cache warm",
+        **feed_result,
+    }
     if rank == 0:
         print(json.dumps({
             "probe": "host-link",
@@ -566,6 +632,7 @@ def workload_config(args, payload_bytes: int) -> dict:
         + ("" if args.layers == 32 else f" (reduced to {args.layers} layers)"),
         "payload_bytes_per_rank": payload_bytes,
         "pack_mode": args.mode or "staged",
+        "arena_limit_bytes": int(getattr(args, "arena_limit_gb", 0.0) * (1 << 30)),
         "cache": "inputs larger than L2 (14.05 GB per rank vs 126 MB)",
         "objects_per_rank": 1,
     }
@@ -822,7 +889,7 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
     shard = build_shard(rank, device, layers=args.layers)
     payload = sum(t.numel() * t.element_size() for _, t, _, _ in shard)
     items, resolver = write_items_for(shard)
-    engine = gpu_engine.CudaCopyEngine(device=device, mode=args.mode)
+    engine = gpu_engine.CudaCopyEngine(device=device, mode=args.mode, arena_limit_bytes=int(args.arena_limit_gb * (1 << 30)))
     gpu_engine.set_default_engine(engine)  # replication looks the HBM image up through the process-wide engine
 
     # size the pool buffer exactly: header sizes are known without touching the GPU

@@ -86,7 +86,8 @@ int32_t mlf_buf_read_to_device(const mlf_buf* b, uint64_t offset, void* dev_ptr,
  * there is one lane; it pays off where the cores, not the host link, bound a restore (several
  * ranks restoring at once on one host). Needs write permission on the file (nothing is written);
  * without it, or if locking fails, the threads move everything. lock_run_mib = 0 is
- * mlf_buf_read_to_device. Same reference counterpart: the loader's per-tensor host reads
+ * mlf_buf_read_to_device. nthreads < 0 makes the lane work alone (the threads only move what it
+ * leaves behind when it cannot run). Same reference counterpart: the loader's per-tensor host reads
  * (core/checkpoint_loader.py:177-219). */
 int32_t mlf_buf_read_to_device_hybrid(const mlf_buf* b, uint64_t offset, void* dev_ptr, uint64_t nbytes, int32_t nthreads,
                                       int32_t lock_run_mib);

@@ -109,6 +109,9 @@ int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off
                         int32_t nthreads, const char* lock_path, uint32_t lock_run_units) {
   if (nbytes == 0) return MLF_OK;
   if (!dev_ptr || (!host_ptr && fd < 0)) return mlf::fail(MLF_ERR_INVALID, "bounce transfer: null pointer");
+  // nthreads < 0 (with a lock lane): the pread threads stand back and only move what the lane leaves
+  // behind when it cannot run; the lane then works alone, from the back of the range to its front
+  const bool lane_only = nthreads < 0 && lock_path && lock_run_units > 0;
   int workers = nthreads > 0 ? nthreads : (int)std::max(1u, std::thread::hardware_concurrency() / 2);
   workers = std::min(workers, kMaxWorkers);
   const uint64_t chunk = chunk_bytes();
@@ -116,7 +119,8 @@ int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off
   const uint64_t space1 = space0 + nbytes;
   const uint64_t unit0 = space0 / chunk, unit1 = (space1 + chunk - 1) / chunk;
   workers = (int)std::min<uint64_t>((uint64_t)workers, unit1 - unit0);
-  const bool lane_wanted = lock_path && to_device && fd >= 0 && lock_run_units > 0 && (unit1 - unit0) >= 4ull * lock_run_units;
+  const bool lane_wanted = lock_path && to_device && fd >= 0 && lock_run_units > 0 &&
+                           (lane_only || (unit1 - unit0) >= 4ull * lock_run_units);
   int dev = 0;
   MLF_CUDA(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> hold(g_ring.mu);
@@ -279,7 +283,11 @@ int32_t bounce_transfer(void* dev_ptr, void* host_ptr, int fd, uint64_t file_off
   };
 
   std::vector<std::thread> pool;
-  if (lane_wanted) pool.emplace_back(lane);
+  if (lane_wanted && lane_only) {
+    lane();  // alone; whatever it could not take (no write access, locking refused) is left for the threads
+  } else if (lane_wanted) {
+    pool.emplace_back(lane);
+  }
   for (int w = 1; w < workers; ++w) pool.emplace_back(run, w);
   run(0);
   for (auto& t : pool) t.join();

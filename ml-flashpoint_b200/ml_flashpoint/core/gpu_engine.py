@@ -127,6 +127,33 @@ def plan_object_layout(
     return ObjectLayout(pos - start_offset, records, placements, chunks, payload_total)
 
 
+def split_layout(layout: ObjectLayout, piece_limit: int) -> Tuple[int, List[Tuple[int, int, List[TensorPlacement], List[HostChunk]]]]:
+    """Cuts a layout into consecutive image ranges for a save through a bounded arena.
+
+    Returns ``(slot_bytes, [(lo, hi, tensors, host_chunks)])``: every range holds whole items only (a
+    header, a tensor's payload or a byte item is never cut), ranges follow one another without gaps
+    in image order, and none is longer than ``slot_bytes`` = ``max(piece_limit, largest item)``.
+    """
+    items = [(p.payload_offset, p.tensor.numel() * p.tensor.element_size(), 0, p) for p in layout.tensors]
+    items += [(c.offset, len(c.data), 1, c) for c in layout.host_chunks]
+    items.sort(key=lambda it: (it[0], it[2]))
+    slot = max([piece_limit] + [n for _, n, _, _ in items])
+    pieces = []
+    lo = hi = None
+    tensors, chunks = [], []
+    for off, n, kind, obj in items:
+        if lo is not None and off + n - lo > slot:
+            pieces.append((lo, hi, tensors, chunks))
+            lo, tensors, chunks = None, [], []
+        if lo is None:
+            lo = off
+        hi = off + n
+        (chunks if kind else tensors).append(obj)
+    if lo is not None:
+        pieces.append((lo, hi, tensors, chunks))
+    return slot, pieces
+
+
 def c_strides(shape: Sequence[int]) -> List[int]:
     out = [1] * len(shape)
     for d in range(len(shape) - 2, -1, -1):
@@ -164,12 +191,11 @@ def default_host_threads(share: float = 0.5) -> int:
 
 
 def default_restore_lock_run_mib() -> int:
-    """Whether a restore runs its lock lane, and with which run size. The lane relieves the CPU
-    threads of part of the object; it pays where several ranks share one host's cores."""
-    import os
-
-    local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))
-    return 256 if local_world > 1 else 0
+    """Whether a restore runs its lock lane by default, and with which run size: it does not.
+    Measured on B200 hosts, page-locking pieces of the object while the pread() threads issue their
+    copies slows both down (the driver serialises the calls inside a process); the lane stays
+    available through ``MLFLASHPOINT_GPU_RESTORE_LOCK_RUN_MIB`` for hosts where cores are scarcer."""
+    return 0
 
 
 # ======================================================================================
@@ -228,6 +254,25 @@ class _CachedPack:
     last_kernel: Optional["torch.cuda.Event"] = None  # the last launch that read ``blob``
 
 
+@dataclasses.dataclass
+class _CachedCappedPack:
+    """Plans of a save that goes through the bounded arena piece by piece."""
+
+    slot_bytes: int
+    pieces: list  # (lo, hi, _Plan)
+    blob: _PinnedBlob
+    keepalive: list
+    last_kernel: Optional["torch.cuda.Event"] = None
+
+    @property
+    def plan(self):  # status of the last piece's plan stands for the save (every piece is checked in wait)
+        return self
+
+    def status(self) -> None:
+        for _, _, plan in self.pieces:
+            plan.status()
+
+
 @dataclasses.dataclass(eq=False)
 class _Image:
     """One object image inside the engine's HBM arena."""
@@ -281,7 +326,8 @@ class CudaCopyEngine:
     from host memory, where a handful of CTAs saturate the link (``MLFLASHPOINT_GPU_HOST_CTAS``).
     """
 
-    def __init__(self, device: Optional[torch.device] = None, mode: Optional[str] = None, plan_cache_size: int = 8):
+    def __init__(self, device: Optional[torch.device] = None, mode: Optional[str] = None, plan_cache_size: int = 8,
+                 arena_limit_bytes: Optional[int] = None):
         _native.lib()  # fail here, loudly, if the native library is absent
         if not torch.cuda.is_available():
             raise RuntimeError(
@@ -293,6 +339,13 @@ class CudaCopyEngine:
         if self.mode not in ("staged", "direct"):
             raise ValueError(f"unknown pack mode '{self.mode}' (expected 'staged' or 'direct')")
         self.host_ctas = get_env_val_int("GPU_HOST_CTAS", 32)
+        # Upper bound on the HBM image arena (0 = none: the arena holds the whole save, which lets
+        # training resume after the few milliseconds of the pack kernels and leaves a resident image
+        # for replication). With a bound, a larger save is packed and drained piece by piece through
+        # two arena halves: the tensors stay read-locked until the last piece is packed, i.e. for most
+        # of the host transfer, and replication sends from the host mapping.
+        self.arena_limit = int(arena_limit_bytes if arena_limit_bytes is not None else get_env_val_int("GPU_ARENA_LIMIT_BYTES", 0))
+        self._slot_free: list = [None, None]  # bounded mode: event after which arena half k may be rewritten
         # CPU threads feeding the bounce ring when host memory is not page-locked (0 = half the cores)
         self.host_threads = get_env_val_int("GPU_HOST_THREADS", default_host_threads())
         # a restore runs before training starts, with the host otherwise idle: it may use every core
@@ -342,6 +395,10 @@ class CudaCopyEngine:
             return
         for image in self._images:
             image.done.synchronize()
+        for event in self._slot_free:
+            if event is not None:
+                event.synchronize()
+        self._slot_free = [None, None]
         self._images = []
         self._cursor = 0
         self._arena = None
@@ -351,7 +408,10 @@ class CudaCopyEngine:
         """Announces a save whose object images take ``total_bytes`` in all: the arena is sized for
         the whole save and its objects are placed from the front, so none waits for another's transfer."""
         with self._lock, torch.cuda.device(self.device):
-            self._arena_goal = max(self._arena_goal, int(total_bytes) + self._ARENA_ALIGN * 64)
+            goal = int(total_bytes) + self._ARENA_ALIGN * 64
+            if self.arena_limit and goal > self.arena_limit:
+                goal = self.arena_limit  # the save goes through the arena piece by piece
+            self._arena_goal = max(self._arena_goal, goal)
             self._cursor = 0
 
     def _reserve_image(self, nbytes: int, stream: "torch.cuda.Stream") -> Tuple[torch.Tensor, int]:
@@ -361,6 +421,10 @@ class CudaCopyEngine:
             self._active_read.wait()  # a restore's image occupies the arena until it has arrived
             self._active_read = None
         self._ensure_arena(nbytes)
+        for event in self._slot_free:  # halves of a piecewise save that may still be draining
+            if event is not None:
+                stream.wait_event(event)
+        self._slot_free = [None, None]
         if self._cursor + nbytes > self._arena.numel():
             self._cursor = 0
         offset = self._cursor
@@ -380,6 +444,10 @@ class CudaCopyEngine:
         self._ensure_arena(nbytes)
         for image in self._images:
             image.done.synchronize()
+        for event in self._slot_free:
+            if event is not None:
+                event.synchronize()
+        self._slot_free = [None, None]
         self._images = []
         self._cursor = 0
         return self._arena[:nbytes]
@@ -451,6 +519,123 @@ class CudaCopyEngine:
         entry.blob.fill(layout.host_chunks)
         return entry
 
+    # ------------------------------------------------------------------ save through a bounded arena
+    def _capped(self, nbytes: int) -> bool:
+        return bool(self.arena_limit) and self.mode == "staged" and nbytes > self.arena_limit
+
+    def _capped_pack_entry(self, layout: ObjectLayout) -> _CachedCappedPack:
+        has_host_tensor = any(p.tensor.device.type != "cuda" for p in layout.tensors)
+        key = (
+            "capped",
+            self.arena_limit,
+            tuple(self._tensor_key(p.tensor) + (p.payload_offset,) for p in layout.tensors),
+            tuple((c.offset, len(c.data)) for c in layout.host_chunks),
+        )
+        entry = None if has_host_tensor else self._cache.get(key)
+        if entry is None:
+            slot_bytes, ranges = split_layout(layout, max(self.arena_limit // 2, 4096))
+            blob = _PinnedBlob(layout.host_blob_size())
+            blob_at = {}
+            at = blob.ptr
+            for chunk in layout.host_chunks:  # the blob keeps the layout's chunk order (see _PinnedBlob.fill)
+                blob_at[chunk.offset] = at
+                at += len(chunk.data)
+            keepalive, pieces = [], []
+            for lo, hi, tensors, chunks in ranges:
+                descs = (_native.CopyDesc * max(len(tensors) + len(chunks), 1))()
+                k = 0
+                for placement in tensors:
+                    t = placement.tensor
+                    if t.device.type != "cuda":
+                        t = t.to(self.device, non_blocking=False)
+                        keepalive.append(t)
+                    elif t.device != self.device:
+                        raise ValueError(f"tensor lives on {t.device}, engine on {self.device}")
+                    fill_desc(descs[k], t.data_ptr(), placement.payload_offset - lo, t.element_size(), t.shape, t.stride(), c_strides(t.shape))
+                    k += 1
+                for chunk in chunks:
+                    fill_desc(descs[k], blob_at[chunk.offset], chunk.offset - lo, 1, (len(chunk.data),), (1,), (1,))
+                    k += 1
+                pieces.append((lo, hi, _Plan(descs, k, _native.MLF_PACK)))
+            entry = _CachedCappedPack(slot_bytes, pieces, blob, keepalive)
+            if not has_host_tensor:
+                self._cache[key] = entry
+                while len(self._cache) > self._cache_size:
+                    self._cache.popitem(last=False)
+        else:
+            self._cache.move_to_end(key)
+        if entry.last_kernel is not None:
+            entry.last_kernel.synchronize()
+        entry.blob.fill(layout.host_chunks)
+        return entry
+
+    def _claim_whole_arena(self, nbytes: int, stream: "torch.cuda.Stream") -> None:
+        """Bounded mode uses the arena as two halves of its own: images of earlier saves are given
+        up (work on ``stream`` waits for the transfers out of them) and a restore in flight is awaited."""
+        if self._active_read is not None:
+            self._active_read.wait()
+            self._active_read = None
+        self._arena_goal = max(self._arena_goal, nbytes)
+        self._ensure_arena(nbytes)
+        for image in self._images:
+            stream.wait_event(image.done)
+        self._images = []
+        self._cursor = 0
+
+    def _pack_capped(self, layout: ObjectLayout, buffer_io, start_pos: int, object_id: Optional[str]) -> PackTicket:
+        entry = self._capped_pack_entry(layout)
+        slot_bytes = (entry.slot_bytes + self._ARENA_ALIGN - 1) // self._ARENA_ALIGN * self._ARENA_ALIGN
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        self.pack_stream.wait_event(ready)
+        self._claim_whole_arena(2 * slot_bytes, self.pack_stream)
+        start_event = torch.cuda.Event(enable_timing=True)
+        mutate_event = torch.cuda.Event(enable_timing=True)
+        done_event = torch.cuda.Event(enable_timing=True)
+        registered = self._is_registered(buffer_io)
+        start_event.record(self.pack_stream)
+        for k, (lo, hi, plan) in enumerate(entry.pieces):
+            half = k % 2
+            slot = self._arena[half * slot_bytes : half * slot_bytes + (hi - lo)]
+            if self._slot_free[half] is not None:
+                self.pack_stream.wait_event(self._slot_free[half])  # the piece before last has left this half
+            plan.launch(slot.data_ptr(), hi - lo, self.pack_stream.cuda_stream)
+            packed = torch.cuda.Event()
+            packed.record(self.pack_stream)
+            if registered:
+                self.copy_stream.wait_event(packed)
+                _native.check(
+                    _native.lib().mlf_memcpy_async(
+                        ctypes.c_void_p(buffer_io.host_address(start_pos + lo)),
+                        ctypes.c_void_p(slot.data_ptr()),
+                        hi - lo,
+                        _native.MLF_COPY_D2H,
+                        ctypes.c_void_p(self.copy_stream.cuda_stream),
+                    )
+                )
+                drained = torch.cuda.Event()
+                drained.record(self.copy_stream)
+            else:
+                packed.synchronize()
+                _native.check(
+                    _native.lib().mlf_bounce_copy(
+                        ctypes.c_void_p(slot.data_ptr()), ctypes.c_void_p(buffer_io.host_address(start_pos + lo)), hi - lo, 0, self.host_threads
+                    )
+                )
+                drained = packed
+            self._slot_free[half] = drained
+        mutate_event.record(self.pack_stream)
+        if registered:
+            done_event.record(self.copy_stream)
+        else:
+            done_event.record(self.pack_stream)
+        if object_id is not None:
+            self._drains[str(object_id)] = done_event
+            self._drains.move_to_end(str(object_id))
+        entry.last_kernel = mutate_event
+        self.last_ticket = PackTicket(self, entry, start_event, mutate_event, done_event, layout.total_bytes)
+        return self.last_ticket
+
     # ------------------------------------------------------------------ save
     def pack_async(self, layout: ObjectLayout, buffer_io, start_pos: int = 0, object_id: Optional[str] = None) -> PackTicket:
         """Starts writing ``layout`` at stream position ``start_pos`` of ``buffer_io``.
@@ -463,6 +648,8 @@ class CudaCopyEngine:
         """
         with self._lock, torch.cuda.device(self.device):
             self._bind()
+            if self._capped(layout.total_bytes):
+                return self._pack_capped(layout, buffer_io, start_pos, object_id)
             entry = self._pack_entry(layout)
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
@@ -588,6 +775,9 @@ class CudaCopyEngine:
                 )
             )
 
+    def _unpack_capped(self, prepared, buffer_io) -> None:
+        _unpack_capped_impl(self, prepared, buffer_io)
+
     def object_read(self, buffer_io, lo: int, hi: int) -> "_ObjectRead":
         """Context manager that starts moving data-section bytes ``[lo, hi)`` of ``buffer_io`` into HBM
         at once, on a helper thread, so that the caller can parse headers and plan the restore while
@@ -627,6 +817,9 @@ class CudaCopyEngine:
                 hi = max(hi, first + span * esize)
                 prepared.append((target, first, istr))
             lo -= lo % 16  # keep image offsets congruent mod 16 between the mapping and the HBM copy
+            if self._capped(hi - lo) and not (prefetched is not None and prefetched.covers(buffer_io, lo, hi)):
+                self._unpack_capped(prepared, buffer_io)
+                return
             use_prefetch = prefetched is not None and prefetched.covers(buffer_io, lo, hi)
             if use_prefetch:
                 lo, hi = prefetched.lo, prefetched.hi
@@ -676,6 +869,80 @@ class CudaCopyEngine:
             torch.cuda.current_stream(self.device).wait_event(done)
 
 
+def _unpack_capped_impl(engine: "CudaCopyEngine", prepared, buffer_io) -> None:
+    """Restore through the bounded arena: the reads are grouped, in image order, into pieces that fit
+    half the arena; each piece is brought into its half and scattered by a launch of its own while
+    the next piece travels into the other half."""
+    spans = []
+    for target, first, istr in prepared:
+        span = sum((int(n) - 1) * s for n, s in zip(target.shape, istr)) + 1
+        spans.append((first, first + span * target.element_size(), target, istr))
+    spans.sort(key=lambda x: x[0])
+    limit = max(engine.arena_limit // 2, 4096)
+    slot_bytes = max([limit] + [hi - (lo - lo % 16) for lo, hi, _, _ in spans])
+    pieces, current, p_lo, p_hi = [], [], None, None
+    for lo, hi, target, istr in spans:
+        if current and max(hi, p_hi) - p_lo > slot_bytes:
+            pieces.append((p_lo, p_hi, current))
+            current, p_lo, p_hi = [], None, None
+        if p_lo is None:
+            p_lo, p_hi = lo - lo % 16, hi
+        p_hi = max(p_hi, hi)
+        current.append((target, lo, istr))
+    if current:
+        pieces.append((p_lo, p_hi, current))
+    slot_bytes = (slot_bytes + engine._ARENA_ALIGN - 1) // engine._ARENA_ALIGN * engine._ARENA_ALIGN
+    stream = engine.pack_stream
+    ready = torch.cuda.Event()
+    ready.record(torch.cuda.current_stream(engine.device))
+    stream.wait_event(ready)
+    engine._claim_whole_arena(2 * slot_bytes, stream)
+    for event in engine._slot_free:  # halves of an earlier piecewise save
+        if event is not None:
+            event.synchronize()
+    engine._slot_free = [None, None]
+    host_targets, plans = [], []
+    scattered = [None, None]
+    fill_ms = kernel_ms = 0.0
+    timers = []
+    for k, (p_lo, p_hi, group) in enumerate(pieces):
+        descs = (_native.CopyDesc * len(group))()
+        for j, (target, first, istr) in enumerate(group):
+            dev_target = target
+            if target.device.type != "cuda":
+                dev_target = torch.empty(target.shape, dtype=target.dtype, device=engine.device)
+                host_targets.append((target, dev_target))
+            elif target.device != engine.device:
+                raise ValueError(f"target lives on {target.device}, engine on {engine.device}")
+            fill_desc(descs[j], dev_target.data_ptr(), first - p_lo, dev_target.element_size(), dev_target.shape, dev_target.stride(), istr)
+        plan = _Plan(descs, len(group), _native.MLF_UNPACK)
+        plans.append(plan)
+        half = k % 2
+        slot = engine._arena[half * slot_bytes : half * slot_bytes + (p_hi - p_lo)]
+        if scattered[half] is not None:
+            scattered[half].synchronize()  # the bounce ring writes the half outside any stream
+        t0, t1, t2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        t0.record(stream)
+        engine._fill_image(slot, buffer_io, p_lo, p_hi - p_lo, stream)
+        t1.record(stream)
+        plan.launch(slot.data_ptr(), p_hi - p_lo, stream.cuda_stream)
+        t2.record(stream)
+        scattered[half] = t2
+        timers.append((t0, t1, t2))
+    stream.synchronize()
+    for plan in plans:
+        plan.status()
+    for t0, t1, t2 in timers:
+        fill_ms += t0.elapsed_time(t1)
+        kernel_ms += t1.elapsed_time(t2)
+    engine.last_unpack_ms = (fill_ms, kernel_ms)
+    for target, dev_target in host_targets:
+        target.copy_(dev_target)
+    done = torch.cuda.Event()
+    done.record(stream)
+    torch.cuda.current_stream(engine.device).wait_event(done)
+
+
 class _ObjectRead:
     """An object's bytes on their way into the engine's HBM arena (see ``CudaCopyEngine.object_read``)."""
 
@@ -699,8 +966,8 @@ class _ObjectRead:
         engine._lock.acquire()
         self._entered = True
         try:
-            if self.hi <= self.lo:
-                return self
+            if self.hi <= self.lo or engine._capped(self.hi - self.lo):
+                return self  # nothing to fetch ahead, or the restore goes through the bounded arena piece by piece
             with torch.cuda.device(engine.device):
                 engine._bind()
                 if engine._active_read is not None:

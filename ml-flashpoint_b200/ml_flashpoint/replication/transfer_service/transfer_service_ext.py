@@ -198,6 +198,7 @@ class TransferService:
         self._opened_ipc: Dict[str, int] = {}
         self._bounce: Optional[_DeviceBuffer] = None
         self._stream = ctypes.c_void_p()
+        self._task_marks = threading.local()  # phase timestamps of the transfer a worker thread is running
         self._transport = os.environ.get("MLFLASHPOINT_REPL_TRANSPORT", "auto").lower()
         self._cuda = False
         # device timing of the most recent outgoing transfer: {"bytes", "hop_ms", "from_hbm_image"}
@@ -300,15 +301,16 @@ class TransferService:
 
         The memory is borrowed until the future completes.
         """
-        return self._submit(self._run_put, int(data_ptr), int(data_size), dest_address, dest_object_id)
+        return self._submit(self._run_put, "PUT", int(data_size), int(data_ptr), int(data_size), dest_address, dest_object_id)
 
     def async_get(self, remote_object_id_to_get_obj_from: str, source_address: str, local_object_id_to_save_received_obj: str) -> concurrent.futures.Future:
         """Asks the peer at ``source_address`` to send one of its objects here."""
-        return self._submit(self._run_get, remote_object_id_to_get_obj_from, source_address, local_object_id_to_save_received_obj)
+        return self._submit(self._run_get, "GET", 0, remote_object_id_to_get_obj_from, source_address, local_object_id_to_save_received_obj)
 
-    def _submit(self, fn, *args) -> concurrent.futures.Future:
+    def _submit(self, fn, task_type: str, data_size: int, *args) -> concurrent.futures.Future:
         future: concurrent.futures.Future = concurrent.futures.Future()
         task_id = uuid.uuid4().hex
+        submitted = time.perf_counter()
         with self._lock:
             if not self._running:
                 future.set_exception(RuntimeError("TransferService is not running"))
@@ -316,12 +318,17 @@ class TransferService:
             self._pending[task_id] = future
 
         def _run():
+            marks = {"start": time.perf_counter()}
+            self._task_marks.marks = marks
             try:
                 fn(task_id, *args)
                 outcome, error = TransferResult(task_id, True, ""), None
             except Exception as e:  # surfaces on the future, as the reference's service does
                 _LOGGER.exception("transfer task %s failed", task_id)
                 outcome, error = None, e
+            finally:
+                self._task_marks.marks = None
+            self._report_result(task_id, task_type, data_size, error, submitted, marks)
             with self._lock:
                 self._pending.pop(task_id, None)
             if future.done():
@@ -333,6 +340,38 @@ class TransferService:
 
         self._workers.submit(_run)
         return future
+
+    def _mark(self, name: str) -> None:
+        """Timestamps a phase of the transfer running on this worker thread."""
+        marks = getattr(self._task_marks, "marks", None)
+        if marks is not None:
+            marks.setdefault(name, time.perf_counter())
+
+    @staticmethod
+    def _report_result(task_id: str, task_type: str, data_size: int, error, submitted: float, marks: dict) -> None:
+        """One line per finished transfer in the shape the reference's service logs
+        (transfer_service.cpp:489-492 with the fields of task.cpp:39-111), which its log
+        summariser reads. ``data_sent`` covers the GPU-to-GPU hop for the NVLink transport."""
+        finished = time.perf_counter()
+
+        def span(a, b):
+            if a is None or b is None:
+                return 0.0
+            return (b - a) * 1e3
+
+        start = marks.get("start")
+        connected = marks.get("connection_acquired")
+        header = marks.get("header_sent")
+        moved = marks.get("data_sent") or marks.get("data_received")
+        label = "data_received" if task_type == "GET" else "data_sent"
+        timing = (
+            f"wait_to_be_executed={span(submitted, start):.3f}ms, connection_acquired={span(start, connected):.3f}ms, "
+            f"header_sent={span(connected, header):.3f}ms, {label}={span(header, moved):.3f}ms, total={span(submitted, finished):.3f}ms"
+        )
+        _LOGGER.info(
+            "TransferService::report_result: task_id=%s, task_type=%s, data_size=%d, success=%d, message=%s, timing=%s",
+            task_id, task_type, data_size, 0 if error else 1, "" if error is None else str(error), timing,
+        )
 
     # ------------------------------------------------------------------ sender side
     def _connect(self, address: str) -> socket.socket:
@@ -371,6 +410,7 @@ class TransferService:
         if self._cuda:
             _native.check(lib.mlf_set_device(self._device))
         with self._connect(dest_address) as sock:
+            self._mark("connection_acquired")
             _send_msg(
                 sock,
                 {
@@ -379,12 +419,14 @@ class TransferService:
                 },
             )
             reply = _recv_msg(sock)
+            self._mark("header_sent")
             if not reply.get("ok"):
                 raise RuntimeError(f"peer refused put of '{dest_object_id}': {reply.get('error')}")
             if reply.get("transport") == "tcp":
                 gpu_engine.wait_object_on_host(dest_object_id)  # a save of it may still be draining
                 source = (ctypes.c_ubyte * data_size).from_address(data_ptr)
                 sock.sendall(memoryview(source).cast("B"))
+                self._mark("data_sent")
                 self.last_put_stats = {"bytes": data_size, "hop_ms": None, "from_hbm_image": False, "transport": "tcp"}
                 final = _recv_msg(sock)
                 if not final.get("ok"):
@@ -434,6 +476,7 @@ class TransferService:
                         _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(peer), ctypes.c_void_p(bounce.ptr), data_size, stream, 0))
                         _native.check(lib.mlf_event_record(t1, stream))
                         _native.check(lib.mlf_stream_sync(stream))
+                self._mark("data_sent")
                 ms = ctypes.c_float()
                 _native.check(lib.mlf_event_elapsed_ms(t0, t1, ctypes.byref(ms)))
                 self.last_put_stats = {
@@ -454,8 +497,11 @@ class TransferService:
 
     def _run_get(self, task_id: str, remote_object_id: str, source_address: str, local_object_id: str) -> None:
         with self._connect(source_address) as sock:
+            self._mark("connection_acquired")
             _send_msg(sock, {"op": "get", "obj": remote_object_id, "dest_obj": local_object_id, "reply_to": self.address, "task": task_id, "src_rank": self._rank})
-            reply = _recv_msg(sock)
+            self._mark("header_sent")
+            reply = _recv_msg(sock)  # arrives once the peer has put the object into this service's file
+            self._mark("data_received")
             if not reply.get("ok"):
                 raise RuntimeError(f"Received error message from peer for '{remote_object_id}': {reply.get('error')}")
 

@@ -744,3 +744,92 @@ def test_hybrid_restore_read_moves_exactly_the_files_bytes(shm_path, offset, tri
             assert lane == 0
         obj.close()
     assert int(_native.lib().mlf_last_lock_lane_bytes()) >= 0
+
+
+@pytest.fixture(scope="module")
+def bounded_engine():
+    from ml_flashpoint.core.gpu_engine import CudaCopyEngine
+
+    return CudaCopyEngine(mode="staged", arena_limit_bytes=16 << 10)
+
+
+@pytest.mark.parametrize("pooled", [False, True])
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_bounded_arena_saves_reference_bytes_and_restores_them(name, pooled, shm_path, golden_dir, bounded_engine):
+    """With the image arena capped (here at 16 KiB, so every golden object takes several pieces) a
+    save is packed and drained piece by piece through two arena halves, into a page-locked pool file
+    or a plain file: same object bytes, same records, and the piecewise restore gives the tensors back."""
+    from torch.distributed.checkpoint.planner import LoadItemType, ReadItem
+
+    from ml_flashpoint.core.buffer_pool import BufferPoolConfig
+
+    gold = load_golden(golden_dir, f"{name}.json")
+    case = case_to_device(cases.CASES[name](), "cuda")
+    kw = {}
+    if pooled:
+        kw["pool_config"] = BufferPoolConfig(str(shm_path / "pool"), 0, 2, 1 << 20, register_cuda=True)
+    saver, com, ckpt, buckets, results = _save(case, shm_path, bounded_engine, **kw)
+    try:
+        for bucket, g in zip(buckets, gold["objects"]):
+            with open(str(bucket.object_id), "rb") as f:
+                data = f.read()
+            assert len(data) == g["size"] and hashlib.sha256(data).hexdigest() == g["sha256"], bucket.object_name
+        got = sorted((r.storage_data.relative_path, r.storage_data.offset, r.storage_data.length) for r in results)
+        assert got == [(w["relative_path"], w["offset"], w["length"]) for w in gold["write_results"]]
+        assert bounded_engine.held_device_bytes() <= max(1 << 20, 2 * max(t.numel() * t.element_size() for t in case["tensors"].values()) + 4096)
+
+        loader = make_loader(com, copy_engine=bounded_engine)
+        storage = {r.index: r.storage_data for r in results}
+        targets, per_object = {}, {}
+        for r in results:
+            fqn = r.index.fqn
+            if fqn in case["blobs"]:
+                continue
+            t = case["tensors"][fqn]
+            if t.numel() == 0:
+                continue
+            targets[fqn] = torch.zeros(t.shape, dtype=t.dtype, device="cuda")
+            req = ReadItem(LoadItemType.TENSOR, r.index, torch.Size([0] * t.dim()), r.index, torch.Size([0] * t.dim()), torch.Size(t.shape))
+            per_object.setdefault(r.storage_data.relative_path, []).append(req)
+
+        class _Planner:
+            def resolve_tensor(self, req):
+                return targets[req.dest_index.fqn]
+
+            def commit_tensor(self, req, tensor):
+                pass
+
+        for bucket in buckets:
+            loader.read_data(bucket.object_id, per_object.get(bucket.object_name, []), _Planner(), storage)
+        torch.cuda.synchronize()
+        for fqn, target in targets.items():
+            assert tensor_bytes(target) == tensor_bytes(case["tensors"][fqn]), fqn
+    finally:
+        com.teardown_pool()
+
+
+def test_bounded_arena_at_size_keeps_the_arena_small(shm_path):
+    """256 MB of tensors through a 32 MiB arena into a page-locked pool file: the arena never grows
+    past its bound (two halves of 16 MiB), the object equals the unbounded engine's byte for byte."""
+    from ml_flashpoint.core.buffer_pool import BufferPoolConfig
+    from ml_flashpoint.core.gpu_engine import CudaCopyEngine
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    tensors = {f"t{i}": torch.randint(0, 1 << 30, (n,), device="cuda", dtype=torch.int32, generator=g)
+               for i, n in enumerate([1 << 20, 3 << 20, 1 << 18, 2 << 20, 5, 4 << 20, 1 << 22] * 4)}
+    case = {"tensors": tensors, "blobs": {"cfg": b"x" * 333}, "bucket_count": 1}
+    digests = []
+    for limit in (0, 32 << 20):
+        engine = CudaCopyEngine(mode="staged", arena_limit_bytes=limit)
+        pool = BufferPoolConfig(str(shm_path / f"pool{limit}"), 0, 1, 300 << 20, register_cuda=True)
+        saver, com, ckpt, buckets, results = _save(case, shm_path / f"run{limit}", engine, pool_config=pool, initial_buffer_size_bytes=300 << 20)
+        try:
+            with open(str(buckets[0].object_id), "rb") as f:
+                digests.append(hashlib.sha256(f.read()).hexdigest())
+            if limit:
+                assert engine.held_device_bytes() <= limit + 8192
+            else:
+                assert engine.held_device_bytes() >= sum(t.numel() * 4 for t in tensors.values())
+        finally:
+            com.teardown_pool()
+    assert digests[0] == digests[1]

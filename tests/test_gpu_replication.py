@@ -466,7 +466,16 @@ def test_two_devices_in_one_process_pack_replicate_and_restore(shm_path):
             services.append(s)
     try:
         gpu_engine.set_default_engine(engines[0])
-        com, oid, _, _ = objects[0]
+        com, oid, _, case0 = objects[0]
+        # the restore above gave the arena to its own image; save once more so that the push below
+        # finds the object's image resident in device 0's HBM
+        with torch.cuda.device(0):
+            saver0, com = make_saver(copy_engine=engines[0], rank=0)
+            ckpt0 = CheckpointContainerId(os.path.dirname(str(oid)))
+            items0, resolver0 = cases.write_items_and_resolver(case0)
+            again = saver0.prepare_write_data(ckpt0, items0, resolver0, "__0_", bucket_count=1)
+            saver0.write_data(ckpt0, again, replicate_after_write=False)
+            assert str(again[0].object_id) == str(oid) and open(str(oid), "rb").read() == first
         buf = com.get_buffer(oid)
         assert services[0].async_put(buf.buffer_obj.get_data_ptr(), buf.buffer_obj.get_capacity(), services[1].address, str(oid)).result(timeout=60).success
         buf.close()

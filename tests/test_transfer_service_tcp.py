@@ -95,3 +95,50 @@ def test_receiver_discards_a_partial_object(pair, tmp_path):
             break
         deadline.wait(0.05)
     assert not os.path.exists(target) and not os.path.exists(target + ".tmp")
+
+
+def test_every_transfer_logs_the_result_line_the_reference_logs(pair, tmp_path):
+    """``TransferService::report_result: task_id=…, task_type=…, data_size=…, success=…, message=…,
+    timing=…`` once per finished task, with the reference's phase names, so that log summarisers
+    written for the reference service keep working."""
+    import logging
+    import re
+
+    from ml_flashpoint.replication.transfer_service import transfer_service_ext as mod
+
+    lines = []
+
+    class _Collect(logging.Handler):
+        def emit(self, record):
+            lines.append(record.getMessage())
+
+    handler = _Collect(level=logging.INFO)
+    before = mod._LOGGER.level
+    mod._LOGGER.addHandler(handler)
+    mod._LOGGER.setLevel(logging.INFO)
+    try:
+        a, b, replicas = pair
+        src = tmp_path / "primary" / "step-1_ckpt" / "o_src0.distcp"
+        _object(src, 70000, 3)
+        ro = BufferObject(str(src))
+        put = a.async_put(ro.get_data_ptr(), ro.get_capacity(), b.address, str(src)).result(timeout=60)
+        ro.close()
+        got = a.async_get(str(src), b.address, str(tmp_path / "back.distcp")).result(timeout=60)
+        with pytest.raises(RuntimeError):
+            a.async_get("/no/such/object", b.address, str(tmp_path / "nothing")).result(timeout=60)
+    finally:
+        mod._LOGGER.removeHandler(handler)
+        mod._LOGGER.setLevel(before)
+    reports = [l for l in lines if l.startswith("TransferService::report_result:")]
+    shape = re.compile(
+        r"task_id=(\w+), task_type=(PUT|GET), data_size=(\d+), success=([01]), message=(.*), "
+        r"timing=wait_to_be_executed=[\d.]+ms, connection_acquired=[\d.]+ms, header_sent=[\d.]+ms, "
+        r"(data_sent|data_received)=[\d.]+ms, total=[\d.]+ms$"
+    )
+    parsed = [shape.search(l) for l in reports]
+    assert all(parsed) and len(parsed) == 3
+    by_task = {m.group(1): m for m in parsed}
+    assert by_task[put.task_id].group(2, 3, 4) == ("PUT", "70000", "1")
+    assert by_task[got.task_id].group(2, 4) == ("GET", "1")
+    failed = [m for m in parsed if m.group(4) == "0"]
+    assert len(failed) == 1 and "not held here" in failed[0].group(5)
