@@ -147,6 +147,188 @@ __device__ __forceinline__ void drain_swizzled(uint8_t* __restrict__ dst, const 
   }
 }
 
+// Vector form of the wide TRANSPOSE tile (segments planned with g.reserved == 2, bulk kernels only).
+// The tensor side is read and written as aligned 16-byte granules instead of single elements:
+// per tensor row (fixed l) a tile takes 8 granules = 128 bytes along C and delivers the 112 bytes
+// that are complete behind any misalignment of the row start (7 granules after the shift), so a
+// warp-wide access covers four rows of 128 contiguous bytes whatever the element size. A sub-tile is
+// 128 elements along L: image row segments of 128 * E bytes. Staging is in image order, one row
+// per C index, pitch 128 * E + 4.
+template <int E>
+struct TransV {
+  static constexpr int kOutBytes = 112;
+  static constexpr int kC = kOutBytes / E;       // image rows per tile: 112, 56, 28, 14
+  static constexpr int kL = 128;                 // elements along L per sub-tile
+  static constexpr int kRowBytes = kL * E;       // one image row segment
+  static constexpr int kPitch = E == 8 ? kRowBytes + 8 : kRowBytes + 4;  // keeps elements aligned, spreads rows over banks
+  static constexpr int kPer = 16 / E;            // elements per granule
+  static constexpr int kWordsPerRow = kRowBytes / 4;
+  static constexpr int kWordsPerThread = (kC * kWordsPerRow + (int)kThreads - 1) / (int)kThreads;  // 14
+  static constexpr int kDrainLanes = kRowBytes / 16 >= 32 ? 32 : 16;  // lanes that share one image row in the drain
+  static constexpr int kSmemBytes = kC * kPitch + 32;
+};
+constexpr int kTransVSmemBytes = 112 * (128 + 4) + 32;  // widest case (E = 1); fits one ring slot
+inline uint32_t trans_v_cols(uint32_t esize) { return 112u / esize; }
+constexpr int kTransVL = 128;
+
+template <typename T>
+__device__ __forceinline__ T granule_elem(const uint4& v, int e) {
+  constexpr int E = (int)sizeof(T);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (E == 8) return (T)(((uint64_t)w[2 * e + 1] << 32) | w[2 * e]);
+  if (E == 4) return (T)w[e];
+  if (E == 2) return (T)((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
+  return (T)((w[e >> 2] >> ((e & 3) * 8)) & 0xffu);
+}
+template <typename T>
+__device__ __forceinline__ void granule_set(uint32_t (&w)[4], int e, T x) {
+  constexpr int E = (int)sizeof(T);
+  if (E == 8) {
+    w[2 * e] = (uint32_t)((uint64_t)x & 0xffffffffu);
+    w[2 * e + 1] = (uint32_t)((uint64_t)x >> 32);
+  } else if (E == 4) {
+    w[e] = (uint32_t)x;
+  } else if (E == 2) {
+    w[e >> 1] |= (uint32_t)x << ((e & 1) * 16);
+  } else {
+    w[e >> 2] |= (uint32_t)x << ((e & 3) * 8);
+  }
+}
+
+// Wide TRANSPOSE tile, vector form. `smem` must hold kTransVSmemBytes. Must run with kThreads threads.
+template <typename T, int DIR>
+__device__ __noinline__ void transpose_tile_v(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
+  constexpr int E = (int)sizeof(T);
+  using V = TransV<E>;
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  int64_t toff = 0, ioff = 0;
+  for (int d = L - 1; d >= 0; --d) {
+    if (d == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[d]);
+    batch /= (uint64_t)g.shape[d];
+    toff += idx * g.tstride[d];
+    ioff += idx * g.istride[d];
+  }
+  const int64_t nC = g.shape[C], nL = g.shape[L];
+  const int64_t tsL = g.tstride[L], isC = g.istride[C];
+  const int64_t c0 = (int64_t)(in_batch / g.b) * V::kC;
+  const int64_t lfirst = (int64_t)(in_batch % g.b) * (V::kL * kTransSub);
+  const int nsub = (int)min((int64_t)kTransSub, (nL - lfirst + V::kL - 1) / V::kL);
+  const int nc = (int)min((int64_t)V::kC, nC - c0);  // image rows of this tile
+  const uint32_t row_bytes = (uint32_t)nc * E;       // bytes of each tensor row that belong to the tile
+  uint8_t* trow0 = reinterpret_cast<uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;  // tensor row lfirst
+  uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;                    // image row c0 at lfirst
+  const unsigned tid = threadIdx.x;
+  const unsigned j = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
+  auto elems_of = [&](int s) { return (int)min((int64_t)V::kL, nL - (lfirst + (int64_t)s * V::kL)); };
+
+  if (DIR == MLF_PACK) {
+    uint4 v[4];
+    auto load = [&](int s) {
+      const int nl = elems_of(s);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int l = (int)lr + 32 * k;
+        const uint8_t* row = trow0 + ((int64_t)s * V::kL + l) * tsL;
+        const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+        // only granules that hold at least one byte of the row are touched
+        const bool need = l < nl && 16u * j < m + row_bytes;
+        v[k] = need ? mlf::ld_vec(reinterpret_cast<const uint4*>(row - m) + j) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    };
+    load(0);
+    for (int s = 0; s < nsub; ++s) {
+      const int nl = elems_of(s);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int l = (int)lr + 32 * k;
+        const uint8_t* row = trow0 + ((int64_t)s * V::kL + l) * tsL;
+        const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+        const uint4 next = mlf::shfl_down1(v[k]);  // granule j + 1 of the same row (lanes 8r .. 8r + 7 share a row)
+        const uint4 out = m ? mlf::realign(v[k], next, m) : v[k];  // row bytes [16 j, 16 j + 16)
+        if (j < 7u && l < nl) {
+#pragma unroll
+          for (int e = 0; e < V::kPer; ++e) {
+            const int c = (int)j * V::kPer + e;
+            if (c < nc) *reinterpret_cast<T*>(smem + c * V::kPitch + l * E) = granule_elem<T>(out, e);
+          }
+        }
+      }
+      __syncthreads();
+      if (s + 1 < nsub) load(s + 1);
+      uint8_t* irow = ibase + (int64_t)s * V::kL * E;
+      constexpr unsigned DL = (unsigned)V::kDrainLanes;
+      for (unsigned r = tid / DL; r < (unsigned)nc; r += kThreads / DL) {
+        const uint32_t at = r * (uint32_t)V::kPitch;
+        mlf::drain_slot(irow + (int64_t)r * isC, smem + (at & ~15u), at & 15u, (uint32_t)nl * E, tid % DL, DL);
+      }
+      __syncthreads();
+    }
+  } else {
+    constexpr int N = V::kWordsPerThread;
+    uint32_t lo[N], hi[N];
+    auto load = [&](int s) {
+      const uint32_t nwords = ((uint32_t)elems_of(s) * E) >> 2;
+      const uint8_t* irow = ibase + (int64_t)s * V::kL * E;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const uint32_t i = tid + (uint32_t)k * kThreads;
+        const uint32_t r = i / V::kWordsPerRow, w = i % V::kWordsPerRow;
+        ld_word_pair(irow + (int64_t)r * isC, w, r < (uint32_t)nc && w < nwords, &lo[k], &hi[k]);
+      }
+    };
+    load(0);
+    for (int s = 0; s < nsub; ++s) {
+      const int nl = elems_of(s);
+      const uint32_t row_len = (uint32_t)nl * E, nwords = row_len >> 2;
+      const uint8_t* irow = ibase + (int64_t)s * V::kL * E;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const uint32_t i = tid + (uint32_t)k * kThreads;
+        const uint32_t r = i / V::kWordsPerRow, w = i % V::kWordsPerRow;
+        if (r < (uint32_t)nc && w < nwords)
+          *reinterpret_cast<uint32_t*>(smem + r * V::kPitch + w * 4u) = join_word_pair(irow + (int64_t)r * isC, lo[k], hi[k]);
+      }
+      const uint32_t tail = row_len & 3u;  // bytes after the last whole word of each image row
+      if (tail != 0 && tid < (unsigned)nc * tail) {
+        const uint32_t r = tid / tail, b = (nwords << 2) + tid % tail;
+        smem[r * V::kPitch + b] = irow[(int64_t)r * isC + b];
+      }
+      __syncthreads();
+      if (s + 1 < nsub) load(s + 1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int l = (int)lr + 32 * k;
+        if (l >= nl) continue;
+        uint8_t* row = trow0 + ((int64_t)s * V::kL + l) * tsL;
+        const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+        // aligned granule j of this tensor row holds row bytes [16 j - m, 16 j - m + 16)
+        const int first = ((int)(16u * j) - (int)m) / E;  // C index (relative to c0) of its first element; may be negative
+        if (first >= nc || first + V::kPer <= 0) continue;
+        uint8_t* gran = row - m + 16u * j;
+        if (first >= 0 && first + V::kPer <= nc) {
+          uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+          for (int e = 0; e < V::kPer; ++e)
+            granule_set<T>(w, e, *reinterpret_cast<const T*>(smem + (first + e) * V::kPitch + l * E));
+          mlf::st_vec(reinterpret_cast<uint4*>(gran), make_uint4(w[0], w[1], w[2], w[3]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < V::kPer; ++e) {
+            const int c = first + e;
+            if (c >= 0 && c < nc) *reinterpret_cast<T*>(gran + e * E) = *reinterpret_cast<const T*>(smem + c * V::kPitch + l * E);
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 // Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
 template <typename T, int DIR>
 __device__ MLF_TRANSPOSE_ATTR void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
@@ -493,9 +675,17 @@ __global__ void __launch_bounds__(kThreads) mlf_plan_kernel(const Seg* __restric
 #define MLF_STAGED_ATTR
 #endif
 template <int DIR>
-__device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* tsmem) {
+__device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* tsmem, uint8_t* vsmem) {
   if (g.kind == kRows) {
     rows_tile<DIR>(g, local, image);
+  } else if (g.kind == kTranspose && g.d == 0 && g.reserved == 2) {
+    // wide rows in vector form: staged in `vsmem` (kTransVSmemBytes)
+    switch (g.esize) {
+      case 1: transpose_tile_v<uint8_t, DIR>(g, local, image, vsmem); break;
+      case 2: transpose_tile_v<uint16_t, DIR>(g, local, image, vsmem); break;
+      case 4: transpose_tile_v<uint32_t, DIR>(g, local, image, vsmem); break;
+      default: transpose_tile_v<uint64_t, DIR>(g, local, image, vsmem); break;
+    }
   } else if (g.kind == kTranspose) {
     switch (g.esize) {
       case 1: transpose_tile<uint8_t, DIR>(g, local, image, tsmem); break;
@@ -808,7 +998,8 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* _
       __syncthreads();
       cached = sg;
     }
-    staged_tile<DIR>(g, local, image, tsmem);
+    // the ring of the streaming phase is idle by now: its first slot stages the vector-form transposes
+    staged_tile<DIR>(g, local, image, tsmem, ring);
   }
 }
 
@@ -824,6 +1015,7 @@ __global__ void mlf_wait_selftest_kernel(uint64_t budget_ns, int32_t* __restrict
 }
 
 constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
+static_assert(kTransVSmemBytes <= (int)mlf::kSlotBytes, "the vector-form transpose stages through one ring slot");
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
                                                                  const uint8_t* __restrict__ src, uint64_t nbytes) {
@@ -891,6 +1083,15 @@ bool use_bulk_kernel() {
   return bulk;
 }
 
+// MLF_TRANSPOSE_FORM=element keeps the element-wise wide transposes (comparison and fallback).
+bool use_vector_transpose() {
+  static const bool vec = []() {
+    const char* v = getenv("MLF_TRANSPOSE_FORM");
+    return !(v && std::string(v) == "element");
+  }();
+  return vec;
+}
+
 // ---- scratch of mlf_pack_noalloc ---------------------------------------------------------
 // Segment table, tile index and a status word for the entry point that may not allocate. The
 // array lives in every device that loads this library, from load until exit.
@@ -911,7 +1112,8 @@ uint32_t g_noalloc_host_tiles[kNoAllocMaxSegs + 1];
 
 // Turns one descriptor into a segment: validation, canonical form, kind and tile count.
 // On success *ntile_out is 0 if the descriptor moves nothing (the segment is then unused).
-int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg* seg_out, uint64_t* ntile_out,
+// `wide_v`: wide TRANSPOSE boxes get the vector-form tile geometry (only the bulk kernels can run it).
+int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, bool wide_v, Seg* seg_out, uint64_t* ntile_out,
                      uint64_t* payload_out, uint64_t* extent_out) {
   *ntile_out = 0;
   *payload_out = 0;
@@ -1054,6 +1256,11 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, Seg*
           const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
           tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
+        } else if (wide_v) {
+          const uint64_t cols = trans_v_cols(esize);
+          tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
+          tl = ((uint64_t)c.shape[last] + (uint64_t)kTransVL * kTransSub - 1) / ((uint64_t)kTransVL * kTransSub);
+          g.reserved = 2;
         } else {
           tc = ((uint64_t)c.shape[cdim] + kTransCols - 1) / kTransCols;
           tl = ((uint64_t)c.shape[last] + per_row * kTransSub - 1) / (per_row * kTransSub);
@@ -1102,6 +1309,8 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
 
   // Segments in table order: those made of linear tiles first, so that tiles [0, nlinear) are the
   // linear ones (a segment carries its own addresses, so the table order is free).
+  // the vector-form transposes stage through the ring's shared memory, which only the bulk kernels have
+  const bool wide_v = use_bulk_kernel() && use_vector_transpose();
   std::vector<Seg> linear_segs, staged_segs;
   std::vector<uint64_t> linear_tiles, staged_tiles;
   uint64_t tiles = 0, extent = 0, payload = 0;
@@ -1109,7 +1318,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   for (uint64_t i = 0; i < n; ++i) {
     Seg g;
     uint64_t ntile = 0, seg_payload = 0, seg_extent = 0;
-    const int32_t rc = plan_segment(descs[i], i, direction, &g, &ntile, &seg_payload, &seg_extent);
+    const int32_t rc = plan_segment(descs[i], i, direction, wide_v, &g, &ntile, &seg_payload, &seg_extent);
     if (rc != MLF_OK) return rc;
     if (ntile == 0) continue;
     payload += seg_payload;
@@ -1261,7 +1470,7 @@ int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_bas
   uint64_t tiles = 0, extent = 0;
   for (uint64_t i = 0; i < n; ++i) {
     uint64_t ntile = 0, seg_payload = 0, seg_extent = 0;
-    const int32_t rc = plan_segment(descs[i], i, MLF_PACK, &g_noalloc_host_segs[nseg], &ntile, &seg_payload, &seg_extent);
+    const int32_t rc = plan_segment(descs[i], i, MLF_PACK, false, &g_noalloc_host_segs[nseg], &ntile, &seg_payload, &seg_extent);
     if (rc != MLF_OK) return rc;
     if (ntile == 0) continue;
     extent = std::max(extent, seg_extent);

@@ -833,3 +833,70 @@ def test_bounded_arena_at_size_keeps_the_arena_small(shm_path):
         finally:
             com.teardown_pool()
     assert digests[0] == digests[1]
+
+
+def _pack_and_unpack_against_oracle(views, first_offset=3):
+    """Packs ``views`` with one plan, compares every byte of the image with the oracle's payloads,
+    then unpacks into zeroed twins of the views' storages and compares those with the sources."""
+    from ml_flashpoint import _native
+    from ml_flashpoint.core.gpu_engine import _Plan, c_strides, fill_desc
+
+    n = len(views)
+    descs = (_native.CopyDesc * n)()
+    offsets, at = [], first_offset
+    for i, v in enumerate(views):
+        offsets.append(at)
+        at += v.numel() * v.element_size() + 7 + (i % 16)
+    image = torch.full((at + 64,), 0xC3, dtype=torch.uint8, device="cuda")
+    for i, v in enumerate(views):
+        fill_desc(descs[i], v.data_ptr(), offsets[i], v.element_size(), v.shape, v.stride(), c_strides(v.shape))
+    stream = torch.cuda.current_stream().cuda_stream
+    plan = _Plan(descs, n, _native.MLF_PACK)
+    plan.launch(image.data_ptr(), image.numel(), stream)
+    torch.cuda.synchronize()
+    plan.status()
+    expect = bytearray(b"\xc3" * image.numel())
+    for v, o in zip(views, offsets):
+        payload = oracle.tensor_payload(v.cpu())
+        expect[o : o + len(payload)] = payload
+    got = image.cpu().numpy().tobytes()
+    if got != bytes(expect):
+        bad = next(i for i in range(len(got)) if got[i] != expect[i])
+        which = max(k for k, o in enumerate(offsets) if o <= bad)
+        pytest.fail(f"byte {bad} differs, view {which}: shape {tuple(views[which].shape)} stride {views[which].stride()} {views[which].dtype}")
+    targets, bases = [], []
+    for v in views:
+        base = torch.zeros_like(v._base)
+        bases.append(base)
+        targets.append(base.as_strided(v.shape, v.stride(), v.storage_offset()))
+    for i, t in enumerate(targets):
+        fill_desc(descs[i], t.data_ptr(), offsets[i], t.element_size(), t.shape, t.stride(), c_strides(t.shape))
+    plan = _Plan(descs, n, _native.MLF_UNPACK)
+    plan.launch(image.data_ptr(), image.numel(), stream)
+    torch.cuda.synchronize()
+    plan.status()
+    for k, (v, base) in enumerate(zip(views, bases)):
+        want = torch.zeros_like(base)
+        want.as_strided(v.shape, v.stride(), v.storage_offset()).copy_(v)
+        assert torch.equal(base, want), f"view {k}: shape {tuple(v.shape)} stride {v.stride()} {v.dtype}"
+
+
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.int16, torch.int32, torch.int64], ids=lambda d: str(d).split(".")[-1])
+def test_wide_transposes_in_vector_form_at_every_edge(dtype):
+    """Wide transposed views (image rows of 256 bytes or more) move through 16-byte granules on the
+    tensor side. Extents straddle the tile (112 bytes along the tensor's contiguous dimension, 128 and
+    512 elements along the image rows); row pitches and column offsets put the tensor rows on every
+    residue class of 16 bytes, so granules are shifted, partial at both ends, or exactly aligned."""
+    g = torch.Generator().manual_seed(29)
+    esize = torch.empty((), dtype=dtype).element_size()
+    per = 112 // esize  # image rows per tile
+    views = []
+    for n_c, n_l, pitch_extra, off in [
+        (1, 300, 0, 0), (1, 300, 3, 1), (per - 1, 129, 1, 1), (per, 512, 0, 0), (per + 1, 513, 5, 3),
+        (2 * per + 1, 700, 7, 5), (3, 1100, 13, 2), (per, 128, 16 // esize, 0), (5 * per, 384, 16 // esize, 16 // esize),
+    ]:
+        n_l = max(n_l, 256 // esize)  # keep the image rows wide
+        base = torch.randint(0, 250, (n_l, n_c + off + pitch_extra), generator=g, dtype=torch.int64).to(dtype).cuda()
+        views.append(base[:, off : off + n_c].t())
+    views.append(torch.randint(0, 250, (2, 600, 70), generator=g, dtype=torch.int64).to(dtype).cuda().transpose(1, 2))  # batched
+    _pack_and_unpack_against_oracle(views)
