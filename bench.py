@@ -354,6 +354,9 @@ def main() -> None:
     ap.add_argument("--probe", default=None, choices=[None, "host-link"],
                     help="host-link: plain copies between HBM and driver-allocated pinned memory in a process that "
                     "holds nothing else, rank by rank and all ranks at once; prints one JSON line and exits")
+    ap.add_argument("--probe-feed-only", action="store_true", help="host-link probe: only the restore-feed part")
+    ap.add_argument("--probe-alone-ranks", default=None,
+                    help="host-link probe: comma-separated ranks measured one at a time (default: every rank)")
     args = ap.parse_args()
     if args.probe == "host-link":
         run_host_link_probe(args)
@@ -515,10 +518,13 @@ def run_host_link_probe(args) -> None:
     for fn in ops.values():  # warm-up: first touch of the pinned pages by the device, kernel load
         fn()
     torch.cuda.synchronize()
+    alone_ranks = (
+        list(range(world_size)) if not args.probe_alone_ranks else [int(r) for r in args.probe_alone_ranks.split(",") if r != ""]
+    )
     result = {}
-    for name, fn in ops.items():
+    for name, fn in ({} if args.probe_feed_only else ops).items():
         alone = 0.0
-        for turn in range(world_size):  # one rank at a time
+        for turn in alone_ranks:  # one rank at a time
             barrier()
             if turn == rank:
                 alone = timed(fn)
@@ -558,6 +564,8 @@ def run_host_link_probe(args) -> None:
         "pread_threads_plus_lock_lane": (threads, 256),
         "lock_lane_alone": (-1, 256),
     }
+    if args.probe_feed_only:
+        feeds = {"pread_threads": (threads, 0)}
 
     def feed_once(nthreads, run_mib):
         obj = BufferObject(path)  # a fresh read-only mapping each time
@@ -574,7 +582,7 @@ def run_host_link_probe(args) -> None:
         feed_once(threads, 0)  # warm-up: ring slots, streams
         for name, (nthreads, run_mib) in feeds.items():
             alone, lane_share = 0.0, 0.0
-            for turn in range(world_size):
+            for turn in alone_ranks:
                 barrier()
                 if turn == rank:
                     alone, lane_bytes = feed_once(nthreads, run_mib)
@@ -599,6 +607,7 @@ def run_host_link_probe(args) -> None:
         os.remove(path)
     result["restore_feed"] = {
         "what": "4 GiB object file on tmpfs opened read-only into HBM (wall clock of the blocking call), page cache warm",
+        "bounce_chunk_kib": int(os.environ.get("MLF_BOUNCE_CHUNK_KIB", "0") or 0) or 4096,
         **feed_result,
     }
     if rank == 0:
