@@ -342,6 +342,8 @@ def main() -> None:
     ap.add_argument("--mode", default=None, choices=[None, "staged", "direct"], help="pack destination (default: staged)")
     ap.add_argument("--arena-limit-gb", type=float, default=0.0,
                     help="bound the HBM image arena (0 = hold the whole save): larger saves go through it piece by piece")
+    ap.add_argument("--landing-chunk-mb", type=float, default=0.0,
+                    help="replication: receive through a two-slot landing ring of this many MiB per slot (0 = whole-object landing buffer)")
     ap.add_argument("--no-restore", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replication", action="store_true")
@@ -687,7 +689,8 @@ def run_replication(args, rank, world_size, device, workdir, com, engine, items,
 
     # replicas land in a page-locked pool file of their own, like primaries do
     landing_pool = BufferPool(os.path.join(workdir, "replica_pool"), rank, 1, min(full, budget) + (1 << 20), register_cuda=True)
-    service = TransferService(replica_path_mapper=mapper, landing_pool=landing_pool)
+    service = TransferService(replica_path_mapper=mapper, landing_pool=landing_pool,
+                              landing_chunk_bytes=int(args.landing_chunk_mb * (1 << 20)))
     if service.initialize(0, threads=4, global_rank=rank) <= 0:
         raise RuntimeError("transfer service failed to start")
     addresses = [None] * world_size
@@ -818,6 +821,7 @@ def run_replication(args, rank, world_size, device, workdir, com, engine, items,
         "bit_exact": bool(all_ok),
         "bit_exact_how": "SHA-256 of the replica each rank received vs the digest of the sender's primary object (all_gather_object)",
         "hbm_held_bytes": int(all_max(float(held), device)),
+        "landing_chunk_bytes": int(args.landing_chunk_mb * (1 << 20)),
     }
     if digest_error:
         out["bit_exact_error"] = digest_error

@@ -147,8 +147,8 @@ __device__ __forceinline__ void drain_swizzled(uint8_t* __restrict__ dst, const 
   }
 }
 
-// Vector form of the wide TRANSPOSE tile (segments planned with g.reserved == 2, bulk kernels only).
-// The tensor side is read and written as aligned 16-byte granules instead of single elements:
+// Vector form of the wide TRANSPOSE tile (pack direction; segments planned with g.reserved == 2,
+// bulk kernels only). The tensor side is read as aligned 16-byte granules instead of single elements:
 // per tensor row (fixed l) a tile takes 8 granules = 128 bytes along C and delivers the 112 bytes
 // that are complete behind any misalignment of the row start (7 granules after the shift), so a
 // warp-wide access covers four rows of 128 contiguous bytes whatever the element size. A sub-tile is
@@ -162,10 +162,7 @@ struct TransV {
   static constexpr int kRowBytes = kL * E;       // one image row segment
   static constexpr int kPitch = E == 8 ? kRowBytes + 8 : kRowBytes + 4;  // keeps elements aligned, spreads rows over banks
   static constexpr int kPer = 16 / E;            // elements per granule
-  static constexpr int kWordsPerRow = kRowBytes / 4;
-  static constexpr int kWordsPerThread = (kC * kWordsPerRow + (int)kThreads - 1) / (int)kThreads;  // 14
   static constexpr int kDrainLanes = kRowBytes / 16 >= 32 ? 32 : 16;  // lanes that share one image row in the drain
-  static constexpr int kSmemBytes = kC * kPitch + 32;
 };
 constexpr int kTransVSmemBytes = 112 * (128 + 4) + 32;  // widest case (E = 1); fits one ring slot
 inline uint32_t trans_v_cols(uint32_t esize) { return 112u / esize; }
@@ -179,20 +176,6 @@ __device__ __forceinline__ T granule_elem(const uint4& v, int e) {
   if (E == 4) return (T)w[e];
   if (E == 2) return (T)((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
   return (T)((w[e >> 2] >> ((e & 3) * 8)) & 0xffu);
-}
-template <typename T>
-__device__ __forceinline__ void granule_set(uint32_t (&w)[4], int e, T x) {
-  constexpr int E = (int)sizeof(T);
-  if (E == 8) {
-    w[2 * e] = (uint32_t)((uint64_t)x & 0xffffffffu);
-    w[2 * e + 1] = (uint32_t)((uint64_t)x >> 32);
-  } else if (E == 4) {
-    w[e] = (uint32_t)x;
-  } else if (E == 2) {
-    w[e >> 1] |= (uint32_t)x << ((e & 1) * 16);
-  } else {
-    w[e >> 2] |= (uint32_t)x << ((e & 3) * 8);
-  }
 }
 
 // Wide TRANSPOSE tile, vector form. `smem` must hold kTransVSmemBytes. Must run with kThreads threads.
@@ -226,7 +209,8 @@ __device__ __noinline__ void transpose_tile_v(const Seg& g, uint32_t local, uint
   const unsigned j = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
   auto elems_of = [&](int s) { return (int)min((int64_t)V::kL, nL - (lfirst + (int64_t)s * V::kL)); };
 
-  if (DIR == MLF_PACK) {
+  static_assert(DIR == MLF_PACK, "the vector form exists for the pack direction only");
+  {
     uint4 v[4];
     auto load = [&](int s) {
       const int nl = elems_of(s);
@@ -265,64 +249,6 @@ __device__ __noinline__ void transpose_tile_v(const Seg& g, uint32_t local, uint
       for (unsigned r = tid / DL; r < (unsigned)nc; r += kThreads / DL) {
         const uint32_t at = r * (uint32_t)V::kPitch;
         mlf::drain_slot(irow + (int64_t)r * isC, smem + (at & ~15u), at & 15u, (uint32_t)nl * E, tid % DL, DL);
-      }
-      __syncthreads();
-    }
-  } else {
-    constexpr int N = V::kWordsPerThread;
-    uint32_t lo[N], hi[N];
-    auto load = [&](int s) {
-      const uint32_t nwords = ((uint32_t)elems_of(s) * E) >> 2;
-      const uint8_t* irow = ibase + (int64_t)s * V::kL * E;
-#pragma unroll
-      for (int k = 0; k < N; ++k) {
-        const uint32_t i = tid + (uint32_t)k * kThreads;
-        const uint32_t r = i / V::kWordsPerRow, w = i % V::kWordsPerRow;
-        ld_word_pair(irow + (int64_t)r * isC, w, r < (uint32_t)nc && w < nwords, &lo[k], &hi[k]);
-      }
-    };
-    load(0);
-    for (int s = 0; s < nsub; ++s) {
-      const int nl = elems_of(s);
-      const uint32_t row_len = (uint32_t)nl * E, nwords = row_len >> 2;
-      const uint8_t* irow = ibase + (int64_t)s * V::kL * E;
-#pragma unroll
-      for (int k = 0; k < N; ++k) {
-        const uint32_t i = tid + (uint32_t)k * kThreads;
-        const uint32_t r = i / V::kWordsPerRow, w = i % V::kWordsPerRow;
-        if (r < (uint32_t)nc && w < nwords)
-          *reinterpret_cast<uint32_t*>(smem + r * V::kPitch + w * 4u) = join_word_pair(irow + (int64_t)r * isC, lo[k], hi[k]);
-      }
-      const uint32_t tail = row_len & 3u;  // bytes after the last whole word of each image row
-      if (tail != 0 && tid < (unsigned)nc * tail) {
-        const uint32_t r = tid / tail, b = (nwords << 2) + tid % tail;
-        smem[r * V::kPitch + b] = irow[(int64_t)r * isC + b];
-      }
-      __syncthreads();
-      if (s + 1 < nsub) load(s + 1);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int l = (int)lr + 32 * k;
-        if (l >= nl) continue;
-        uint8_t* row = trow0 + ((int64_t)s * V::kL + l) * tsL;
-        const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
-        // aligned granule j of this tensor row holds row bytes [16 j - m, 16 j - m + 16)
-        const int first = ((int)(16u * j) - (int)m) / E;  // C index (relative to c0) of its first element; may be negative
-        if (first >= nc || first + V::kPer <= 0) continue;
-        uint8_t* gran = row - m + 16u * j;
-        if (first >= 0 && first + V::kPer <= nc) {
-          uint32_t w[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-          for (int e = 0; e < V::kPer; ++e)
-            granule_set<T>(w, e, *reinterpret_cast<const T*>(smem + (first + e) * V::kPitch + l * E));
-          mlf::st_vec(reinterpret_cast<uint4*>(gran), make_uint4(w[0], w[1], w[2], w[3]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < V::kPer; ++e) {
-            const int c = first + e;
-            if (c >= 0 && c < nc) *reinterpret_cast<T*>(gran + e * E) = *reinterpret_cast<const T*>(smem + c * V::kPitch + l * E);
-          }
-        }
       }
       __syncthreads();
     }
@@ -678,13 +604,13 @@ template <int DIR>
 __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* tsmem, uint8_t* vsmem) {
   if (g.kind == kRows) {
     rows_tile<DIR>(g, local, image);
-  } else if (g.kind == kTranspose && g.d == 0 && g.reserved == 2) {
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 2) {
     // wide rows in vector form: staged in `vsmem` (kTransVSmemBytes)
     switch (g.esize) {
-      case 1: transpose_tile_v<uint8_t, DIR>(g, local, image, vsmem); break;
-      case 2: transpose_tile_v<uint16_t, DIR>(g, local, image, vsmem); break;
-      case 4: transpose_tile_v<uint32_t, DIR>(g, local, image, vsmem); break;
-      default: transpose_tile_v<uint64_t, DIR>(g, local, image, vsmem); break;
+      case 1: transpose_tile_v<uint8_t, MLF_PACK>(g, local, image, vsmem); break;
+      case 2: transpose_tile_v<uint16_t, MLF_PACK>(g, local, image, vsmem); break;
+      case 4: transpose_tile_v<uint32_t, MLF_PACK>(g, local, image, vsmem); break;
+      default: transpose_tile_v<uint64_t, MLF_PACK>(g, local, image, vsmem); break;
     }
   } else if (g.kind == kTranspose) {
     switch (g.esize) {
@@ -1310,7 +1236,8 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   // Segments in table order: those made of linear tiles first, so that tiles [0, nlinear) are the
   // linear ones (a segment carries its own addresses, so the table order is free).
   // the vector-form transposes stage through the ring's shared memory, which only the bulk kernels have
-  const bool wide_v = use_bulk_kernel() && use_vector_transpose();
+  // (pack only: scattering into tensor granules measured slower than the element-wise form)
+  const bool wide_v = direction == MLF_PACK && use_bulk_kernel() && use_vector_transpose();
   std::vector<Seg> linear_segs, staged_segs;
   std::vector<uint64_t> linear_tiles, staged_tiles;
   uint64_t tiles = 0, extent = 0, payload = 0;

@@ -171,7 +171,8 @@ class _DeviceBuffer:
 
 
 class TransferService:
-    def __init__(self, replica_path_mapper: Optional[Callable[[str, int], str]] = None, landing_pool=None):
+    def __init__(self, replica_path_mapper: Optional[Callable[[str, int], str]] = None, landing_pool=None,
+                 landing_chunk_bytes: Optional[int] = None):
         """``replica_path_mapper(object_id, source_rank) -> path`` decides where a received object is
         stored. The default keeps the sender's path, which is right when peers have separate
         filesystems; ranks that share one must map replicas elsewhere or they would overwrite the
@@ -179,9 +180,18 @@ class TransferService:
 
         ``landing_pool`` is an optional ``BufferPool`` of page-locked files: received objects are then
         drained into a pool file by one copy-engine transfer (and appear as a symlink to it, like
-        objects saved through the pool) instead of into a fresh pageable file."""
+        objects saved through the pool) instead of into a fresh pageable file.
+
+        ``landing_chunk_bytes`` (default: ``MLFLASHPOINT_REPL_LANDING_CHUNK_BYTES``, 0 = off) bounds
+        the HBM a transfer holds: instead of a landing buffer the size of the object, the receiver keeps
+        two slots of that many bytes per sender and drains one to its file while the sender's copy
+        kernel fills the other; the sender's own bounce buffer shrinks to one slot as well. The NVLink
+        hop then runs at the pace of the receiver's drain to host memory."""
         self._map_path = replica_path_mapper or (lambda object_id, source_rank: object_id)
         self._landing_pool = landing_pool
+        if landing_chunk_bytes is None:
+            landing_chunk_bytes = int(os.environ.get("MLFLASHPOINT_REPL_LANDING_CHUNK_BYTES", "0") or 0)
+        self._landing_chunk = max(0, int(landing_chunk_bytes)) // 256 * 256
         self._listener: Optional[socket.socket] = None
         self._accept_thread: Optional[threading.Thread] = None
         self._workers: Optional[concurrent.futures.ThreadPoolExecutor] = None
@@ -435,6 +445,9 @@ class TransferService:
             peer = self._peer_pointer(reply)
             stream = self._stream
             twin = None if exact_path else gpu_engine.resident_image(dest_object_id, data_size - METADATA_SIZE)
+            if reply.get("chunked"):
+                self._put_in_chunks(sock, reply, peer, twin, data_ptr, data_size, dest_object_id)
+                return
             t0, t1 = ctypes.c_void_p(), ctypes.c_void_p()
             _native.check(lib.mlf_event_create(ctypes.byref(t0)))
             _native.check(lib.mlf_event_create(ctypes.byref(t1)))
@@ -495,6 +508,83 @@ class TransferService:
             if not final.get("ok"):
                 raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
 
+    def _put_in_chunks(self, sock, reply: dict, peer: int, twin, data_ptr: int, data_size: int, dest_object_id: str) -> None:
+        """Sender side of a transfer whose receiver keeps a two-slot landing ring: chunk k goes into
+        slot k mod 2 once the receiver has reported the chunk before last drained."""
+        from ml_flashpoint.core import gpu_engine
+
+        lib = _native.lib()
+        stream = self._stream
+        slot_bytes = int(reply["slot_bytes"])
+        nchunks = (data_size + slot_bytes - 1) // slot_bytes
+        t0, t1 = ctypes.c_void_p(), ctypes.c_void_p()
+        _native.check(lib.mlf_event_create(ctypes.byref(t0)))
+        _native.check(lib.mlf_event_create(ctypes.byref(t1)))
+        hop_ms, freed = 0.0, 0
+
+        def await_freed(upto: int) -> None:
+            nonlocal freed
+            while freed < upto:
+                note = _recv_msg(sock)
+                if note.get("op") != "slot_free":
+                    raise RuntimeError(f"peer failed while receiving '{dest_object_id}': {note.get('error', note)}")
+                freed += 1
+
+        try:
+            with contextlib.ExitStack() as lease:
+                image_ptr = None
+                if twin is not None:
+                    try:
+                        image_ptr = lease.enter_context(twin)
+                    except RuntimeError:
+                        image_ptr = None
+                bounce = None
+                if image_ptr is None:
+                    gpu_engine.wait_object_on_host(dest_object_id)
+                    with self._lock:
+                        if self._bounce is None or self._bounce.nbytes < slot_bytes:
+                            if self._bounce:
+                                self._bounce.free()
+                            self._bounce = _DeviceBuffer(slot_bytes)
+                        bounce = self._bounce
+                for k in range(nchunks):
+                    off = k * slot_bytes
+                    n = min(slot_bytes, data_size - off)
+                    await_freed(k - 1)  # chunk k - 2 has left the slot this chunk goes into
+                    slot = peer + (k % 2) * slot_bytes
+                    if image_ptr is not None:
+                        # object byte b < 4096 is the metadata block (host mapping), b >= 4096 is image[b - 4096]
+                        skip = 0
+                        if off < METADATA_SIZE:
+                            skip = min(n, METADATA_SIZE - off)
+                            _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(slot), ctypes.c_void_p(data_ptr + off), skip, _native.MLF_COPY_H2D, stream))
+                        _native.check(lib.mlf_event_record(t0, stream))
+                        if n > skip:
+                            _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(slot + skip), ctypes.c_void_p(image_ptr + off + skip - METADATA_SIZE), n - skip, stream, 0))
+                    else:
+                        _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(bounce.ptr), ctypes.c_void_p(data_ptr + off), n, 1, 0))
+                        _native.check(lib.mlf_event_record(t0, stream))
+                        _native.check(lib.mlf_copy_kernel_launch(ctypes.c_void_p(slot), ctypes.c_void_p(bounce.ptr), n, stream, 0))
+                    _native.check(lib.mlf_event_record(t1, stream))
+                    _native.check(lib.mlf_stream_sync(stream))
+                    ms = ctypes.c_float()
+                    _native.check(lib.mlf_event_elapsed_ms(t0, t1, ctypes.byref(ms)))
+                    hop_ms += float(ms.value)
+                    _send_msg(sock, {"op": "chunk", "k": k, "off": off, "len": n})
+                self._mark("data_sent")
+                await_freed(nchunks)
+            self.last_put_stats = {
+                "bytes": data_size, "hop_ms": hop_ms, "from_hbm_image": image_ptr is not None, "since_save_start_ms": None,
+                "in_peer_hbm_at": time.perf_counter(), "chunks": nchunks, "chunk_bytes": slot_bytes,
+            }
+        finally:
+            lib.mlf_event_destroy(t0)
+            lib.mlf_event_destroy(t1)
+        _send_msg(sock, {"op": "put_commit", "token": reply["token"]})
+        final = _recv_msg(sock)
+        if not final.get("ok"):
+            raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
+
     def _run_get(self, task_id: str, remote_object_id: str, source_address: str, local_object_id: str) -> None:
         with self._connect(source_address) as sock:
             self._mark("connection_acquired")
@@ -554,6 +644,9 @@ class TransferService:
         with self._lock:
             gate = self._inbound_locks.setdefault(source, threading.Lock())
         with gate:  # one inbound object per source at a time: they share the landing buffer
+            if self._landing_chunk and size > 2 * self._landing_chunk:
+                self._receive_in_chunks(conn, request, size, source)
+                return
             landing = self._inbound.get(source)
             if landing is None or landing.nbytes < size:
                 if landing:
@@ -603,6 +696,82 @@ class TransferService:
                 finally:
                     target.close()
                 os.rename(tmp_path, final_path)
+        _send_msg(conn, {"ok": True})
+
+    def _receive_in_chunks(self, conn: socket.socket, request: dict, size: int, source: int) -> None:
+        """Receiver side of a transfer through a two-slot landing ring (see ``landing_chunk_bytes``):
+        every announced chunk is drained from its slot into the object's file at once, then the slot
+        is reported free. The file is opened up front, under its temporary name."""
+        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+        lib = _native.lib()
+        chunk = self._landing_chunk
+        landing = self._inbound.get(source)
+        if landing is None or landing.nbytes < 2 * chunk:
+            if landing:
+                self._retired.append(landing)
+            landing = _DeviceBuffer(2 * chunk)
+            self._inbound[source] = landing
+        final_path = request["obj"] if request.get("exact_path") else self._map_path(request["obj"], source)
+        tmp_path = final_path + ".tmp"
+        os.makedirs(os.path.dirname(final_path), exist_ok=True)
+        for stale in (tmp_path, final_path):
+            if os.path.lexists(stale):
+                os.remove(stale)
+        pooled = None
+        if self._landing_pool is not None:
+            try:
+                pooled = self._landing_pool.acquire(associated_symlink=tmp_path)
+            except RuntimeError:
+                pooled = None
+        target = None
+        stream = ctypes.c_void_p()
+        _native.check(lib.mlf_stream_create(ctypes.byref(stream)))
+        try:
+            if pooled is not None:
+                pooled.ensure_total_size(size)
+                file_obj = pooled._buffer_io.buffer_obj
+            else:
+                target = BufferObject(tmp_path, size, overwrite=True)
+                file_obj = target
+            host = file_obj.get_data_ptr()
+            locked = bool(getattr(file_obj, "is_cuda_registered", False))
+            token = uuid.uuid4().hex
+            _send_msg(conn, {"ok": True, "transport": "nvlink", "token": token, "ipc": landing.ipc_hex, "ptr": landing.ptr,
+                             "pid": os.getpid(), "device": self._device, "chunked": True, "slot_bytes": chunk})
+            while True:
+                note = _recv_msg(conn)
+                if note.get("op") == "put_commit":
+                    if note.get("token") != token:
+                        raise RuntimeError("put was not committed by the sender")
+                    break
+                if note.get("op") != "chunk":
+                    raise RuntimeError(f"unexpected message during a chunked put: {note.get('op')}")
+                k, off, n = int(note["k"]), int(note["off"]), int(note["len"])
+                if off < 0 or n < 0 or n > chunk or off + n > size:
+                    raise RuntimeError("chunk outside the announced object")
+                slot = landing.ptr + (k % 2) * chunk
+                if locked:
+                    _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(host + off), ctypes.c_void_p(slot), n, _native.MLF_COPY_D2H, stream))
+                    _native.check(lib.mlf_stream_sync(stream))
+                else:
+                    _native.check(lib.mlf_bounce_copy(ctypes.c_void_p(slot), ctypes.c_void_p(host + off), n, 0, 0))
+                _send_msg(conn, {"op": "slot_free", "k": k})
+        except BaseException:
+            if target is not None:
+                target.close()
+                try:
+                    os.remove(tmp_path)
+                except OSError:
+                    pass
+            raise
+        finally:
+            lib.mlf_stream_destroy(stream)
+        if pooled is not None:
+            self._landing_pool.relink(pooled, tmp_path, final_path)
+        else:
+            target.close()
+            os.rename(tmp_path, final_path)
         _send_msg(conn, {"ok": True})
 
     def _serve_put_tcp(self, conn: socket.socket, request: dict, size: int, source: int) -> None:

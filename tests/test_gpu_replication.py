@@ -486,3 +486,45 @@ def test_two_devices_in_one_process_pack_replicate_and_restore(shm_path):
         gpu_engine.set_default_engine(None)
         for s in services:
             s.shutdown()
+
+
+@pytest.mark.parametrize("resident", [True, False])
+@pytest.mark.parametrize("pooled_landing", [False, True])
+def test_replication_through_a_two_slot_landing_ring(shm_path, resident, pooled_landing):
+    """With ``landing_chunk_bytes`` the receiver holds two small slots instead of a buffer the size of
+    the object: the sender's copy kernel fills one while the other drains to the file. Same replica
+    bytes whether the source is the save's HBM image or the host mapping, into a plain file or a
+    page-locked pool file, and the get direction (recovery) works through the same ring."""
+    from ml_flashpoint.core import gpu_engine
+    from ml_flashpoint.core.buffer_pool import BufferPool
+    from ml_flashpoint.replication.transfer_service.transfer_service_ext import ReplicaNamespace, TransferService
+
+    chunk = 64 << 10
+    space = ReplicaNamespace(str(shm_path / "replicas"))
+    pool = BufferPool(str(shm_path / "replica_pool"), rank=1, num_buffers=1, buffer_size=1 << 20, register_cuda=True) if pooled_landing else None
+    a = TransferService(landing_chunk_bytes=chunk)
+    b = TransferService(replica_path_mapper=space, landing_pool=pool, landing_chunk_bytes=chunk)
+    assert a.initialize(0, threads=4, global_rank=0) > 0 and b.initialize(0, threads=4, global_rank=1) > 0
+    try:
+        engine = gpu_engine.default_engine()
+        com, oid = _save_object(shm_path, engine, name="gpt2_tiny")  # 839 KB: thirteen chunks
+        primary = open(str(oid), "rb").read()
+        if not resident:
+            engine.drop_resident_images()
+        buf = com.get_buffer(oid)
+        assert a.async_put(buf.buffer_obj.get_data_ptr(), buf.buffer_obj.get_capacity(), b.address, str(oid)).result(timeout=60).success
+        buf.close()
+        stats = a.last_put_stats
+        assert stats["chunks"] == -(-len(primary) // chunk) and stats["from_hbm_image"] is resident
+        assert open(space(str(oid), 0), "rb").read() == primary
+        assert not os.path.exists(space(str(oid), 0) + ".tmp")
+        assert b.held_device_bytes() == 2 * chunk  # not the object's 839 KB
+        back = str(shm_path / "restored" / "obj.distcp")
+        os.makedirs(os.path.dirname(back))
+        assert a.async_get(str(oid), b.address, back).result(timeout=60).success
+        assert open(back, "rb").read() == primary
+    finally:
+        a.shutdown()
+        b.shutdown()
+        if pool is not None:
+            pool.teardown()
