@@ -255,6 +255,187 @@ __device__ __noinline__ void transpose_tile_v(const Seg& g, uint32_t local, uint
   }
 }
 
+// Asynchronous form of the wide TRANSPOSE tile (pack direction; segments planned with g.reserved == 3,
+// bulk kernels only). Tensor rows stream into shared memory as aligned 16-byte granules with
+// cp.async, two 32 KiB stages deep (128 tensor rows of 256 bytes each, of which the 240 bytes behind
+// any misalignment of the row start are delivered), so the loads of the next stage are in flight,
+// without holding registers, while this stage is written out. The image side is produced straight
+// from the staged tensor rows: a lane owns one image row, gathers the 16 / E elements of an aligned
+// 16-byte image vector column-wise (consecutive lanes read consecutive elements of one tensor row),
+// shifts by the image's byte misalignment and stores the vector. Image vectors that straddle two
+// stages take their leading bytes from a per-row carry of the previous stage's last 16 bytes; only
+// the first bytes and the last bytes of a tile's image rows are written bytewise.
+template <int E>
+struct TransA {
+  static constexpr int kLoadBytes = 256;
+  static constexpr int kOutBytes = 240;
+  static constexpr int kC = kOutBytes / E;            // image rows per tile: 240, 120, 60, 30
+  static constexpr int kL = 128;                      // tensor rows (elements along L) per stage
+  static constexpr int kStageBytes = kL * kLoadBytes; // 32 KiB
+  static constexpr int kPer = 16 / E;
+  static constexpr int kSegBytes = kL * E;            // bytes of one image row per full stage
+};
+constexpr int kTransASub = 8;                          // stages per tile
+constexpr int kTransAL = 128;
+constexpr int kTransACarryBytes = 240 * 16;            // one 16-byte carry per image row
+inline uint32_t trans_a_cols(uint32_t esize) { return 240u / esize; }
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(mlf::smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// `stages`: 2 x 32 KiB; `aux`: 2 x kTransACarryBytes of carry followed by 2 x 128 bytes of row shifts.
+template <typename T>
+__device__ __noinline__ void transpose_tile_a(const Seg& g, uint32_t local, uint8_t* image, uint8_t* stages, uint8_t* aux) {
+  constexpr int E = (int)sizeof(T);
+  using A = TransA<E>;
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  int64_t toff = 0, ioff = 0;
+  for (int d = L - 1; d >= 0; --d) {
+    if (d == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[d]);
+    batch /= (uint64_t)g.shape[d];
+    toff += idx * g.tstride[d];
+    ioff += idx * g.istride[d];
+  }
+  const int64_t nC = g.shape[C], nL = g.shape[L];
+  const int64_t tsL = g.tstride[L], isC = g.istride[C];
+  const int64_t c0 = (int64_t)(in_batch / g.b) * A::kC;
+  const int64_t lfirst = (int64_t)(in_batch % g.b) * (A::kL * kTransASub);
+  const int nsub = (int)min((int64_t)kTransASub, (nL - lfirst + A::kL - 1) / A::kL);
+  const int nc = (int)min((int64_t)A::kC, nC - c0);
+  const uint32_t row_bytes = (uint32_t)nc * E;
+  const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;
+  uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;  // image row c0 at element lfirst
+  const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+  uint8_t* carry_buf = aux;
+  uint8_t* shift_tab = aux + 2 * kTransACarryBytes;
+  auto elems_of = [&](int s) { return (int)min((int64_t)A::kL, nL - (lfirst + (int64_t)s * A::kL)); };
+
+  auto issue = [&](int s) {
+    const int nl = elems_of(s);
+    uint8_t* stage = stages + (s & 1) * A::kStageBytes;
+    uint8_t* shifts = shift_tab + (s & 1) * A::kL;
+    const unsigned j = tid & 15u, lr = tid >> 4;  // granule within the row; row within a pass of 16 rows
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int l = (int)lr + 16 * k;
+      if (l < nl) {
+        const uint8_t* row = trow0 + ((int64_t)s * A::kL + l) * tsL;
+        const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+        if (j == 0) shifts[l] = (uint8_t)m;
+        // only granules that hold at least one byte of the row are touched
+        if (16u * j < m + row_bytes) cp_async16(stage + l * A::kLoadBytes + 16u * j, row - m + 16u * j);
+      }
+    }
+    cp_async_commit();
+  };
+
+  issue(0);
+  if (nsub > 1) issue(1); else cp_async_commit();
+  for (int s = 0; s < nsub; ++s) {
+    if (s + 1 < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();  // stage s and its shift table are complete for every thread
+    const int nl = elems_of(s);
+    const int seg_len = nl * E;
+    const bool first = s == 0, last = s == nsub - 1;
+    const uint8_t* stage = stages + (s & 1) * A::kStageBytes;
+    const uint8_t* shifts = shift_tab + (s & 1) * A::kL;
+    const uint8_t* carry_in = carry_buf + ((s + 1) & 1) * kTransACarryBytes;  // written by stage s - 1
+    uint8_t* carry_out = carry_buf + (s & 1) * kTransACarryBytes;
+    // element e of image row c in this stage (e < 0: from the carry of the previous stage)
+    auto elem = [&](int c, int e) -> T {
+      if (e >= 0) return *reinterpret_cast<const T*>(stage + e * A::kLoadBytes + shifts[e] + c * E);
+      return *reinterpret_cast<const T*>(carry_in + c * 16 + (A::kPer + e) * E);
+    };
+    uint8_t* iseg = ibase + (int64_t)s * A::kSegBytes;  // image row c0, first byte of this stage
+    const int nblocks = (nc + 31) >> 5;
+    const int nvmax = (seg_len + 16 + 15) >> 4;
+    for (int item = (int)warp; item < nblocks * nvmax; item += (int)(kThreads >> 5)) {
+      const int c = (item % nblocks) * 32 + (int)lane;
+      const int vq = item / nblocks;
+      if (c >= nc) continue;
+      uint8_t* row = iseg + (int64_t)c * isC;
+      const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);  // the same in every stage: stages are multiples of 16 bytes
+      const int q = (h ? h - 16 : 0) + 16 * vq;  // stage-relative first byte of this aligned vector
+      if (q + 16 > seg_len || (first && q < 0)) continue;
+      const int e0 = q >= 0 ? q / E : -((-q + E - 1) / E);  // floor
+      const int sh = q - e0 * E;                            // 0 .. E - 1
+      uint32_t w[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int i = 0; i < A::kPer; ++i) {
+        const T x = elem(c, e0 + i);
+        if (E == 8) {
+          w[2 * i] = (uint32_t)((uint64_t)x & 0xffffffffu);
+          w[2 * i + 1] = (uint32_t)((uint64_t)x >> 32);
+        } else if (E == 4) {
+          w[i] = (uint32_t)x;
+        } else if (E == 2) {
+          w[i >> 1] |= (uint32_t)x << ((i & 1) * 16);
+        } else {
+          w[i >> 2] |= (uint32_t)x << ((i & 3) * 8);
+        }
+      }
+      uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
+      if (sh) {  // the image is not aligned to the element size: one more element, then shift
+        const T x = elem(c, e0 + A::kPer);
+        if (E == 8) {
+          w[4] = (uint32_t)((uint64_t)x & 0xffffffffu);
+          w[5] = (uint32_t)((uint64_t)x >> 32);
+        } else {
+          w[4] = (uint32_t)x;
+        }
+        out = mlf::realign(out, make_uint4(w[4], w[5], 0u, 0u), (unsigned)sh);
+      }
+      mlf::st_vec(reinterpret_cast<uint4*>(row + q), out);
+    }
+    if (!last) {
+      // the last 16 bytes of every image row of this stage, for the vectors that straddle into the next one
+      for (int c = (int)tid; c < nc; c += (int)kThreads)
+#pragma unroll
+        for (int i = 0; i < A::kPer; ++i) *reinterpret_cast<T*>(carry_out + c * 16 + i * E) = elem(c, nl - A::kPer + i);
+    }
+    if (first) {
+      // bytes before the first aligned vector of each image row
+      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
+        const int c = idx / 15, k = idx % 15;
+        uint8_t* row = iseg + (int64_t)c * isC;
+        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+        if (k < h && k < seg_len) row[k] = stage[(k / E) * A::kLoadBytes + shifts[k / E] + c * E + k % E];
+      }
+    }
+    if (last) {
+      // bytes behind the last aligned vector of each image row
+      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
+        const int c = idx / 15, k = idx % 15;
+        uint8_t* row = iseg + (int64_t)c * isC;
+        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+        // vectors of this stage end at the last 16-byte boundary of the image inside the segment
+        int done = seg_len - (int)(((uintptr_t)row + (uint32_t)seg_len) & 15u);
+        if (first && done < h) done = min(h, seg_len);  // the segment holds no aligned vector at all
+        const int b = done + k;
+        if (b >= seg_len || (first && b < h)) continue;
+        if (b >= 0)
+          row[b] = stage[(b / E) * A::kLoadBytes + shifts[b / E] + c * E + b % E];
+        else if (!first)
+          row[b] = carry_in[c * 16 + 16 + b];  // a last stage shorter than the image's misalignment: the previous stage's tail
+      }
+    }
+    __syncthreads();  // every thread is done with stage s: its buffer may be refilled
+    if (s + 2 < nsub) issue(s + 2); else cp_async_commit();
+  }
+  cp_async_wait<0>();
+}
+
 // Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
 template <typename T, int DIR>
 __device__ MLF_TRANSPOSE_ATTR void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
@@ -604,6 +785,14 @@ template <int DIR>
 __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* tsmem, uint8_t* vsmem) {
   if (g.kind == kRows) {
     rows_tile<DIR>(g, local, image);
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 3) {
+    // wide rows in asynchronous form: two 32 KiB stages in `vsmem` (the idle ring), carries in `tsmem`
+    switch (g.esize) {
+      case 1: transpose_tile_a<uint8_t>(g, local, image, vsmem, tsmem); break;
+      case 2: transpose_tile_a<uint16_t>(g, local, image, vsmem, tsmem); break;
+      case 4: transpose_tile_a<uint32_t>(g, local, image, vsmem, tsmem); break;
+      default: transpose_tile_a<uint64_t>(g, local, image, vsmem, tsmem); break;
+    }
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 2) {
     // wide rows in vector form: staged in `vsmem` (kTransVSmemBytes)
     switch (g.esize) {
@@ -942,6 +1131,8 @@ __global__ void mlf_wait_selftest_kernel(uint64_t budget_ns, int32_t* __restrict
 
 constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
 static_assert(kTransVSmemBytes <= (int)mlf::kSlotBytes, "the vector-form transpose stages through one ring slot");
+static_assert(2 * 128 * 256 <= (int)kBulkDynSmem, "the asynchronous transpose uses the ring as two 32 KiB stages");
+static_assert(2 * kTransACarryBytes + 2 * kTransAL <= kTransSmemBytes, "carries and shift tables fit the static staging area");
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
                                                                  const uint8_t* __restrict__ src, uint64_t nbytes) {
@@ -1009,13 +1200,16 @@ bool use_bulk_kernel() {
   return bulk;
 }
 
-// MLF_TRANSPOSE_FORM=element keeps the element-wise wide transposes (comparison and fallback).
-bool use_vector_transpose() {
-  static const bool vec = []() {
+// Form of the wide transposes in pack plans: MLF_TRANSPOSE_FORM = async (default) | vector | element.
+int wide_transpose_form() {
+  static const int form = []() {
     const char* v = getenv("MLF_TRANSPOSE_FORM");
-    return !(v && std::string(v) == "element");
+    const std::string want = v ? v : "";
+    if (want == "element") return 0;
+    if (want == "vector") return 2;
+    return 3;
   }();
-  return vec;
+  return form;
 }
 
 // ---- scratch of mlf_pack_noalloc ---------------------------------------------------------
@@ -1038,8 +1232,9 @@ uint32_t g_noalloc_host_tiles[kNoAllocMaxSegs + 1];
 
 // Turns one descriptor into a segment: validation, canonical form, kind and tile count.
 // On success *ntile_out is 0 if the descriptor moves nothing (the segment is then unused).
-// `wide_v`: wide TRANSPOSE boxes get the vector-form tile geometry (only the bulk kernels can run it).
-int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, bool wide_v, Seg* seg_out, uint64_t* ntile_out,
+// `wide_form`: tile geometry of wide TRANSPOSE boxes: 0 element-wise, 2 vector form, 3 asynchronous
+// form (the last two only exist in the bulk kernels, for the pack direction).
+int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int wide_form, Seg* seg_out, uint64_t* ntile_out,
                      uint64_t* payload_out, uint64_t* extent_out) {
   *ntile_out = 0;
   *payload_out = 0;
@@ -1182,7 +1377,12 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, bool
           const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
           tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
-        } else if (wide_v) {
+        } else if (wide_form == 3) {
+          const uint64_t cols = trans_a_cols(esize);
+          tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
+          tl = ((uint64_t)c.shape[last] + (uint64_t)kTransAL * kTransASub - 1) / ((uint64_t)kTransAL * kTransASub);
+          g.reserved = 3;
+        } else if (wide_form == 2) {
           const uint64_t cols = trans_v_cols(esize);
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransVL * kTransSub - 1) / ((uint64_t)kTransVL * kTransSub);
@@ -1237,7 +1437,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   // linear ones (a segment carries its own addresses, so the table order is free).
   // the vector-form transposes stage through the ring's shared memory, which only the bulk kernels have
   // (pack only: scattering into tensor granules measured slower than the element-wise form)
-  const bool wide_v = direction == MLF_PACK && use_bulk_kernel() && use_vector_transpose();
+  const int wide_form = direction == MLF_PACK && use_bulk_kernel() ? wide_transpose_form() : 0;
   std::vector<Seg> linear_segs, staged_segs;
   std::vector<uint64_t> linear_tiles, staged_tiles;
   uint64_t tiles = 0, extent = 0, payload = 0;
@@ -1245,7 +1445,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   for (uint64_t i = 0; i < n; ++i) {
     Seg g;
     uint64_t ntile = 0, seg_payload = 0, seg_extent = 0;
-    const int32_t rc = plan_segment(descs[i], i, direction, wide_v, &g, &ntile, &seg_payload, &seg_extent);
+    const int32_t rc = plan_segment(descs[i], i, direction, wide_form, &g, &ntile, &seg_payload, &seg_extent);
     if (rc != MLF_OK) return rc;
     if (ntile == 0) continue;
     payload += seg_payload;
@@ -1397,7 +1597,7 @@ int32_t mlf_pack_noalloc(const mlf_copy_desc* descs, uint64_t n, void* image_bas
   uint64_t tiles = 0, extent = 0;
   for (uint64_t i = 0; i < n; ++i) {
     uint64_t ntile = 0, seg_payload = 0, seg_extent = 0;
-    const int32_t rc = plan_segment(descs[i], i, MLF_PACK, false, &g_noalloc_host_segs[nseg], &ntile, &seg_payload, &seg_extent);
+    const int32_t rc = plan_segment(descs[i], i, MLF_PACK, 0, &g_noalloc_host_segs[nseg], &ntile, &seg_payload, &seg_extent);
     if (rc != MLF_OK) return rc;
     if (ntile == 0) continue;
     extent = std::max(extent, seg_extent);
