@@ -436,6 +436,147 @@ __device__ __noinline__ void transpose_tile_a(const Seg& g, uint32_t local, uint
   cp_async_wait<0>();
 }
 
+// Matrix form of the wide TRANSPOSE tile: 16-bit elements, pack direction, tensor rows that all start
+// on 16-byte boundaries (segments planned with g.reserved == 4, bulk kernels only). Stages of 128
+// tensor rows by 64 elements (128 bytes) arrive by cp.async, two deep, granules XOR-swizzled so that
+// the warp-level matrix loads below are conflict-free. One ldmatrix.x4.trans per warp turns a block of
+// 32 rows by 8 elements into registers that hold, per thread, 8 CONSECUTIVE elements of one image
+// row (the four 8x8 matrices are given interleaved row lists for exactly that), i.e. one aligned
+// 16-byte piece of the image row, which goes to an image-order staging area with a single 16-byte
+// shared-memory store. The staging rows are then written out as aligned 16-byte image vectors,
+// shifted by the image's byte misalignment; vectors that straddle two stages take their leading
+// bytes from a per-row carry, so only the two ends of a tile's image rows are written bytewise.
+constexpr int kTransMCols = 64;     // elements along C per tile (128 bytes of each tensor row)
+constexpr int kTransML = 128;       // tensor rows per stage
+constexpr int kTransMSub = 8;       // stages per tile
+constexpr int kTransMStageBytes = kTransML * 128;      // 16 KiB, tensor order
+constexpr int kTransMPitch = 320;                       // image-order staging row: 256 data bytes, pitch = 4 mod 8 granules
+constexpr int kTransMStagingOff = 2 * kTransMStageBytes;
+constexpr int kTransMCarryBytes = kTransMCols * 16;    // per parity
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(mlf::smem_addr(smem_row)));
+}
+// position of granule g of tensor row l inside its 128-byte stage row
+__device__ __forceinline__ uint32_t matrix_swizzle(uint32_t l, uint32_t g) { return (g ^ ((((l >> 3) & 3u) << 1) | (l & 1u))) << 4; }
+
+// `ring`: two tensor-order stages, then the image-order staging area; `aux`: two parities of carries.
+__device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint8_t* image, uint8_t* ring, uint8_t* aux) {
+  constexpr int E = 2;
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  int64_t toff = 0, ioff = 0;
+  for (int d = L - 1; d >= 0; --d) {
+    if (d == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[d]);
+    batch /= (uint64_t)g.shape[d];
+    toff += idx * g.tstride[d];
+    ioff += idx * g.istride[d];
+  }
+  const int64_t nC = g.shape[C], nL = g.shape[L];
+  const int64_t tsL = g.tstride[L], isC = g.istride[C];
+  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransMCols;
+  const int64_t lfirst = (int64_t)(in_batch % g.b) * (kTransML * kTransMSub);
+  const int nsub = (int)min((int64_t)kTransMSub, (nL - lfirst + kTransML - 1) / kTransML);
+  const int nc = (int)min((int64_t)kTransMCols, nC - c0);
+  const uint32_t row_bytes = (uint32_t)nc * E;
+  const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;  // 16-byte aligned
+  uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;
+  const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+  uint8_t* staging = ring + kTransMStagingOff;
+  auto elems_of = [&](int s) { return (int)min((int64_t)kTransML, nL - (lfirst + (int64_t)s * kTransML)); };
+
+  auto issue = [&](int s) {
+    const int nl = elems_of(s);
+    uint8_t* stage = ring + (s & 1) * kTransMStageBytes;
+    const unsigned gq = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const unsigned l = lr + 32u * k;
+      if ((int)l < nl && 16u * gq < row_bytes)
+        cp_async16(stage + l * 128u + matrix_swizzle(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
+    }
+    cp_async_commit();
+  };
+
+  issue(0);
+  if (nsub > 1) issue(1); else cp_async_commit();
+  for (int s = 0; s < nsub; ++s) {
+    if (s + 1 < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();  // stage s has landed; every thread is done draining the staging area of stage s - 1
+    const int nl = elems_of(s);
+    const int seg_len = nl * E;
+    const bool first = s == 0, last = s == nsub - 1;
+    const uint8_t* stage = ring + (s & 1) * kTransMStageBytes;
+    // ---- transpose: blocks of 32 tensor rows by 8 elements, four per warp
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const unsigned blk = warp + 8u * b, lb = blk >> 3, cb = blk & 7u;
+      // lane = 8 i + k supplies row k of matrix i: tensor row 32 lb + 8 (k / 2) + 2 i + (k % 2)
+      const unsigned i = lane >> 3, k = lane & 7u;
+      const unsigned l = 32u * lb + 8u * (k >> 1) + 2u * i + (k & 1u);
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, stage + l * 128u + matrix_swizzle(l, cb));
+      // this thread now holds image row 8 cb + lane / 4, elements 32 lb + 8 (lane % 4) .. + 7
+      const unsigned c = 8u * cb + (lane >> 2), l0 = 32u * lb + 8u * (lane & 3u);
+      *reinterpret_cast<uint4*>(staging + c * kTransMPitch + l0 * E) = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+    __syncthreads();  // staging holds the stage in image order; the tensor-order buffer is free again
+    if (s + 2 < nsub) issue(s + 2); else cp_async_commit();
+    // ---- write out: aligned 16-byte image vectors, 17 candidate positions per image row
+    const uint8_t* carry_in = aux + ((s + 1) & 1) * kTransMCarryBytes;  // last 16 bytes of stage s - 1 per image row
+    uint8_t* carry_out = aux + (s & 1) * kTransMCarryBytes;
+    uint8_t* iseg = ibase + (int64_t)s * (kTransML * E);
+    for (int idx = (int)tid; idx < nc * 17; idx += (int)kThreads) {
+      const int c = idx / 17, vq = idx % 17;
+      uint8_t* row = iseg + (int64_t)c * isC;
+      const uint8_t* data = staging + c * kTransMPitch;
+      const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);  // the same in every stage
+      if (vq == 16 && !last) *reinterpret_cast<uint4*>(carry_out + c * 16) = *reinterpret_cast<const uint4*>(data + 240);
+      if (h == 0) {
+        if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
+      } else {
+        const int q = h - 16 + 16 * vq;  // stage-relative first byte of the vector
+        if (q + 16 <= seg_len && !(first && vq == 0)) {
+          const uint4 lo = vq == 0 ? *reinterpret_cast<const uint4*>(carry_in + c * 16) : *reinterpret_cast<const uint4*>(data + 16 * (vq - 1));
+          const uint4 hi = *reinterpret_cast<const uint4*>(data + 16 * vq);
+          mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
+        }
+      }
+    }
+    if (first) {
+      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
+        const int c = idx / 15, kb = idx % 15;
+        uint8_t* row = iseg + (int64_t)c * isC;
+        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+        if (kb < h && kb < seg_len) row[kb] = staging[c * kTransMPitch + kb];
+      }
+    }
+    if (last) {
+      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
+        const int c = idx / 15, kb = idx % 15;
+        uint8_t* row = iseg + (int64_t)c * isC;
+        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+        int done = seg_len - (int)(((uintptr_t)row + (uint32_t)seg_len) & 15u);  // last 16-byte boundary of the image inside the segment
+        if (first && done < h) done = min(h, seg_len);
+        const int b = done + kb;
+        if (b >= seg_len || (first && b < h)) continue;
+        if (b >= 0)
+          row[b] = staging[c * kTransMPitch + b];
+        else if (!first)
+          row[b] = carry_in[c * 16 + 16 + b];
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // the staging area and the carries are free for the next tile
+}
+
 // Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
 template <typename T, int DIR>
 __device__ MLF_TRANSPOSE_ATTR void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
@@ -785,6 +926,8 @@ template <int DIR>
 __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* tsmem, uint8_t* vsmem) {
   if (g.kind == kRows) {
     rows_tile<DIR>(g, local, image);
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 4) {
+    transpose_tile_m(g, local, image, vsmem, tsmem);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 3) {
     // wide rows in asynchronous form: two 32 KiB stages in `vsmem` (the idle ring), carries in `tsmem`
     switch (g.esize) {
@@ -1133,6 +1276,8 @@ constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
 static_assert(kTransVSmemBytes <= (int)mlf::kSlotBytes, "the vector-form transpose stages through one ring slot");
 static_assert(2 * 128 * 256 <= (int)kBulkDynSmem, "the asynchronous transpose uses the ring as two 32 KiB stages");
 static_assert(2 * kTransACarryBytes + 2 * kTransAL <= kTransSmemBytes, "carries and shift tables fit the static staging area");
+static_assert(kTransMStagingOff + kTransMCols * kTransMPitch <= (int)kBulkDynSmem, "matrix form: two stages and the staging area fit the ring");
+static_assert(2 * kTransMCarryBytes <= kTransSmemBytes, "matrix form: carries fit the static staging area");
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
                                                                  const uint8_t* __restrict__ src, uint64_t nbytes) {
@@ -1200,14 +1345,15 @@ bool use_bulk_kernel() {
   return bulk;
 }
 
-// Form of the wide transposes in pack plans: MLF_TRANSPOSE_FORM = async (default) | vector | element.
+// Form of the wide transposes in pack plans: MLF_TRANSPOSE_FORM = matrix (default) | vector | async | element.
 int wide_transpose_form() {
   static const int form = []() {
     const char* v = getenv("MLF_TRANSPOSE_FORM");
     const std::string want = v ? v : "";
     if (want == "element") return 0;
+    if (want == "async") return 3;
     if (want == "vector") return 2;
-    return 3;
+    return 4;
   }();
   return form;
 }
@@ -1232,8 +1378,17 @@ uint32_t g_noalloc_host_tiles[kNoAllocMaxSegs + 1];
 
 // Turns one descriptor into a segment: validation, canonical form, kind and tile count.
 // On success *ntile_out is 0 if the descriptor moves nothing (the segment is then unused).
+// The matrix form moves 16-bit elements whose tensor rows all start on 16-byte boundaries.
+bool matrix_form_eligible(uint32_t esize, uint64_t tensor_ptr, const Canon& c, int cdim) {
+  if (esize != 2 || (tensor_ptr & 15u)) return false;
+  for (int k = 0; k < c.ndim; ++k)
+    if (k != cdim && (c.ts[k] & 15)) return false;
+  return true;
+}
+
 // `wide_form`: tile geometry of wide TRANSPOSE boxes: 0 element-wise, 2 vector form, 3 asynchronous
-// form (the last two only exist in the bulk kernels, for the pack direction).
+// form, 4 matrix form where eligible and vector form elsewhere (all but 0 only exist in the bulk
+// kernels, for the pack direction).
 int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int wide_form, Seg* seg_out, uint64_t* ntile_out,
                      uint64_t* payload_out, uint64_t* extent_out) {
   *ntile_out = 0;
@@ -1377,12 +1532,16 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
           const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
           tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
+        } else if (wide_form == 4 && matrix_form_eligible(esize, d.tensor_ptr, c, cdim)) {
+          tc = ((uint64_t)c.shape[cdim] + kTransMCols - 1) / kTransMCols;
+          tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
+          g.reserved = 4;
         } else if (wide_form == 3) {
           const uint64_t cols = trans_a_cols(esize);
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransAL * kTransASub - 1) / ((uint64_t)kTransAL * kTransASub);
           g.reserved = 3;
-        } else if (wide_form == 2) {
+        } else if (wide_form == 2 || wide_form == 4) {
           const uint64_t cols = trans_v_cols(esize);
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransVL * kTransSub - 1) / ((uint64_t)kTransVL * kTransSub);
