@@ -353,15 +353,20 @@ def main() -> None:
     ap.add_argument("--cpu-baseline-budget-s", type=float, default=20.0, help="time budget of the CPU-baseline leg's saves")
     ap.add_argument("--workdir", default=None)
     ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
-    ap.add_argument("--probe", default=None, choices=[None, "host-link"],
+    ap.add_argument("--probe", default=None, choices=[None, "host-link", "transpose"],
                     help="host-link: plain copies between HBM and driver-allocated pinned memory in a process that "
-                    "holds nothing else, rank by rank and all ranks at once; prints one JSON line and exits")
+                    "holds nothing else, rank by rank and all ranks at once; transpose: kernel-only pack / unpack "
+                    "timing of transposed views through the C ABI; each prints one JSON line and exits")
+    ap.add_argument("--probe-case", default=None, help="transpose probe: run only the case with this name")
     ap.add_argument("--probe-feed-only", action="store_true", help="host-link probe: only the restore-feed part")
     ap.add_argument("--probe-alone-ranks", default=None,
                     help="host-link probe: comma-separated ranks measured one at a time (default: every rank)")
     args = ap.parse_args()
     if args.probe == "host-link":
         run_host_link_probe(args)
+        return
+    if args.probe == "transpose":
+        run_transpose_probe(args)
         return
     if args.impl == "mlf_b200":
         args.warmup = max(args.warmup, 3)  # fewer warm-up saves would time plan creation and buffer sizing
@@ -473,6 +478,96 @@ def run_reference_arm(args, device, workdir: str) -> None:
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def run_transpose_probe(args) -> None:
+    """Kernel-only throughput of transposed views, pack and unpack, through the C ABI (one plan, one
+    launch per direction, CUDA events, L2 flushed between launches), each result checked against
+    torch. Read + write bytes per second. ``MLF_TRANSPOSE_FORM`` selects the form of wide pack
+    transposes (matrix | vector | async | element)."""
+    from ml_flashpoint import _native
+    from ml_flashpoint.core.gpu_engine import _Plan, c_strides, fill_desc
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    gen = torch.Generator(device=device).manual_seed(7)
+
+    def rnd(shape, dtype):
+        if dtype in (torch.int64, torch.uint8):
+            return torch.randint(0, 250, shape, dtype=dtype, device=device, generator=gen)
+        return torch.randn(shape, device=device, generator=gen).to(dtype)
+
+    def run(views):
+        n = len(views)
+        descs = (_native.CopyDesc * n)()
+        offsets, at = [], 7
+        for v in views:
+            offsets.append(at)
+            at += v.numel() * v.element_size() + 137
+        image = torch.zeros(at + 64, dtype=torch.uint8, device=device)
+        stream = torch.cuda.current_stream().cuda_stream
+        rates = {}
+        for direction in ("pack", "unpack"):
+            if direction == "pack":
+                ends = views
+            else:
+                ends = [torch.zeros_like(v._base if v._base is not None else v).as_strided(v.shape, v.stride(), v.storage_offset()) for v in views]
+            for i, t in enumerate(ends):
+                fill_desc(descs[i], t.data_ptr(), offsets[i], t.element_size(), t.shape, t.stride(), c_strides(t.shape))
+            plan = _Plan(descs, n, _native.MLF_PACK if direction == "pack" else _native.MLF_UNPACK)
+            times = []
+            for it in range(5):
+                flush.fill_(it)
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                plan.launch(image.data_ptr(), image.numel(), stream)
+                t1.record()
+                torch.cuda.synchronize()
+                plan.status()
+                times.append(t0.elapsed_time(t1))
+            ms = sorted(times[1:])[len(times[1:]) // 2]
+            rates[direction] = 2 * plan.payload / 1e9 / (ms / 1e3)
+            for v, t, o in zip(views, ends, offsets):
+                if direction == "pack":
+                    nbytes = v.numel() * v.element_size()
+                    assert torch.equal(image[o : o + nbytes], v.contiguous().reshape(-1).view(torch.uint8)), "pack differs from torch"
+                else:
+                    assert torch.equal(t, v), "unpack differs from torch"
+        return {"payload_mb": round(sum(v.numel() * v.element_size() for v in views) / 1e6, 1),
+                "pack_gbs": round(rates["pack"]), "unpack_gbs": round(rates["unpack"])}
+
+    def microbench_views(kind):
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import workloads
+
+        tensors = list(workloads.packing_microbench(device).values())
+        transposed = [t for t in tensors if not t.is_contiguous()]
+        if kind == "wide":
+            return [t for t in transposed if t.shape[-1] * t.element_size() >= 256]
+        return transposed if kind == "transposed" else tensors
+
+    cases = {
+        "flat_bf16_1gib": lambda: [rnd((512 << 20,), torch.bfloat16)],
+        "uint8_square": lambda: [rnd((16384, 16384), torch.uint8).t()],
+        "bf16_square_odd_pitch": lambda: [rnd((11585, 11585), torch.bfloat16).t()],
+        "fp32_square": lambda: [rnd((8192, 8192), torch.float32).t()],
+        "int64_square": lambda: [rnd((5792, 5792), torch.int64).t()],
+        "bf16_weight_14336x4096": lambda: [rnd((14336, 4096), torch.bfloat16).t()],
+        "fp32_weight_4096x14336": lambda: [rnd((4096, 14336), torch.float32).t()],
+        "bf16_batched_64x1000x300": lambda: [rnd((64, 1000, 300), torch.bfloat16).mT],
+        "microbench_transposed_wide_rows": lambda: microbench_views("wide"),
+        "microbench_transposed_all": lambda: microbench_views("transposed"),
+        "microbench_all_1024_tensors": lambda: microbench_views("all"),
+    }
+    results = {}
+    for name, make in cases.items():
+        if args.probe_case and name != args.probe_case:
+            continue
+        results[name] = run(make())
+        torch.cuda.empty_cache()
+    print(json.dumps({"probe": "transpose", "form": os.environ.get("MLF_TRANSPOSE_FORM", "matrix"),
+                      "unit": "GB/s of read + write bytes, kernel only, median of 4 launches", "results": results}))
 
 
 def run_host_link_probe(args) -> None:
