@@ -528,16 +528,16 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
     }
     __syncthreads();  // staging holds the stage in image order; the tensor-order buffer is free again
     if (s + 2 < nsub) issue(s + 2); else cp_async_commit();
-    // ---- write out: aligned 16-byte image vectors, 17 candidate positions per image row
+    // ---- write out: aligned 16-byte image vectors, 16 positions per image row
     const uint8_t* carry_in = aux + ((s + 1) & 1) * kTransMCarryBytes;  // last 16 bytes of stage s - 1 per image row
     uint8_t* carry_out = aux + (s & 1) * kTransMCarryBytes;
     uint8_t* iseg = ibase + (int64_t)s * (kTransML * E);
-    for (int idx = (int)tid; idx < nc * 17; idx += (int)kThreads) {
-      const int c = idx / 17, vq = idx % 17;
+    // 16 lanes per image row take the 16 vector positions (a warp-wide store covers two rows of 256
+    // contiguous bytes)
+    auto emit = [&](int c, int vq) {
       uint8_t* row = iseg + (int64_t)c * isC;
       const uint8_t* data = staging + c * kTransMPitch;
       const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);  // the same in every stage
-      if (vq == 16 && !last) *reinterpret_cast<uint4*>(carry_out + c * 16) = *reinterpret_cast<const uint4*>(data + 240);
       if (h == 0) {
         if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
       } else {
@@ -548,7 +548,16 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
           mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
         }
       }
+    };
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = (int)(tid >> 4) + 16 * k;
+      if (c < nc) emit(c, (int)(tid & 15u));
     }
+    // (a stage holds 16 vector positions per row whatever the misalignment: with h != 0 the first one
+    // straddles in from the previous stage and the row's last 16 - h bytes wait in the carry)
+    if (!last && (int)tid < nc)
+      *reinterpret_cast<uint4*>(carry_out + tid * 16) = *reinterpret_cast<const uint4*>(staging + tid * kTransMPitch + 240);
     if (first) {
       for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
         const int c = idx / 15, kb = idx % 15;
