@@ -554,6 +554,7 @@ def run_transpose_probe(args) -> None:
         "fp32_square": lambda: [rnd((8192, 8192), torch.float32).t()],
         "int64_square": lambda: [rnd((5792, 5792), torch.int64).t()],
         "bf16_weight_14336x4096": lambda: [rnd((14336, 4096), torch.bfloat16).t()],
+        "bf16_weight_28672x8192": lambda: [rnd((28672, 8192), torch.bfloat16).t()],
         "fp32_weight_4096x14336": lambda: [rnd((4096, 14336), torch.float32).t()],
         "bf16_batched_64x1000x300": lambda: [rnd((64, 1000, 300), torch.bfloat16).mT],
         "microbench_transposed_wide_rows": lambda: microbench_views("wide"),

@@ -436,35 +436,52 @@ __device__ __noinline__ void transpose_tile_a(const Seg& g, uint32_t local, uint
   cp_async_wait<0>();
 }
 
-// Matrix form of the wide TRANSPOSE tile: 16-bit elements, pack direction, tensor rows that all start
-// on 16-byte boundaries (segments planned with g.reserved == 4, bulk kernels only). Stages of 128
-// tensor rows by 64 elements (128 bytes) arrive by cp.async, two deep, granules XOR-swizzled so that
-// the warp-level matrix loads below are conflict-free. One ldmatrix.x4.trans per warp turns a block of
-// 32 rows by 8 elements into registers that hold, per thread, 8 CONSECUTIVE elements of one image
-// row (the four 8x8 matrices are given interleaved row lists for exactly that), i.e. one aligned
-// 16-byte piece of the image row, which goes to an image-order staging area with a single 16-byte
-// shared-memory store. The staging rows are then written out as aligned 16-byte image vectors,
-// shifted by the image's byte misalignment; vectors that straddle two stages take their leading
-// bytes from a per-row carry, so only the two ends of a tile's image rows are written bytewise.
-constexpr int kTransMCols = 64;     // elements along C per tile (128 bytes of each tensor row)
+// Matrix form of the wide TRANSPOSE tile: 16- and 32-bit elements, pack direction, tensor rows that
+// all start on 16-byte boundaries (segments planned with g.reserved == 4, bulk kernels only). Stages
+// of 128 tensor rows by 128 bytes arrive by cp.async, two deep, granules XOR-swizzled so that the
+// warp-level matrix loads below are conflict-free. One ldmatrix.x4.trans per warp turns a block of
+// 32 rows by one granule into registers that hold, per thread, CONSECUTIVE elements of one image
+// row: the four 8x8 matrices of 16-bit values are given interleaved row lists for exactly that
+// (32-bit elements arrive as their two halves in neighbouring threads and are put together with one
+// shuffle and one byte permute per register). Each thread then owns one aligned 16-byte piece of an
+// image row, which goes to an image-order staging area with a single conflict-free 16-byte
+// shared-memory store. The staging rows are written out as aligned 16-byte image vectors, shifted by
+// the image's byte misalignment; vectors that straddle two stages take their leading bytes from a
+// per-row carry, so only the two ends of a tile's image rows are written bytewise.
+template <int E>
+struct TransM {
+  static constexpr int kCols = 128 / E;            // elements along C per tile: 64 or 32 (128 bytes of each tensor row)
+  static constexpr int kSegBytes = 128 * E;        // bytes of one image row per full stage: 256 or 512
+  static constexpr int kPitch = kSegBytes + 64;    // image-order staging row; pitch = 4 mod 8 granules
+  static constexpr int kPositions = kSegBytes / 16;  // aligned image vectors per row and stage
+  static constexpr int kCarryBytes = kCols * 16;   // per parity
+};
 constexpr int kTransML = 128;       // tensor rows per stage
-constexpr int kTransMSub = 8;       // stages per tile
+#ifndef MLF_TRANSM_SUB
+#define MLF_TRANSM_SUB 8
+#endif
+constexpr int kTransMSub = MLF_TRANSM_SUB;  // stages per tile
 constexpr int kTransMStageBytes = kTransML * 128;      // 16 KiB, tensor order
-constexpr int kTransMPitch = 320;                       // image-order staging row: 256 data bytes, pitch = 4 mod 8 granules
 constexpr int kTransMStagingOff = 2 * kTransMStageBytes;
-constexpr int kTransMCarryBytes = kTransMCols * 16;    // per parity
+inline uint32_t trans_m_cols(uint32_t esize) { return 128u / esize; }
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(mlf::smem_addr(smem_row)));
 }
-// position of granule g of tensor row l inside its 128-byte stage row
-__device__ __forceinline__ uint32_t matrix_swizzle(uint32_t l, uint32_t g) { return (g ^ ((((l >> 3) & 3u) << 1) | (l & 1u))) << 4; }
+// Position of granule g of tensor row l inside its 128-byte stage row. The key takes the bits of l
+// in which the eight rows of one 8x8 matrix differ (see the row lists in transpose_tile_m).
+template <int E>
+__device__ __forceinline__ uint32_t matrix_swizzle(uint32_t l, uint32_t g) {
+  const uint32_t key = (((l >> 3) & 3u) << 1) | (E == 2 ? (l & 1u) : ((l >> 2) & 1u));
+  return (g ^ key) << 4;
+}
 
 // `ring`: two tensor-order stages, then the image-order staging area; `aux`: two parities of carries.
+template <int E>
 __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint8_t* image, uint8_t* ring, uint8_t* aux) {
-  constexpr int E = 2;
+  using M = TransM<E>;
   const int L = (int)g.ndim - 1;
   const int C = (int)g.c;
   const uint32_t tiles_per_batch = (uint32_t)g.a;
@@ -480,10 +497,10 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
   }
   const int64_t nC = g.shape[C], nL = g.shape[L];
   const int64_t tsL = g.tstride[L], isC = g.istride[C];
-  const int64_t c0 = (int64_t)(in_batch / g.b) * kTransMCols;
+  const int64_t c0 = (int64_t)(in_batch / g.b) * M::kCols;
   const int64_t lfirst = (int64_t)(in_batch % g.b) * (kTransML * kTransMSub);
   const int nsub = (int)min((int64_t)kTransMSub, (nL - lfirst + kTransML - 1) / kTransML);
-  const int nc = (int)min((int64_t)kTransMCols, nC - c0);
+  const int nc = (int)min((int64_t)M::kCols, nC - c0);
   const uint32_t row_bytes = (uint32_t)nc * E;
   const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;  // 16-byte aligned
   uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;
@@ -499,7 +516,7 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
     for (int k = 0; k < 4; ++k) {
       const unsigned l = lr + 32u * k;
       if ((int)l < nl && 16u * gq < row_bytes)
-        cp_async16(stage + l * 128u + matrix_swizzle(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
+        cp_async16(stage + l * 128u + matrix_swizzle<E>(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
     }
     cp_async_commit();
   };
@@ -513,57 +530,74 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
     const int seg_len = nl * E;
     const bool first = s == 0, last = s == nsub - 1;
     const uint8_t* stage = ring + (s & 1) * kTransMStageBytes;
-    // ---- transpose: blocks of 32 tensor rows by 8 elements, four per warp
+    // ---- transpose: blocks of 32 tensor rows by one granule, four per warp
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
       const unsigned blk = warp + 8u * b, lb = blk >> 3, cb = blk & 7u;
-      // lane = 8 i + k supplies row k of matrix i: tensor row 32 lb + 8 (k / 2) + 2 i + (k % 2)
+      // lane = 8 i + k supplies row k of matrix i. A thread receives rows 2 t and 2 t + 1 (t = lane % 4)
+      // of every matrix, so the row lists are laid out for its four registers to be consecutive
+      // elements of one image row:
+      //   16-bit: row(i, k) = 32 lb + 8 (k / 2) + 2 i + k % 2        -> registers hold l = 8 t + 0 .. 7
+      //   32-bit: row(i, k) = 32 lb + 8 (k / 2) + i + 4 (k % 2)      -> after the exchange: l = 8 t + 4 p + 0 .. 3
       const unsigned i = lane >> 3, k = lane & 7u;
-      const unsigned l = 32u * lb + 8u * (k >> 1) + 2u * i + (k & 1u);
+      const unsigned l = 32u * lb + 8u * (k >> 1) + (E == 2 ? 2u * i + (k & 1u) : i + 4u * (k & 1u));
       uint32_t r[4];
-      ldmatrix_x4_trans(r, stage + l * 128u + matrix_swizzle(l, cb));
-      // this thread now holds image row 8 cb + lane / 4, elements 32 lb + 8 (lane % 4) .. + 7
-      const unsigned c = 8u * cb + (lane >> 2), l0 = 32u * lb + 8u * (lane & 3u);
-      *reinterpret_cast<uint4*>(staging + c * kTransMPitch + l0 * E) = make_uint4(r[0], r[1], r[2], r[3]);
+      ldmatrix_x4_trans(r, stage + l * 128u + matrix_swizzle<E>(l, cb));
+      const unsigned t = lane & 3u;
+      if (E == 2) {
+        // image row 8 cb + lane / 4, elements 32 lb + 8 t .. + 7
+        const unsigned c = 8u * cb + (lane >> 2), l0 = 32u * lb + 8u * t;
+        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(r[0], r[1], r[2], r[3]);
+      } else {
+        // the two halves of a 32-bit element sit in this thread and in lane ^ 4: the thread with the
+        // low halves (p = 0) assembles the element of row 2 t, its neighbour that of row 2 t + 1
+        const unsigned p = (lane >> 2) & 1u;
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t other = __shfl_xor_sync(0xffffffffu, r[q], 4);
+          o[q] = p ? __byte_perm(other, r[q], 0x7632) : __byte_perm(r[q], other, 0x5410);
+        }
+        const unsigned c = 4u * cb + (lane >> 3), l0 = 32u * lb + 8u * t + 4u * p;
+        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
     }
     __syncthreads();  // staging holds the stage in image order; the tensor-order buffer is free again
     if (s + 2 < nsub) issue(s + 2); else cp_async_commit();
-    // ---- write out: aligned 16-byte image vectors, 16 positions per image row
-    const uint8_t* carry_in = aux + ((s + 1) & 1) * kTransMCarryBytes;  // last 16 bytes of stage s - 1 per image row
-    uint8_t* carry_out = aux + (s & 1) * kTransMCarryBytes;
-    uint8_t* iseg = ibase + (int64_t)s * (kTransML * E);
-    // 16 lanes per image row take the 16 vector positions (a warp-wide store covers two rows of 256
-    // contiguous bytes)
-    auto emit = [&](int c, int vq) {
+    // ---- write out: aligned 16-byte image vectors, kPositions per image row. With a misaligned row
+    // (h != 0) the first position straddles in from the previous stage and the row's last 16 - h
+    // bytes wait in the carry, so the count is the same.
+    const uint8_t* carry_in = aux + ((s + 1) & 1) * M::kCarryBytes;  // last 16 bytes of stage s - 1 per image row
+    uint8_t* carry_out = aux + (s & 1) * M::kCarryBytes;
+    uint8_t* iseg = ibase + (int64_t)s * M::kSegBytes;
+    // 16 lanes per image row (a warp-wide store covers two rows of 256 contiguous bytes)
+    for (int c = (int)(tid >> 4); c < nc; c += (int)(kThreads >> 4)) {
       uint8_t* row = iseg + (int64_t)c * isC;
-      const uint8_t* data = staging + c * kTransMPitch;
+      const uint8_t* data = staging + c * M::kPitch;
       const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);  // the same in every stage
-      if (h == 0) {
-        if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
-      } else {
-        const int q = h - 16 + 16 * vq;  // stage-relative first byte of the vector
-        if (q + 16 <= seg_len && !(first && vq == 0)) {
-          const uint4 lo = vq == 0 ? *reinterpret_cast<const uint4*>(carry_in + c * 16) : *reinterpret_cast<const uint4*>(data + 16 * (vq - 1));
-          const uint4 hi = *reinterpret_cast<const uint4*>(data + 16 * vq);
-          mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
+#pragma unroll
+      for (int j = 0; j < M::kPositions / 16; ++j) {
+        const int vq = (int)(tid & 15u) + 16 * j;
+        if (h == 0) {
+          if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
+        } else {
+          const int q = h - 16 + 16 * vq;  // stage-relative first byte of the vector
+          if (q + 16 <= seg_len && !(first && vq == 0)) {
+            const uint4 lo = vq == 0 ? *reinterpret_cast<const uint4*>(carry_in + c * 16) : *reinterpret_cast<const uint4*>(data + 16 * (vq - 1));
+            const uint4 hi = *reinterpret_cast<const uint4*>(data + 16 * vq);
+            mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
+          }
         }
       }
-    };
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int c = (int)(tid >> 4) + 16 * k;
-      if (c < nc) emit(c, (int)(tid & 15u));
     }
-    // (a stage holds 16 vector positions per row whatever the misalignment: with h != 0 the first one
-    // straddles in from the previous stage and the row's last 16 - h bytes wait in the carry)
     if (!last && (int)tid < nc)
-      *reinterpret_cast<uint4*>(carry_out + tid * 16) = *reinterpret_cast<const uint4*>(staging + tid * kTransMPitch + 240);
+      *reinterpret_cast<uint4*>(carry_out + tid * 16) = *reinterpret_cast<const uint4*>(staging + tid * M::kPitch + M::kSegBytes - 16);
     if (first) {
       for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
         const int c = idx / 15, kb = idx % 15;
         uint8_t* row = iseg + (int64_t)c * isC;
         const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
-        if (kb < h && kb < seg_len) row[kb] = staging[c * kTransMPitch + kb];
+        if (kb < h && kb < seg_len) row[kb] = staging[c * M::kPitch + kb];
       }
     }
     if (last) {
@@ -576,7 +610,7 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
         const int b = done + kb;
         if (b >= seg_len || (first && b < h)) continue;
         if (b >= 0)
-          row[b] = staging[c * kTransMPitch + b];
+          row[b] = staging[c * M::kPitch + b];
         else if (!first)
           row[b] = carry_in[c * 16 + 16 + b];
       }
@@ -936,7 +970,10 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
   if (g.kind == kRows) {
     rows_tile<DIR>(g, local, image);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 4) {
-    transpose_tile_m(g, local, image, vsmem, tsmem);
+    if (g.esize == 2)
+      transpose_tile_m<2>(g, local, image, vsmem, tsmem);
+    else
+      transpose_tile_m<4>(g, local, image, vsmem, tsmem);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 3) {
     // wide rows in asynchronous form: two 32 KiB stages in `vsmem` (the idle ring), carries in `tsmem`
     switch (g.esize) {
@@ -1285,8 +1322,10 @@ constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
 static_assert(kTransVSmemBytes <= (int)mlf::kSlotBytes, "the vector-form transpose stages through one ring slot");
 static_assert(2 * 128 * 256 <= (int)kBulkDynSmem, "the asynchronous transpose uses the ring as two 32 KiB stages");
 static_assert(2 * kTransACarryBytes + 2 * kTransAL <= kTransSmemBytes, "carries and shift tables fit the static staging area");
-static_assert(kTransMStagingOff + kTransMCols * kTransMPitch <= (int)kBulkDynSmem, "matrix form: two stages and the staging area fit the ring");
-static_assert(2 * kTransMCarryBytes <= kTransSmemBytes, "matrix form: carries fit the static staging area");
+static_assert(kTransMStagingOff + TransM<2>::kCols * TransM<2>::kPitch <= (int)kBulkDynSmem &&
+                  kTransMStagingOff + TransM<4>::kCols * TransM<4>::kPitch <= (int)kBulkDynSmem,
+              "matrix form: two stages and the staging area fit the ring");
+static_assert(2 * TransM<2>::kCarryBytes <= kTransSmemBytes, "matrix form: carries fit the static staging area");
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
                                                                  const uint8_t* __restrict__ src, uint64_t nbytes) {
@@ -1387,9 +1426,9 @@ uint32_t g_noalloc_host_tiles[kNoAllocMaxSegs + 1];
 
 // Turns one descriptor into a segment: validation, canonical form, kind and tile count.
 // On success *ntile_out is 0 if the descriptor moves nothing (the segment is then unused).
-// The matrix form moves 16-bit elements whose tensor rows all start on 16-byte boundaries.
+// The matrix form moves 16- and 32-bit elements whose tensor rows all start on 16-byte boundaries.
 bool matrix_form_eligible(uint32_t esize, uint64_t tensor_ptr, const Canon& c, int cdim) {
-  if (esize != 2 || (tensor_ptr & 15u)) return false;
+  if ((esize != 2 && esize != 4) || (tensor_ptr & 15u)) return false;
   for (int k = 0; k < c.ndim; ++k)
     if (k != cdim && (c.ts[k] & 15)) return false;
   return true;
@@ -1542,7 +1581,8 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
           tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
         } else if (wide_form == 4 && matrix_form_eligible(esize, d.tensor_ptr, c, cdim)) {
-          tc = ((uint64_t)c.shape[cdim] + kTransMCols - 1) / kTransMCols;
+          const uint64_t cols = trans_m_cols(esize);
+          tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
           g.reserved = 4;
         } else if (wide_form == 3) {

@@ -902,22 +902,28 @@ def test_wide_transposes_in_vector_form_at_every_edge(dtype):
     _pack_and_unpack_against_oracle(views)
 
 
-def test_sixteen_bit_transposes_in_matrix_form_at_every_edge():
-    """16-bit transposed views whose tensor rows all start on 16-byte boundaries go through warp-level
-    matrix loads (32 x 8 blocks) and a per-row carry between stages of 128 rows. Extents straddle the
-    tile (64 elements along the tensor's contiguous dimension, 128 and 1024 along the image rows),
-    images start on every byte residue, and batched and column-offset views are in the mix."""
+@pytest.mark.parametrize("dtype", [torch.int16, torch.int32], ids=["16bit", "32bit"])
+def test_transposes_in_matrix_form_at_every_edge(dtype):
+    """16- and 32-bit transposed views whose tensor rows all start on 16-byte boundaries go through
+    warp-level matrix loads (blocks of 32 rows by one granule) and a per-row carry between stages of
+    128 rows. Extents straddle the tile (128 bytes along the tensor's contiguous dimension, 128 and
+    1024 elements along the image rows), images start on every byte residue, and batched and
+    column-offset views are in the mix."""
     g = torch.Generator().manual_seed(31)
+    esize = torch.empty((), dtype=dtype).element_size()
+    cols, gran = 128 // esize, 16 // esize  # elements per tile row / per 16-byte granule
 
-    def base(rows, cols):
-        return torch.randint(-30000, 30000, (rows, cols), generator=g, dtype=torch.int64).to(torch.int16).cuda()
+    def base(rows, pitch):
+        return torch.randint(-30000, 30000, (rows, pitch), generator=g, dtype=torch.int64).to(dtype).cuda()
 
     views = []
     for n_c, n_l, pitch, off in [
-        (64, 1024, 64, 0), (63, 1023, 64, 0), (65, 1025, 72, 0), (1, 128, 8, 0), (7, 129, 16, 8), (128, 2049, 136, 8),
-        (200, 300, 208, 0), (64, 127, 64, 0), (300, 5000, 304, 0), (64, 135, 64, 0), (33, 1030, 40, 0),
+        (cols, 1024, cols, 0), (cols - 1, 1023, cols, 0), (cols + 1, 1025, cols + gran, 0), (1, 128, gran, 0),
+        (7, 129, 2 * gran, gran), (2 * cols, 2049, 2 * cols + gran, gran), (200, 300, 208, 0), (cols, 127, cols, 0),
+        (300, 5000, 304, 0), (cols, 135, cols, 0), (33, 1030, 40, 0),
     ]:
         views.append(base(n_l, pitch)[:, off : off + n_c].t())
-    views.append(torch.randint(-9, 9, (3, 700, 80), generator=g, dtype=torch.int64).to(torch.bfloat16).cuda().transpose(1, 2))
+    float_dtype = torch.bfloat16 if esize == 2 else torch.float32
+    views.append(torch.randint(-9, 9, (3, 700, 80), generator=g, dtype=torch.int64).to(float_dtype).cuda().transpose(1, 2))
     for first_offset in (0, 1, 2, 9, 15):
         _pack_and_unpack_against_oracle(views, first_offset=first_offset)
