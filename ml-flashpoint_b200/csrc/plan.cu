@@ -620,6 +620,163 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
   __syncthreads();  // the staging area and the carries are free for the next tile
 }
 
+// Matrix form for tensor rows that start anywhere (segments planned with g.reserved == 5): the same
+// transposition and write-out as transpose_tile_m, but the tensor rows are read the way the vector
+// form reads them, as aligned granules through registers (one stage ahead), shifted into place with
+// shf.r and then stored, 16 bytes at a time, into the swizzled tensor-order stage. A tile row
+// delivers the 112 bytes (7 granules) that are complete behind any shift.
+template <int E>
+struct TransMS {
+  static constexpr int kCols = 112 / E;            // 56 or 28 image rows per tile
+  static constexpr int kGranules = 7;
+  static constexpr int kSegBytes = 128 * E;
+  static constexpr int kPitch = kSegBytes + 64;
+  static constexpr int kPositions = kSegBytes / 16;
+  static constexpr int kCarryBytes = kCols * 16;
+};
+inline uint32_t trans_ms_cols(uint32_t esize) { return 112u / esize; }
+
+// `ring`: one tensor-order stage (16 KiB), then (at kTransMStagingOff) the image-order staging area.
+template <int E>
+__device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uint8_t* image, uint8_t* ring, uint8_t* aux) {
+  using M = TransMS<E>;
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  int64_t toff = 0, ioff = 0;
+  for (int d = L - 1; d >= 0; --d) {
+    if (d == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[d]);
+    batch /= (uint64_t)g.shape[d];
+    toff += idx * g.tstride[d];
+    ioff += idx * g.istride[d];
+  }
+  const int64_t nC = g.shape[C], nL = g.shape[L];
+  const int64_t tsL = g.tstride[L], isC = g.istride[C];
+  const int64_t c0 = (int64_t)(in_batch / g.b) * M::kCols;
+  const int64_t lfirst = (int64_t)(in_batch % g.b) * (kTransML * kTransMSub);
+  const int nsub = (int)min((int64_t)kTransMSub, (nL - lfirst + kTransML - 1) / kTransML);
+  const int nc = (int)min((int64_t)M::kCols, nC - c0);
+  const uint32_t row_bytes = (uint32_t)nc * E;
+  const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;
+  uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;
+  const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+  uint8_t* stage = ring;
+  uint8_t* staging = ring + kTransMStagingOff;
+  auto elems_of = [&](int s) { return (int)min((int64_t)kTransML, nL - (lfirst + (int64_t)s * kTransML)); };
+  const unsigned gq = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
+
+  uint4 v[4];
+  auto load = [&](int s) {
+    const int nl = elems_of(s);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int l = (int)lr + 32 * k;
+      const uint8_t* row = trow0 + ((int64_t)s * kTransML + l) * tsL;
+      const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+      const bool need = l < nl && 16u * gq < m + row_bytes;  // only granules that hold at least one byte of the row
+      v[k] = need ? mlf::ld_vec(reinterpret_cast<const uint4*>(row - m) + gq) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+
+  load(0);
+  for (int s = 0; s < nsub; ++s) {
+    const int nl = elems_of(s);
+    const int seg_len = nl * E;
+    const bool first = s == 0, last = s == nsub - 1;
+    // ---- shift the rows into place and put them into the swizzled stage
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const unsigned l = lr + 32u * k;
+      const uint8_t* row = trow0 + ((int64_t)s * kTransML + l) * tsL;
+      const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+      const uint4 next = mlf::shfl_down1(v[k]);  // granule gq + 1 of the same row (lanes 8 r .. 8 r + 7 share a row)
+      const uint4 out = m ? mlf::realign(v[k], next, m) : v[k];  // row bytes [16 gq, 16 gq + 16)
+      if (gq < (unsigned)M::kGranules) *reinterpret_cast<uint4*>(stage + l * 128u + matrix_swizzle<E>(l, gq)) = out;
+    }
+    __syncthreads();  // the stage is complete; every thread is done draining the staging area of stage s - 1
+    if (s + 1 < nsub) load(s + 1);  // in flight while this stage is transposed and written out
+    // ---- transpose: blocks of 32 tensor rows by one granule (7 granule columns)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const unsigned blk = warp + 8u * b;
+      if (blk >= 4u * M::kGranules) break;  // warp-uniform
+      const unsigned lb = blk / M::kGranules, cb = blk % M::kGranules;
+      const unsigned i = lane >> 3, k = lane & 7u;
+      const unsigned l = 32u * lb + 8u * (k >> 1) + (E == 2 ? 2u * i + (k & 1u) : i + 4u * (k & 1u));
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, stage + l * 128u + matrix_swizzle<E>(l, cb));
+      const unsigned t = lane & 3u;
+      if (E == 2) {
+        const unsigned c = 8u * cb + (lane >> 2), l0 = 32u * lb + 8u * t;
+        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(r[0], r[1], r[2], r[3]);
+      } else {
+        const unsigned p = (lane >> 2) & 1u;
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t other = __shfl_xor_sync(0xffffffffu, r[q], 4);
+          o[q] = p ? __byte_perm(other, r[q], 0x7632) : __byte_perm(r[q], other, 0x5410);
+        }
+        const unsigned c = 4u * cb + (lane >> 3), l0 = 32u * lb + 8u * t + 4u * p;
+        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    __syncthreads();  // staging holds the stage in image order; the tensor-order stage is free again
+    // ---- write out (as in transpose_tile_m)
+    const uint8_t* carry_in = aux + ((s + 1) & 1) * M::kCarryBytes;
+    uint8_t* carry_out = aux + (s & 1) * M::kCarryBytes;
+    uint8_t* iseg = ibase + (int64_t)s * M::kSegBytes;
+    for (int c = (int)(tid >> 4); c < nc; c += (int)(kThreads >> 4)) {
+      uint8_t* row = iseg + (int64_t)c * isC;
+      const uint8_t* data = staging + c * M::kPitch;
+      const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+#pragma unroll
+      for (int j = 0; j < M::kPositions / 16; ++j) {
+        const int vq = (int)(tid & 15u) + 16 * j;
+        if (h == 0) {
+          if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
+        } else {
+          const int q = h - 16 + 16 * vq;
+          if (q + 16 <= seg_len && !(first && vq == 0)) {
+            const uint4 lo = vq == 0 ? *reinterpret_cast<const uint4*>(carry_in + c * 16) : *reinterpret_cast<const uint4*>(data + 16 * (vq - 1));
+            const uint4 hi = *reinterpret_cast<const uint4*>(data + 16 * vq);
+            mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
+          }
+        }
+      }
+    }
+    if (!last && (int)tid < nc)
+      *reinterpret_cast<uint4*>(carry_out + tid * 16) = *reinterpret_cast<const uint4*>(staging + tid * M::kPitch + M::kSegBytes - 16);
+    if (first) {
+      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
+        const int c = idx / 15, kb = idx % 15;
+        uint8_t* row = iseg + (int64_t)c * isC;
+        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+        if (kb < h && kb < seg_len) row[kb] = staging[c * M::kPitch + kb];
+      }
+    }
+    if (last) {
+      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
+        const int c = idx / 15, kb = idx % 15;
+        uint8_t* row = iseg + (int64_t)c * isC;
+        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
+        int done = seg_len - (int)(((uintptr_t)row + (uint32_t)seg_len) & 15u);
+        if (first && done < h) done = min(h, seg_len);
+        const int b = done + kb;
+        if (b >= seg_len || (first && b < h)) continue;
+        if (b >= 0)
+          row[b] = staging[c * M::kPitch + b];
+        else if (!first)
+          row[b] = carry_in[c * 16 + 16 + b];
+      }
+    }
+  }
+  __syncthreads();  // the staging area and the carries are free for the next tile
+}
+
 // Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
 template <typename T, int DIR>
 __device__ MLF_TRANSPOSE_ATTR void transpose_tile(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
@@ -974,6 +1131,11 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
       transpose_tile_m<2>(g, local, image, vsmem, tsmem);
     else
       transpose_tile_m<4>(g, local, image, vsmem, tsmem);
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 5) {
+    if (g.esize == 2)
+      transpose_tile_ms<2>(g, local, image, vsmem, tsmem);
+    else
+      transpose_tile_ms<4>(g, local, image, vsmem, tsmem);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 3) {
     // wide rows in asynchronous form: two 32 KiB stages in `vsmem` (the idle ring), carries in `tsmem`
     switch (g.esize) {
@@ -1435,8 +1597,9 @@ bool matrix_form_eligible(uint32_t esize, uint64_t tensor_ptr, const Canon& c, i
 }
 
 // `wide_form`: tile geometry of wide TRANSPOSE boxes: 0 element-wise, 2 vector form, 3 asynchronous
-// form, 4 matrix form where eligible and vector form elsewhere (all but 0 only exist in the bulk
-// kernels, for the pack direction).
+// form, 4 matrix form for 16- and 32-bit elements (cp.async-fed where every tensor row starts on a
+// 16-byte boundary, register-fed with a shift elsewhere) and vector form for the other element
+// sizes (all but 0 only exist in the bulk kernels, for the pack direction).
 int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int wide_form, Seg* seg_out, uint64_t* ntile_out,
                      uint64_t* payload_out, uint64_t* extent_out) {
   *ntile_out = 0;
@@ -1585,6 +1748,12 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
           g.reserved = 4;
+        } else if (wide_form == 4 && (esize == 2 || esize == 4)) {
+          // 16- and 32-bit rows that start anywhere: matrix form behind a register-side shift
+          const uint64_t cols = trans_ms_cols(esize);
+          tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
+          tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
+          g.reserved = 5;
         } else if (wide_form == 3) {
           const uint64_t cols = trans_a_cols(esize);
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
