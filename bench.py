@@ -705,7 +705,8 @@ def run_host_link_probe(args) -> None:
         os.remove(path)
     result["restore_feed"] = {
         "what": "4 GiB object file on tmpfs opened read-only into HBM (wall clock of the blocking call), page cache warm",
-        "bounce_chunk_kib": int(os.environ.get("MLF_BOUNCE_CHUNK_KIB", "0") or 0) or 4096,
+        "bounce_chunk_kib": int(os.environ.get("MLF_BOUNCE_CHUNK_KIB", "0") or 0)
+        or max(1024, 4096 // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))),
         **feed_result,
     }
     if rank == 0:
@@ -1198,11 +1199,11 @@ def run_native_arm(args, rank: int, world_size: int, device, workdir: str) -> No
     if rank != 0:
         return
     achieved = 2 * payload / 1e9 / kernel_s
-    d2h_gbs = (
-        layout.total_bytes / 1e9 / ((statistics.mean(device_ms) - statistics.mean(kernel_ms)) / 1e3)
-        if statistics.mean(device_ms) > statistics.mean(kernel_ms)
-        else achieved / 2
-    )
+    if (args.mode or "staged") == "direct" or statistics.mean(device_ms) <= statistics.mean(kernel_ms):
+        # the kernel's own stores cross the host link: kernel time is transfer time
+        d2h_gbs = layout.total_bytes / 1e9 / (statistics.mean(device_ms) / 1e3)
+    else:
+        d2h_gbs = layout.total_bytes / 1e9 / ((statistics.mean(device_ms) - statistics.mean(kernel_ms)) / 1e3)
     if restore is not None:
         per_gpu = restore["e2e_value"] / world_size
         restore["roofline"] = {
