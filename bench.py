@@ -557,6 +557,14 @@ def run_transpose_probe(args) -> None:
         "bf16_weight_28672x8192": lambda: [rnd((28672, 8192), torch.bfloat16).t()],
         "fp32_weight_4096x14336": lambda: [rnd((4096, 14336), torch.float32).t()],
         "bf16_batched_64x1000x300": lambda: [rnd((64, 1000, 300), torch.bfloat16).mT],
+        # narrow rows: image rows shorter than 256 bytes lying back to back
+        "narrow_bf16_rows_of_2": lambda: [rnd((2, 32 << 20), torch.bfloat16).t()],
+        "narrow_bf16_rows_of_3": lambda: [rnd((3, 21 << 20), torch.bfloat16).t()],
+        "narrow_bf16_rows_of_8": lambda: [rnd((8, 8 << 20), torch.bfloat16).t()],
+        "narrow_bf16_rows_of_82": lambda: [rnd((82, 800000), torch.bfloat16).t()],
+        "narrow_fp32_rows_of_3": lambda: [rnd((3, 10 << 20), torch.float32).t()],
+        "narrow_fp32_rows_of_19": lambda: [rnd((19, 1600000), torch.float32).t()],
+        "narrow_int64_rows_of_12": lambda: [rnd((12, 1300000), torch.int64).t()],
         "microbench_transposed_wide_rows": lambda: microbench_views("wide"),
         "microbench_transposed_all": lambda: microbench_views("transposed"),
         "microbench_all_1024_tensors": lambda: microbench_views("all"),

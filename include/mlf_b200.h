@@ -136,7 +136,9 @@ uint64_t mlf_plan_num_tiles(const mlf_plan* p);
 /* Launches the plan's single kernel on `stream` (a cudaStream_t; NULL = default stream).
  * `image_base` is a device-visible address (HBM, or a registered host mapping) and
  * `image_capacity` the bytes valid behind it: the launch is refused with MLF_ERR_BOUNDS if the
- * plan's extent exceeds it. `max_ctas` limits the grid (0 = one wave sized from the SM count). */
+ * plan's extent exceeds it. `max_ctas` limits the grid (0 = one wave sized from the SM count).
+ * Launches of ONE plan must not overlap on the GPU (they share the plan's status word and tile
+ * counter): order them on one stream or wait for the previous one. */
 int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, void* stream, int32_t max_ctas);
 /* After the stream has been synchronised: 0, or the MLF_ERR_* a kernel recorded. Clears it. */
 int32_t mlf_plan_status(mlf_plan* p);

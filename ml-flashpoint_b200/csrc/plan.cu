@@ -1451,20 +1451,27 @@ __global__ void __launch_bounds__(kThreads, 3) mlf_plan_kernel_bulk(const Seg* _
   if (!stream_linear_tiles<DIR>(segs, tile_begin, nseg, nlinear, image, status, ring, &shared)) return;
   const unsigned tid = threadIdx.x;
   uint32_t cached = 0xffffffffu;
-  // this CTA's staged tiles: the same stride as before, continued behind the linear tiles
-  const uint32_t first = nlinear + (blockIdx.x + gridDim.x - nlinear % gridDim.x) % gridDim.x;
-  for (uint32_t tile = first; tile < ntiles; tile += gridDim.x) {
+  // Staged tiles differ in cost by an order of magnitude (a matrix-form tile moves 128 KiB, a tile
+  // of single elements 8 KiB), and the CTAs leave the streaming phase at different times: they are
+  // handed out one by one from a counter behind the status word (zeroed by the launch), heaviest
+  // segments first (the planner's order), instead of in fixed strides.
+  __shared__ uint32_t claimed;
+  for (;;) {
+    if (tid == 0) claimed = nlinear + atomicAdd(reinterpret_cast<unsigned int*>(status) + 1, 1u);
+    __syncthreads();
+    const uint32_t tile = claimed;
+    if (tile >= ntiles) break;
     const uint32_t sg = find_segment(tile_begin, nseg, tile);
     const uint32_t local = tile - tile_begin[sg];
+    __syncthreads();  // everyone has read `claimed` (and is done with the previous tile's segment copy)
     if (sg != cached) {
-      __syncthreads();
       const uint32_t* src = reinterpret_cast<const uint32_t*>(segs + sg);
       uint32_t* dst = reinterpret_cast<uint32_t*>(&g);
       for (uint32_t w = tid; w < sizeof(Seg) / 4; w += blockDim.x) dst[w] = src[w];
       __syncthreads();
       cached = sg;
     }
-    // the ring of the streaming phase is idle by now: its first slot stages the vector-form transposes
+    // the ring of the streaming phase is idle by now: it stages the vector- and matrix-form transposes
     staged_tile<DIR>(g, local, image, tsmem, ring);
   }
 }
@@ -1816,7 +1823,7 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   // (pack only: scattering into tensor granules measured slower than the element-wise form)
   const int wide_form = direction == MLF_PACK && use_bulk_kernel() ? wide_transpose_form() : 0;
   std::vector<Seg> linear_segs, staged_segs;
-  std::vector<uint64_t> linear_tiles, staged_tiles;
+  std::vector<uint64_t> linear_tiles, staged_tiles, staged_payload;
   uint64_t tiles = 0, extent = 0, payload = 0;
 
   for (uint64_t i = 0; i < n; ++i) {
@@ -1832,6 +1839,24 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
     const bool linear = g.kind == kFlat || g.kind == kRows;  // everything the streaming phase moves
     (linear ? linear_segs : staged_segs).push_back(g);
     (linear ? linear_tiles : staged_tiles).push_back(ntile);
+    if (!linear) staged_payload.push_back(seg_payload);
+  }
+  // staged segments in order of bytes per tile, heaviest first: the kernel hands staged tiles out
+  // dynamically, and starting with the big ones leaves the small ones to even out the finish
+  {
+    std::vector<size_t> order(staged_segs.size());
+    for (size_t k = 0; k < order.size(); ++k) order[k] = k;
+    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
+      return staged_payload[a] * staged_tiles[b] > staged_payload[b] * staged_tiles[a];  // payload / tiles, without dividing
+    });
+    std::vector<Seg> sorted_segs;
+    std::vector<uint64_t> sorted_tiles;
+    for (size_t k : order) {
+      sorted_segs.push_back(staged_segs[k]);
+      sorted_tiles.push_back(staged_tiles[k]);
+    }
+    staged_segs.swap(sorted_segs);
+    staged_tiles.swap(sorted_tiles);
   }
   std::vector<Seg> segs(linear_segs);
   segs.insert(segs.end(), staged_segs.begin(), staged_segs.end());
@@ -1860,11 +1885,11 @@ int32_t mlf_plan_create(const mlf_copy_desc* descs, uint64_t n, int32_t directio
   if (e == cudaSuccess && p->nseg > 0) {
     e = cudaMalloc(&p->d_segs, segs.size() * sizeof(Seg));
     if (e == cudaSuccess) e = cudaMalloc(&p->d_tile_begin, tile_begin.size() * sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMalloc(&p->d_status, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&p->d_status, 2 * sizeof(int32_t));  // status word, staged-tile counter
     if (e == cudaSuccess) e = cudaMemcpy(p->d_segs, segs.data(), segs.size() * sizeof(Seg), cudaMemcpyHostToDevice);
     if (e == cudaSuccess)
       e = cudaMemcpy(p->d_tile_begin, tile_begin.data(), tile_begin.size() * sizeof(uint32_t), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemset(p->d_status, 0, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemset(p->d_status, 0, 2 * sizeof(int32_t));
   }
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -1923,6 +1948,7 @@ int32_t mlf_plan_launch(mlf_plan* p, void* image_base, uint64_t image_capacity, 
     const BulkKernel kernel = kernels[p->direction == MLF_PACK ? 0 : 1][staged ? 1 : 0];
     const int32_t rc = wave_grid(kernel, max_ctas, p->ntiles, &grid, kBulkDynSmem);
     if (rc != MLF_OK) return rc;
+    if (staged) MLF_CUDA(cudaMemsetAsync(p->d_status + 1, 0, sizeof(int32_t), s));  // the staged-tile counter starts at 0
     kernel<<<grid, kThreads, kBulkDynSmem, s>>>(p->d_segs, p->d_tile_begin, p->nseg, p->nlinear, p->ntiles, image, p->d_status);
   } else {
     int32_t rc = p->direction == MLF_PACK ? wave_grid(mlf_plan_kernel<MLF_PACK>, max_ctas, p->ntiles, &grid)
