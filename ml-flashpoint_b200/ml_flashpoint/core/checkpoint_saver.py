@@ -361,14 +361,15 @@ class DefaultMLFlashpointCheckpointSaver(MLFlashpointCheckpointSaver):
     def _can_replicate_early(self, writer) -> bool:
         """True when replication of the object behind ``writer`` may start before its bytes have
         reached the host mapping: the file must already have its final size (a pool buffer sized by
-        ``ensure_total_size``), because the receiver is told the object's size up front, and a
-        replication manager must be present. The transfer service then either sends the finished HBM
-        image or waits for the drain itself."""
-        return (
-            self._replication_manager is not None
-            and hasattr(writer, "ensure_total_size")
-            and hasattr(self._engine(), "wait_object_on_host")
-        )
+        ``ensure_total_size``), because the receiver is told the object's size up front; a
+        replication manager must be present; and this saver's engine must be the process-wide one,
+        because that is where the transfer service looks the object up: it then either sends the
+        finished HBM image or waits for the drain itself (``wait_object_on_host``). A saver with an
+        engine of its own replicates after the write, as before."""
+        if self._replication_manager is None or not hasattr(writer, "ensure_total_size"):
+            return False
+        engine = self._engine()
+        return hasattr(engine, "wait_object_on_host") and engine is gpu_engine.peek_default_engine()
 
     @log_execution_time(logger=_LOGGER, name="_write_to_buffer_from_queue_worker")
     def _write_to_buffer_from_queue_worker(

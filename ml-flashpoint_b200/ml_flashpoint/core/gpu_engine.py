@@ -1094,6 +1094,11 @@ def default_engine() -> CudaCopyEngine:
         return _default_engine
 
 
+def peek_default_engine() -> Optional[CudaCopyEngine]:
+    """The process-wide engine if one exists already (never creates one)."""
+    return _default_engine
+
+
 def set_default_engine(engine: Optional[CudaCopyEngine]) -> None:
     """Makes ``engine`` the process-wide engine (for callers that configure their own)."""
     global _default_engine

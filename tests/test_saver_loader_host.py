@@ -251,3 +251,43 @@ def test_load_converts_to_the_target_dtype(tmp_path):
 
     loader.read_data(buckets[0].object_id, [req], _P(), {idx: results[0].storage_data})
     assert torch.equal(target, src[1:3].to(torch.bfloat16))
+
+
+def test_replication_follows_the_write_unless_the_process_wide_cuda_engine_moves_the_bytes(tmp_path, golden_dir):
+    """Replication may only start together with the pack kernel when the transfer service can find
+    the save in the process-wide CUDA engine. With any other engine (here the numpy double), pool
+    buffer or not, ``async_replicate`` is called once per object, after the object is complete."""
+    from ml_flashpoint.core.buffer_pool import BufferPoolConfig
+
+    gold = load_golden(golden_dir, "mixed.json")["objects"][0]
+    seen = []
+
+    class _Repl:
+        def async_replicate(self, buffer_io):
+            seen.append(bytes(memoryview(buffer_io.buffer_obj)))
+            buffer_io.close()
+            return []
+
+    case = cases.CASES["mixed"]()
+    for pooled in (False, True):
+        seen.clear()
+        pool = BufferPoolConfig(str(tmp_path / f"pool{pooled}"), 0, 2, 1 << 20) if pooled else None
+        saver, com = make_saver(copy_engine=NumpyCopyEngine(), pool_config=pool, replication_manager=_Repl())
+        try:
+            ckpt = CheckpointContainerId(str(tmp_path / f"run{pooled}" / "step-1_ckpt"))
+            saver.initialize_checkpoint(ckpt)
+            items, resolver = cases.write_items_and_resolver(case)
+            buckets = saver.prepare_write_data(ckpt, items, resolver, "__0_", bucket_count=1)
+            assert saver._can_replicate_early(com.acquire_buffer(CheckpointObjectId(str(tmp_path / f"probe{pooled}.distcp")), 1 << 16)) is False
+            saver.write_data(ckpt, buckets, replicate_after_write=True)
+            assert seen == [golden_object_bytes(golden_dir, gold)]
+            seen.clear()
+            ckpt2 = CheckpointContainerId(str(tmp_path / f"run{pooled}" / "step-2_ckpt"))
+            saver.initialize_checkpoint(ckpt2)
+            buckets = saver.prepare_write_data(ckpt2, items, resolver, "__0_", bucket_count=1)
+            pending = saver.write_data_async(ckpt2, buckets, replicate_after_write=True)
+            assert seen == []  # nothing before result()
+            pending.result()
+            assert seen == [golden_object_bytes(golden_dir, gold)] and pending.replication_futures == []
+        finally:
+            com.teardown_pool()
