@@ -283,6 +283,9 @@ inline uint32_t trans_a_cols(uint32_t esize) { return 240u / esize; }
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(mlf::smem_addr(smem_dst)), "l"(gmem_src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(mlf::smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -479,7 +482,10 @@ __device__ __forceinline__ uint32_t matrix_swizzle(uint32_t l, uint32_t g) {
 }
 
 // `ring`: two tensor-order stages, then the image-order staging area; `aux`: two parities of carries.
-template <int E>
+// WORDS: the tensor rows start on 4-byte instead of 16-byte boundaries; the stages are then fed by
+// 4-byte cp.async copies (a warp covers one row's 128 bytes per instruction), which land every row
+// at the start of its stage row whatever its alignment in global memory.
+template <int E, bool WORDS>
 __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint8_t* image, uint8_t* ring, uint8_t* aux) {
   using M = TransM<E>;
   const int L = (int)g.ndim - 1;
@@ -511,12 +517,22 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
   auto issue = [&](int s) {
     const int nl = elems_of(s);
     uint8_t* stage = ring + (s & 1) * kTransMStageBytes;
-    const unsigned gq = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
+    if (WORDS) {
+      const unsigned w = tid & 31u, lr = tid >> 5;  // word within the row; row within a pass of 8 rows
+#pragma unroll 4
+      for (int k = 0; k < 16; ++k) {
+        const unsigned l = lr + 8u * k;
+        if ((int)l < nl && 4u * w < row_bytes)
+          cp_async4(stage + l * 128u + matrix_swizzle<E>(l, w >> 2) + 4u * (w & 3u), trow0 + ((int64_t)s * kTransML + l) * tsL + 4u * w);
+      }
+    } else {
+      const unsigned gq = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const unsigned l = lr + 32u * k;
-      if ((int)l < nl && 16u * gq < row_bytes)
-        cp_async16(stage + l * 128u + matrix_swizzle<E>(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
+      for (int k = 0; k < 4; ++k) {
+        const unsigned l = lr + 32u * k;
+        if ((int)l < nl && 16u * gq < row_bytes)
+          cp_async16(stage + l * 128u + matrix_swizzle<E>(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
+      }
     }
     cp_async_commit();
   };
@@ -1128,9 +1144,14 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
     rows_tile<DIR>(g, local, image);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 4) {
     if (g.esize == 2)
-      transpose_tile_m<2>(g, local, image, vsmem, tsmem);
+      transpose_tile_m<2, false>(g, local, image, vsmem, tsmem);
     else
-      transpose_tile_m<4>(g, local, image, vsmem, tsmem);
+      transpose_tile_m<4, false>(g, local, image, vsmem, tsmem);
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 6) {
+    if (g.esize == 2)
+      transpose_tile_m<2, true>(g, local, image, vsmem, tsmem);
+    else
+      transpose_tile_m<4, true>(g, local, image, vsmem, tsmem);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 5) {
     if (g.esize == 2)
       transpose_tile_ms<2>(g, local, image, vsmem, tsmem);
@@ -1595,11 +1616,12 @@ uint32_t g_noalloc_host_tiles[kNoAllocMaxSegs + 1];
 
 // Turns one descriptor into a segment: validation, canonical form, kind and tile count.
 // On success *ntile_out is 0 if the descriptor moves nothing (the segment is then unused).
-// The matrix form moves 16- and 32-bit elements whose tensor rows all start on 16-byte boundaries.
-bool matrix_form_eligible(uint32_t esize, uint64_t tensor_ptr, const Canon& c, int cdim) {
-  if ((esize != 2 && esize != 4) || (tensor_ptr & 15u)) return false;
+// The cp.async-fed matrix form moves 16- and 32-bit elements whose tensor rows all start on
+// boundaries of `align` bytes: 16 (granule copies) or 4 (word copies).
+bool matrix_form_eligible(uint32_t esize, uint64_t tensor_ptr, const Canon& c, int cdim, uint32_t align) {
+  if ((esize != 2 && esize != 4) || (tensor_ptr & (align - 1))) return false;
   for (int k = 0; k < c.ndim; ++k)
-    if (k != cdim && (c.ts[k] & 15)) return false;
+    if (k != cdim && (c.ts[k] & (int64_t)(align - 1))) return false;
   return true;
 }
 
@@ -1750,11 +1772,11 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
           const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
           tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
-        } else if (wide_form == 4 && matrix_form_eligible(esize, d.tensor_ptr, c, cdim)) {
+        } else if (wide_form == 4 && matrix_form_eligible(esize, d.tensor_ptr, c, cdim, 4)) {
           const uint64_t cols = trans_m_cols(esize);
+          g.reserved = matrix_form_eligible(esize, d.tensor_ptr, c, cdim, 16) ? 4 : 6;  // granule-fed or word-fed
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
-          g.reserved = 4;
         } else if (wide_form == 4 && (esize == 2 || esize == 4)) {
           // 16- and 32-bit rows that start anywhere: matrix form behind a register-side shift
           const uint64_t cols = trans_ms_cols(esize);

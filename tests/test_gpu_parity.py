@@ -908,10 +908,11 @@ def test_transposes_in_matrix_form_at_every_edge(dtype):
     warp-level matrix loads (blocks of 32 rows by one granule) and a per-row carry between stages of
     128 rows. Extents straddle the tile (128 bytes along the tensor's contiguous dimension, 128 and
     1024 elements along the image rows), images start on every byte residue, and batched and
-    column-offset views are in the mix."""
+    column-offset views are in the mix. The second group has rows that start on 4-byte boundaries
+    only (every residue of 4 within a granule): those stages are fed by 4-byte copies."""
     g = torch.Generator().manual_seed(31)
     esize = torch.empty((), dtype=dtype).element_size()
-    cols, gran = 128 // esize, 16 // esize  # elements per tile row / per 16-byte granule
+    cols, gran, word = 128 // esize, 16 // esize, 4 // esize  # elements per tile row / 16-byte granule / 4-byte word
 
     def base(rows, pitch):
         return torch.randint(-30000, 30000, (rows, pitch), generator=g, dtype=torch.int64).to(dtype).cuda()
@@ -921,6 +922,10 @@ def test_transposes_in_matrix_form_at_every_edge(dtype):
         (cols, 1024, cols, 0), (cols - 1, 1023, cols, 0), (cols + 1, 1025, cols + gran, 0), (1, 128, gran, 0),
         (7, 129, 2 * gran, gran), (2 * cols, 2049, 2 * cols + gran, gran), (200, 300, 208, 0), (cols, 127, cols, 0),
         (300, 5000, 304, 0), (cols, 135, cols, 0), (33, 1030, 40, 0),
+        # word-aligned rows
+        (cols, 1024, cols + word, 0), (cols - 1, 1023, cols + 3 * word, word), (cols + 1, 1025, cols + gran + word, 2 * word),
+        (1, 128, word, 0), (5, 129, 2 * gran + word, 3 * word), (2 * cols + 1, 2049, 2 * cols + gran, word),
+        (200, 300, 200 + 2 * word, word), (300, 5000, 302 + word * (esize // 4), 0), (33, 1030, 33 + (33 * esize % 4) // esize, 0),
     ]:
         views.append(base(n_l, pitch)[:, off : off + n_c].t())
     float_dtype = torch.bfloat16 if esize == 2 else torch.float32
