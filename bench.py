@@ -551,7 +551,9 @@ def run_transpose_probe(args) -> None:
         "flat_bf16_1gib": lambda: [rnd((512 << 20,), torch.bfloat16)],
         "uint8_square": lambda: [rnd((16384, 16384), torch.uint8).t()],
         "bf16_square_odd_pitch": lambda: [rnd((11585, 11585), torch.bfloat16).t()],
+        "bf16_square_word_pitch": lambda: [rnd((11586, 11586), torch.bfloat16).t()],
         "fp32_square": lambda: [rnd((8192, 8192), torch.float32).t()],
+        "fp32_square_odd_pitch": lambda: [rnd((8191, 8191), torch.float32).t()],
         "int64_square": lambda: [rnd((5792, 5792), torch.int64).t()],
         "bf16_weight_14336x4096": lambda: [rnd((14336, 4096), torch.bfloat16).t()],
         "bf16_weight_28672x8192": lambda: [rnd((28672, 8192), torch.bfloat16).t()],
@@ -575,6 +577,13 @@ def run_transpose_probe(args) -> None:
             continue
         results[name] = run(make())
         torch.cuda.empty_cache()
+    if args.probe_case == "microbench_each":  # every transposed view of the microbench of 8 MB or more, alone
+        for v in microbench_views("transposed"):
+            if v.numel() * v.element_size() >= (8 << 20):
+                key = f"{str(v.dtype).split('.')[-1]} shape {tuple(v.shape)} stride {tuple(v.stride())}"
+                copies = max(1, (256 << 20) // (v.numel() * v.element_size()))  # enough of them to outweigh the launch
+                results[key] = run([v._base.clone().as_strided(v.shape, v.stride(), v.storage_offset()) for _ in range(copies)])
+                torch.cuda.empty_cache()
     print(json.dumps({"probe": "transpose", "form": os.environ.get("MLF_TRANSPOSE_FORM", "matrix"),
                       "unit": "GB/s of read + write bytes, kernel only, median of 4 launches", "results": results}))
 

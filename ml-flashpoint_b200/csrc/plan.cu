@@ -283,8 +283,32 @@ inline uint32_t trans_a_cols(uint32_t esize) { return 240u / esize; }
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(mlf::smem_addr(smem_dst)), "l"(gmem_src) : "memory");
 }
-__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(mlf::smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+// Shared-memory accesses by 32-bit shared-window address (mlf::smem_addr): pointers that reach a
+// non-inlined tile function are generic, and generic loads and stores cost 64-bit address arithmetic.
+__device__ __forceinline__ void sts_b8(uint32_t a, uint32_t v) { asm volatile("st.shared.b8 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory"); }
+__device__ __forceinline__ void sts_b16(uint32_t a, uint32_t v) { asm volatile("st.shared.b16 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory"); }
+__device__ __forceinline__ void sts_b32(uint32_t a, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts_b64(uint32_t a, uint32_t lo, uint32_t hi) {
+  asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(a), "r"(lo), "r"(hi) : "memory");
+}
+__device__ __forceinline__ void sts_b128(uint32_t a, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 lds_b128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint8_t lds_b8(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=h"(v) : "r"(a) : "memory");
+  return (uint8_t)v;
+}
+__device__ __forceinline__ void cp_async16_at(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async4_at(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -468,10 +492,10 @@ constexpr int kTransMStageBytes = kTransML * 128;      // 16 KiB, tensor order
 constexpr int kTransMStagingOff = 2 * kTransMStageBytes;
 inline uint32_t trans_m_cols(uint32_t esize) { return 128u / esize; }
 
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_row) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(mlf::smem_addr(smem_row)));
+               : "r"(smem_row));
 }
 // Position of granule g of tensor row l inside its 128-byte stage row. The key takes the bits of l
 // in which the eight rows of one 8x8 matrix differ (see the row lists in transpose_tile_m).
@@ -511,19 +535,20 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
   const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;  // 16-byte aligned
   uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;
   const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-  uint8_t* staging = ring + kTransMStagingOff;
+  const uint32_t ring_at = mlf::smem_addr(ring), aux_at = mlf::smem_addr(aux);
+  const uint32_t staging = ring_at + kTransMStagingOff;  // shared-window addresses from here on
   auto elems_of = [&](int s) { return (int)min((int64_t)kTransML, nL - (lfirst + (int64_t)s * kTransML)); };
 
   auto issue = [&](int s) {
     const int nl = elems_of(s);
-    uint8_t* stage = ring + (s & 1) * kTransMStageBytes;
+    const uint32_t stage = ring_at + (uint32_t)(s & 1) * kTransMStageBytes;
     if (WORDS) {
       const unsigned w = tid & 31u, lr = tid >> 5;  // word within the row; row within a pass of 8 rows
 #pragma unroll 4
       for (int k = 0; k < 16; ++k) {
         const unsigned l = lr + 8u * k;
         if ((int)l < nl && 4u * w < row_bytes)
-          cp_async4(stage + l * 128u + matrix_swizzle<E>(l, w >> 2) + 4u * (w & 3u), trow0 + ((int64_t)s * kTransML + l) * tsL + 4u * w);
+          cp_async4_at(stage + l * 128u + matrix_swizzle<E>(l, w >> 2) + 4u * (w & 3u), trow0 + ((int64_t)s * kTransML + l) * tsL + 4u * w);
       }
     } else {
       const unsigned gq = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
@@ -531,7 +556,7 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
       for (int k = 0; k < 4; ++k) {
         const unsigned l = lr + 32u * k;
         if ((int)l < nl && 16u * gq < row_bytes)
-          cp_async16(stage + l * 128u + matrix_swizzle<E>(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
+          cp_async16_at(stage + l * 128u + matrix_swizzle<E>(l, gq), trow0 + ((int64_t)s * kTransML + l) * tsL + 16u * gq);
       }
     }
     cp_async_commit();
@@ -545,7 +570,7 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
     const int nl = elems_of(s);
     const int seg_len = nl * E;
     const bool first = s == 0, last = s == nsub - 1;
-    const uint8_t* stage = ring + (s & 1) * kTransMStageBytes;
+    const uint32_t stage = ring_at + (uint32_t)(s & 1) * kTransMStageBytes;
     // ---- transpose: blocks of 32 tensor rows by one granule, four per warp
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
@@ -563,7 +588,7 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
       if (E == 2) {
         // image row 8 cb + lane / 4, elements 32 lb + 8 t .. + 7
         const unsigned c = 8u * cb + (lane >> 2), l0 = 32u * lb + 8u * t;
-        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(r[0], r[1], r[2], r[3]);
+        sts_b128(staging + c * M::kPitch + l0 * E, make_uint4(r[0], r[1], r[2], r[3]));
       } else {
         // the two halves of a 32-bit element sit in this thread and in lane ^ 4: the thread with the
         // low halves (p = 0) assembles the element of row 2 t, its neighbour that of row 2 t + 1
@@ -575,7 +600,7 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
           o[q] = p ? __byte_perm(other, r[q], 0x7632) : __byte_perm(r[q], other, 0x5410);
         }
         const unsigned c = 4u * cb + (lane >> 3), l0 = 32u * lb + 8u * t + 4u * p;
-        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(o[0], o[1], o[2], o[3]);
+        sts_b128(staging + c * M::kPitch + l0 * E, make_uint4(o[0], o[1], o[2], o[3]));
       }
     }
     __syncthreads();  // staging holds the stage in image order; the tensor-order buffer is free again
@@ -583,37 +608,37 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
     // ---- write out: aligned 16-byte image vectors, kPositions per image row. With a misaligned row
     // (h != 0) the first position straddles in from the previous stage and the row's last 16 - h
     // bytes wait in the carry, so the count is the same.
-    const uint8_t* carry_in = aux + ((s + 1) & 1) * M::kCarryBytes;  // last 16 bytes of stage s - 1 per image row
-    uint8_t* carry_out = aux + (s & 1) * M::kCarryBytes;
+    const uint32_t carry_in = aux_at + (uint32_t)((s + 1) & 1) * M::kCarryBytes;  // last 16 bytes of stage s - 1 per image row
+    const uint32_t carry_out = aux_at + (uint32_t)(s & 1) * M::kCarryBytes;
     uint8_t* iseg = ibase + (int64_t)s * M::kSegBytes;
     // 16 lanes per image row (a warp-wide store covers two rows of 256 contiguous bytes)
     for (int c = (int)(tid >> 4); c < nc; c += (int)(kThreads >> 4)) {
       uint8_t* row = iseg + (int64_t)c * isC;
-      const uint8_t* data = staging + c * M::kPitch;
+      const uint32_t data = staging + (uint32_t)c * M::kPitch;
       const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);  // the same in every stage
 #pragma unroll
       for (int j = 0; j < M::kPositions / 16; ++j) {
         const int vq = (int)(tid & 15u) + 16 * j;
         if (h == 0) {
-          if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
+          if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), lds_b128(data + 16u * vq));
         } else {
           const int q = h - 16 + 16 * vq;  // stage-relative first byte of the vector
           if (q + 16 <= seg_len && !(first && vq == 0)) {
-            const uint4 lo = vq == 0 ? *reinterpret_cast<const uint4*>(carry_in + c * 16) : *reinterpret_cast<const uint4*>(data + 16 * (vq - 1));
-            const uint4 hi = *reinterpret_cast<const uint4*>(data + 16 * vq);
+            const uint4 lo = lds_b128(vq == 0 ? carry_in + (uint32_t)c * 16u : data + 16u * (vq - 1));
+            const uint4 hi = lds_b128(data + 16u * vq);
             mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
           }
         }
       }
     }
     if (!last && (int)tid < nc)
-      *reinterpret_cast<uint4*>(carry_out + tid * 16) = *reinterpret_cast<const uint4*>(staging + tid * M::kPitch + M::kSegBytes - 16);
+      sts_b128(carry_out + tid * 16u, lds_b128(staging + tid * M::kPitch + M::kSegBytes - 16));
     if (first) {
       for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
         const int c = idx / 15, kb = idx % 15;
         uint8_t* row = iseg + (int64_t)c * isC;
         const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
-        if (kb < h && kb < seg_len) row[kb] = staging[c * M::kPitch + kb];
+        if (kb < h && kb < seg_len) row[kb] = lds_b8(staging + (uint32_t)(c * M::kPitch + kb));
       }
     }
     if (last) {
@@ -626,9 +651,9 @@ __device__ __noinline__ void transpose_tile_m(const Seg& g, uint32_t local, uint
         const int b = done + kb;
         if (b >= seg_len || (first && b < h)) continue;
         if (b >= 0)
-          row[b] = staging[c * M::kPitch + b];
+          row[b] = lds_b8(staging + (uint32_t)(c * M::kPitch + b));
         else if (!first)
-          row[b] = carry_in[c * 16 + 16 + b];
+          row[b] = lds_b8(carry_in + (uint32_t)(c * 16 + 16 + b));
       }
     }
   }
@@ -679,8 +704,8 @@ __device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uin
   const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;
   uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;
   const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-  uint8_t* stage = ring;
-  uint8_t* staging = ring + kTransMStagingOff;
+  const uint32_t stage = mlf::smem_addr(ring), aux_at = mlf::smem_addr(aux);  // shared-window addresses from here on
+  const uint32_t staging = stage + kTransMStagingOff;
   auto elems_of = [&](int s) { return (int)min((int64_t)kTransML, nL - (lfirst + (int64_t)s * kTransML)); };
   const unsigned gq = tid & 7u, lr = tid >> 3;  // granule within the row; row within a pass of 32 rows
 
@@ -710,7 +735,7 @@ __device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uin
       const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
       const uint4 next = mlf::shfl_down1(v[k]);  // granule gq + 1 of the same row (lanes 8 r .. 8 r + 7 share a row)
       const uint4 out = m ? mlf::realign(v[k], next, m) : v[k];  // row bytes [16 gq, 16 gq + 16)
-      if (gq < (unsigned)M::kGranules) *reinterpret_cast<uint4*>(stage + l * 128u + matrix_swizzle<E>(l, gq)) = out;
+      if (gq < (unsigned)M::kGranules) sts_b128(stage + l * 128u + matrix_swizzle<E>(l, gq), out);
     }
     __syncthreads();  // the stage is complete; every thread is done draining the staging area of stage s - 1
     if (s + 1 < nsub) load(s + 1);  // in flight while this stage is transposed and written out
@@ -727,7 +752,7 @@ __device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uin
       const unsigned t = lane & 3u;
       if (E == 2) {
         const unsigned c = 8u * cb + (lane >> 2), l0 = 32u * lb + 8u * t;
-        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(r[0], r[1], r[2], r[3]);
+        sts_b128(staging + c * M::kPitch + l0 * E, make_uint4(r[0], r[1], r[2], r[3]));
       } else {
         const unsigned p = (lane >> 2) & 1u;
         uint32_t o[4];
@@ -737,41 +762,41 @@ __device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uin
           o[q] = p ? __byte_perm(other, r[q], 0x7632) : __byte_perm(r[q], other, 0x5410);
         }
         const unsigned c = 4u * cb + (lane >> 3), l0 = 32u * lb + 8u * t + 4u * p;
-        *reinterpret_cast<uint4*>(staging + c * M::kPitch + l0 * E) = make_uint4(o[0], o[1], o[2], o[3]);
+        sts_b128(staging + c * M::kPitch + l0 * E, make_uint4(o[0], o[1], o[2], o[3]));
       }
     }
     __syncthreads();  // staging holds the stage in image order; the tensor-order stage is free again
     // ---- write out (as in transpose_tile_m)
-    const uint8_t* carry_in = aux + ((s + 1) & 1) * M::kCarryBytes;
-    uint8_t* carry_out = aux + (s & 1) * M::kCarryBytes;
+    const uint32_t carry_in = aux_at + (uint32_t)((s + 1) & 1) * M::kCarryBytes;
+    const uint32_t carry_out = aux_at + (uint32_t)(s & 1) * M::kCarryBytes;
     uint8_t* iseg = ibase + (int64_t)s * M::kSegBytes;
     for (int c = (int)(tid >> 4); c < nc; c += (int)(kThreads >> 4)) {
       uint8_t* row = iseg + (int64_t)c * isC;
-      const uint8_t* data = staging + c * M::kPitch;
+      const uint32_t data = staging + (uint32_t)c * M::kPitch;
       const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
 #pragma unroll
       for (int j = 0; j < M::kPositions / 16; ++j) {
         const int vq = (int)(tid & 15u) + 16 * j;
         if (h == 0) {
-          if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), *reinterpret_cast<const uint4*>(data + 16 * vq));
+          if (16 * (vq + 1) <= seg_len) mlf::st_vec(reinterpret_cast<uint4*>(row + 16 * vq), lds_b128(data + 16u * vq));
         } else {
           const int q = h - 16 + 16 * vq;
           if (q + 16 <= seg_len && !(first && vq == 0)) {
-            const uint4 lo = vq == 0 ? *reinterpret_cast<const uint4*>(carry_in + c * 16) : *reinterpret_cast<const uint4*>(data + 16 * (vq - 1));
-            const uint4 hi = *reinterpret_cast<const uint4*>(data + 16 * vq);
+            const uint4 lo = lds_b128(vq == 0 ? carry_in + (uint32_t)c * 16u : data + 16u * (vq - 1));
+            const uint4 hi = lds_b128(data + 16u * vq);
             mlf::st_vec(reinterpret_cast<uint4*>(row + q), mlf::realign(lo, hi, (unsigned)h));
           }
         }
       }
     }
     if (!last && (int)tid < nc)
-      *reinterpret_cast<uint4*>(carry_out + tid * 16) = *reinterpret_cast<const uint4*>(staging + tid * M::kPitch + M::kSegBytes - 16);
+      sts_b128(carry_out + tid * 16u, lds_b128(staging + tid * M::kPitch + M::kSegBytes - 16));
     if (first) {
       for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
         const int c = idx / 15, kb = idx % 15;
         uint8_t* row = iseg + (int64_t)c * isC;
         const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
-        if (kb < h && kb < seg_len) row[kb] = staging[c * M::kPitch + kb];
+        if (kb < h && kb < seg_len) row[kb] = lds_b8(staging + (uint32_t)(c * M::kPitch + kb));
       }
     }
     if (last) {
@@ -784,13 +809,241 @@ __device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uin
         const int b = done + kb;
         if (b >= seg_len || (first && b < h)) continue;
         if (b >= 0)
-          row[b] = staging[c * M::kPitch + b];
+          row[b] = lds_b8(staging + (uint32_t)(c * M::kPitch + b));
         else if (!first)
-          row[b] = carry_in[c * 16 + 16 + b];
+          row[b] = lds_b8(carry_in + (uint32_t)(c * 16 + 16 + b));
       }
     }
   }
   __syncthreads();  // the staging area and the carries are free for the next tile
+}
+
+// Narrow transposed rows, pack direction: sub-tile j holds the image rows [cfirst + j d, + d) of
+// nln elements each, one contiguous run of the image, staged in shared memory in image order. The
+// tensor side is read in aligned 16-byte granules: granule q of tensor row l covers bytes
+// [16 q - m, 16 q - m + 16) of that row's run of ncn elements, m being the row's misalignment. Only
+// granules holding at least one byte of the run are read; elements outside it are dropped when the
+// granule is scattered into the staging area. A sub-tile has at most narrow_bytes / 16 + 2 nln such
+// granules, which is below 3 kThreads for every element size (rows are shorter than 256 bytes, 128
+// for single bytes).
+template <typename T>
+__device__ __noinline__ void transpose_narrow_granules(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
+  constexpr int E = (int)sizeof(T);
+  constexpr int NG = 3;
+  constexpr int EPG = 16 / E;
+  constexpr int LOG_E = E == 1 ? 0 : E == 2 ? 1 : E == 4 ? 2 : 3;
+  constexpr int32_t kNone = 0x40000000;  // as first image row: every element fails the range check
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  int64_t toff = 0, ioff = 0;
+  for (int k = L - 1; k >= 0; --k) {
+    if (k == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[k]);
+    batch /= (uint64_t)g.shape[k];
+    toff += idx * g.tstride[k];
+    ioff += idx * g.istride[k];
+  }
+  const uint8_t* tbase = reinterpret_cast<const uint8_t*>(g.tensor) + toff;
+  uint8_t* ibase = image + g.image_off + ioff;
+  const int64_t nC = g.shape[C], tsL = g.tstride[L], isC = g.istride[C];
+  const uint32_t nln = (uint32_t)g.shape[L], d = g.d;
+  const int64_t cfirst = (int64_t)in_batch * d * kTransSub;
+  const int nsub = (int)min((int64_t)kTransSub, (nC - cfirst + d - 1) / d);
+  const unsigned tid = threadIdx.x;
+  const uint32_t step = nln * E;  // staging distance between neighbouring image rows
+  uint4 q[NG];
+  int32_t gc[NG];  // image row (within the sub-tile) of the granule's first element; may be negative
+  int32_t at[NG];  // staging offset of that element
+  auto rows_of = [&](int j) { return (uint32_t)min((int64_t)d, nC - (cfirst + (int64_t)j * d)); };
+  auto load = [&](int j) {
+    const uint32_t run = rows_of(j) * E;
+    const uint8_t* trun = tbase + (cfirst + (int64_t)j * d) * E;
+    const uint32_t per_row = ((run + 15u) >> 4) + 1u;
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+      const uint32_t idx = tid + (uint32_t)k * kThreads;
+      const uint32_t l = idx / per_row, qi = idx - l * per_row;
+      const uint8_t* row = trun + (int64_t)l * tsL;
+      const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+      const bool have = l < nln && 16u * qi < m + run;
+      q[k] = have ? mlf::ld_vec(reinterpret_cast<const uint4*>(row - m + 16u * qi)) : make_uint4(0, 0, 0, 0);
+      const int32_t c = ((int32_t)(16u * qi) - (int32_t)m) >> LOG_E;
+      gc[k] = have ? c : kNone;
+      at[k] = c * (int32_t)step + (int32_t)(l * E);
+    }
+  };
+  load(0);
+  for (int j = 0; j < nsub; ++j) {
+    const uint32_t ncn = rows_of(j);
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+      const uint32_t w[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+#pragma unroll
+      for (int i = 0; i < EPG; ++i) {
+        if ((uint32_t)(gc[k] + i) < ncn) {
+          uint8_t* p = smem + swz((uint32_t)(at[k] + i * (int32_t)step));
+          if (E == 8)
+            *reinterpret_cast<uint2*>(p) = make_uint2(w[2 * i], w[2 * i + 1]);
+          else if (E == 4)
+            *reinterpret_cast<uint32_t*>(p) = w[i];
+          else if (E == 2)
+            *reinterpret_cast<uint16_t*>(p) = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
+          else
+            *p = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+        }
+      }
+    }
+    __syncthreads();
+    if (j + 1 < nsub) load(j + 1);
+    drain_swizzled(ibase + (cfirst + (int64_t)j * d) * isC, smem, ncn * step, tid, kThreads);
+    __syncthreads();
+  }
+}
+
+// drain_swizzled with the staging area given by its shared-window address.
+__device__ __forceinline__ void drain_swizzled_at(uint8_t* __restrict__ dst, uint32_t staged, uint32_t len, unsigned tid, unsigned nthr) {
+  const uint32_t head = min((16u - (uint32_t)((uintptr_t)dst & 15u)) & 15u, len);
+  if (tid < head) dst[tid] = lds_b8(staged + swz(tid));
+  const uint32_t nvec = (len - head) >> 4;
+  uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + head);
+  if (head == 0) {
+#pragma unroll 4
+    for (uint32_t i = tid; i < nvec; i += nthr) mlf::st_vec(d4 + i, lds_b128(staged + swz(i << 4)));
+  } else {
+#pragma unroll 4
+    for (uint32_t i = tid; i < nvec; i += nthr)
+      mlf::st_vec(d4 + i, mlf::realign(lds_b128(staged + swz(i << 4)), lds_b128(staged + swz((i + 1) << 4)), head));
+  }
+  const uint32_t tail = (len - head) & 15u;
+  if (tid < tail) {
+    const uint32_t o = head + (nvec << 4) + tid;
+    dst[o] = lds_b8(staged + swz(o));
+  }
+}
+
+// Pipelined form of the narrow transposed rows (pack direction, bulk kernels; segments planned with
+// g.reserved == 7 and kNarrowASub sub-tiles per tile). The granules of transpose_narrow_granules
+// arrive by cp.async in stages of their own, kNarrowAStages - 1 sub-tiles ahead; every thread reads
+// back exactly the granules it asked for, so a stage needs no barrier. The image-order staging area
+// is doubled: while a sub-tile drains, the next one is scattered into the other half, with one
+// barrier per sub-tile. `ring`: the stages, then the two staging halves.
+constexpr int kNarrowASub = 16;
+constexpr int kNarrowAStages = 4;
+constexpr int kNarrowAGranules = 3;  // per thread and sub-tile
+constexpr int kNarrowARawBytes = kNarrowAGranules * (int)kThreads * 16;
+constexpr int kNarrowAStagingOff = kNarrowAStages * kNarrowARawBytes;
+constexpr int kNarrowASmemBytes = kNarrowAStagingOff + 2 * 8192;
+template <typename T>
+__device__ __noinline__ void transpose_narrow_async(const Seg& g, uint32_t local, uint8_t* image, uint8_t* ring) {
+  constexpr int E = (int)sizeof(T);
+  constexpr int NG = kNarrowAGranules;
+  constexpr int S = kNarrowAStages;
+  constexpr int EPG = 16 / E;
+  constexpr int LOG_E = E == 1 ? 0 : E == 2 ? 1 : E == 4 ? 2 : 3;
+  const int L = (int)g.ndim - 1;
+  const int C = (int)g.c;
+  const uint32_t tiles_per_batch = (uint32_t)g.a;
+  uint64_t batch = local / tiles_per_batch;
+  const uint32_t in_batch = local % tiles_per_batch;
+  int64_t toff = 0, ioff = 0;
+  for (int k = L - 1; k >= 0; --k) {
+    if (k == C) continue;
+    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[k]);
+    batch /= (uint64_t)g.shape[k];
+    toff += idx * g.tstride[k];
+    ioff += idx * g.istride[k];
+  }
+  const uint8_t* tbase = reinterpret_cast<const uint8_t*>(g.tensor) + toff;
+  uint8_t* ibase = image + g.image_off + ioff;
+  const int64_t nC = g.shape[C], tsL = g.tstride[L], isC = g.istride[C];
+  const uint32_t nln = (uint32_t)g.shape[L], d = g.d;
+  const int64_t cfirst = (int64_t)in_batch * d * kNarrowASub;
+  const int nsub = (int)min((int64_t)kNarrowASub, (nC - cfirst + d - 1) / d);
+  const unsigned tid = threadIdx.x;
+  const uint32_t step = nln * E;  // staging distance between neighbouring image rows
+  auto rows_of = [&](int j) { return (uint32_t)min((int64_t)d, nC - (cfirst + (int64_t)j * d)); };
+  // Granule k of this thread is granule gq[k] of tensor row gl[k] in every sub-tile: rows are cut
+  // into per_row granules as for a full sub-tile of d image rows; shorter runs leave some unused.
+  struct Granule {
+    const uint8_t* src;
+    int32_t c;  // image row (within the sub-tile) of the first element; may be negative
+    bool have;  // the granule holds at least one byte of the run
+  };
+  const uint32_t per_row = ((d * E + 15u) >> 4) + 1u;
+  uint32_t gl[NG], gq[NG];
+#pragma unroll
+  for (int k = 0; k < NG; ++k) {
+    const uint32_t idx = tid + (uint32_t)k * kThreads;
+    gl[k] = idx / per_row;
+    gq[k] = 16u * (idx - gl[k] * per_row);
+  }
+  auto granule = [&](int j, int k) {
+    const uint32_t run = rows_of(j) * E;
+    const uint8_t* row = tbase + (cfirst + (int64_t)j * d) * E + (int64_t)gl[k] * tsL;
+    const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
+    Granule r;
+    r.have = gl[k] < nln && gq[k] < m + run;
+    r.src = row - m + gq[k];
+    r.c = ((int32_t)gq[k] - (int32_t)m) >> LOG_E;
+    return r;
+  };
+  const uint32_t ring_at = mlf::smem_addr(ring);
+  auto issue = [&](int j) {
+    const uint32_t raw = ring_at + (uint32_t)(j % S) * kNarrowARawBytes;
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+      const Granule r = granule(j, k);
+      if (r.have)
+        cp_async16_at(raw + (tid + (uint32_t)k * kThreads) * 16u, r.src);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int j = 0; j < S - 1; ++j) {
+    if (j < nsub) issue(j); else cp_async_commit();
+  }
+  for (int j = 0; j < nsub; ++j) {
+    if (j + S - 1 < nsub) issue(j + S - 1); else cp_async_commit();
+    cp_async_wait<S - 1>();  // this thread's granules of sub-tile j have landed
+    const uint32_t raw = ring_at + (uint32_t)(j % S) * kNarrowARawBytes;
+    const uint32_t staging = ring_at + kNarrowAStagingOff + (uint32_t)(j & 1) * 8192u;
+    const uint32_t ncn = rows_of(j);
+    auto put = [&](uint32_t off, const uint32_t (&w)[4], int i) {
+      const uint32_t a = staging + swz(off);
+      if (E == 8)
+        sts_b64(a, w[(2 * i) & 3], w[(2 * i + 1) & 3]);
+      else if (E == 4)
+        sts_b32(a, w[i & 3]);
+      else if (E == 2)
+        sts_b16(a, w[(i >> 1) & 3] >> (16 * (i & 1)));
+      else
+        sts_b8(a, w[(i >> 2) & 3] >> (8 * (i & 3)));
+    };
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+      const Granule r = granule(j, k);
+      if (r.have) {
+        const uint4 v = lds_b128(raw + (tid + (uint32_t)k * kThreads) * 16u);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t at = (uint32_t)(r.c * (int32_t)step + (int32_t)(gl[k] * E));
+        if (r.c >= 0 && r.c + EPG <= (int32_t)ncn) {  // every element lies in the run
+#pragma unroll
+          for (int i = 0; i < EPG; ++i) put(at + (uint32_t)i * step, w, i);
+        } else {
+#pragma unroll
+          for (int i = 0; i < EPG; ++i)
+            if ((uint32_t)(r.c + i) < ncn) put(at + (uint32_t)i * step, w, i);
+        }
+      }
+    }
+    __syncthreads();  // sub-tile j is staged; everyone is done draining sub-tile j - 1
+    drain_swizzled_at(ibase + (cfirst + (int64_t)j * d) * isC, staging, ncn * step, tid, kThreads);
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // the stages and the staging halves are free for the next tile
 }
 
 // Tile `local` of TRANSPOSE segment g. Must run with kThreads threads.
@@ -826,7 +1079,7 @@ __device__ MLF_TRANSPOSE_ATTR void transpose_tile(const Seg& g, uint32_t local, 
     // (slow, fast) = (n / nfast, n % nfast), advanced incrementally by kThreads per step.
     //   transposed (g.reserved == 0): fast = image row c, slow = position l in the row
     //   row order  (g.reserved == 1): fast = position in the row, slow = image row
-    const bool row_order = g.reserved != 0;
+    const bool row_order = g.reserved == 1;
     const uint32_t nln = (uint32_t)nL;
     const int64_t cfirst = (int64_t)in_batch * g.d * kTransSub;
     const int nsub = (int)min((int64_t)kTransSub, (nC - cfirst + g.d - 1) / g.d);
@@ -1173,6 +1426,22 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
       case 4: transpose_tile_v<uint32_t, MLF_PACK>(g, local, image, vsmem); break;
       default: transpose_tile_v<uint64_t, MLF_PACK>(g, local, image, vsmem); break;
     }
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d != 0 && g.reserved == 7) {
+    // narrow transposed rows, pipelined: stages and staging halves in `vsmem` (the idle ring)
+    switch (g.esize) {
+      case 1: transpose_narrow_async<uint8_t>(g, local, image, vsmem); break;
+      case 2: transpose_narrow_async<uint16_t>(g, local, image, vsmem); break;
+      case 4: transpose_narrow_async<uint32_t>(g, local, image, vsmem); break;
+      default: transpose_narrow_async<uint64_t>(g, local, image, vsmem); break;
+    }
+  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d != 0 && g.reserved == 0) {
+    // narrow transposed rows: tensor side read in 16-byte granules
+    switch (g.esize) {
+      case 1: transpose_narrow_granules<uint8_t>(g, local, image, tsmem); break;
+      case 2: transpose_narrow_granules<uint16_t>(g, local, image, tsmem); break;
+      case 4: transpose_narrow_granules<uint32_t>(g, local, image, tsmem); break;
+      default: transpose_narrow_granules<uint64_t>(g, local, image, tsmem); break;
+    }
   } else if (g.kind == kTranspose) {
     switch (g.esize) {
       case 1: transpose_tile<uint8_t, DIR>(g, local, image, tsmem); break;
@@ -1515,6 +1784,7 @@ static_assert(2 * kTransACarryBytes + 2 * kTransAL <= kTransSmemBytes, "carries 
 static_assert(kTransMStagingOff + TransM<2>::kCols * TransM<2>::kPitch <= (int)kBulkDynSmem &&
                   kTransMStagingOff + TransM<4>::kCols * TransM<4>::kPitch <= (int)kBulkDynSmem,
               "matrix form: two stages and the staging area fit the ring");
+static_assert(kNarrowASmemBytes <= (int)kBulkDynSmem, "pipelined narrow rows: stages and staging halves fit the ring");
 static_assert(2 * TransM<2>::kCarryBytes <= kTransSmemBytes, "matrix form: carries fit the static staging area");
 
 __global__ void __launch_bounds__(kThreads) mlf_flat_copy_kernel(uint8_t* __restrict__ dst,
@@ -1769,7 +2039,8 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
         if (row_bytes < row_cap && (uint64_t)c.is[cdim] == row_bytes) {
           // short image rows lying back to back: a sub-tile is as many whole rows as fit the staging area
           g.d = (uint32_t)std::max<uint64_t>(1, (uint64_t)trans_narrow_bytes(esize) / row_bytes);
-          const uint64_t rows_per_tile = (uint64_t)g.d * kTransSub;
+          if (wide_form != 0) g.reserved = 7;  // pack plans of the bulk kernels: pipelined form, longer tiles
+          const uint64_t rows_per_tile = (uint64_t)g.d * (wide_form != 0 ? kNarrowASub : kTransSub);
           tc = ((uint64_t)c.shape[cdim] + rows_per_tile - 1) / rows_per_tile;
           tl = 1;
         } else if (wide_form == 4 && matrix_form_eligible(esize, d.tensor_ptr, c, cdim, 4)) {

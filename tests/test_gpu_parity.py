@@ -932,3 +932,27 @@ def test_transposes_in_matrix_form_at_every_edge(dtype):
     views.append(torch.randint(-9, 9, (3, 700, 80), generator=g, dtype=torch.int64).to(float_dtype).cuda().transpose(1, 2))
     for first_offset in (0, 1, 2, 9, 15):
         _pack_and_unpack_against_oracle(views, first_offset=first_offset)
+
+
+def test_narrow_transposed_rows_across_tiles_and_alignments():
+    """Transposed views whose image rows are shorter than 256 bytes: the tensor side is read in
+    aligned 16-byte granules, several sub-tiles ahead. Extents span several tiles of sixteen
+    sub-tiles with ragged last tiles and sub-tiles; column offsets and odd pitches put the tensor
+    rows on every residue of 16 bytes; images start on odd bytes."""
+    g = torch.Generator().manual_seed(37)
+
+    def base(rows, pitch, dtype):
+        return torch.randint(0, 250, (rows, pitch), generator=g, dtype=torch.int64).to(dtype).cuda()
+
+    views = []
+    for dtype, n_l, n_c, extra, off in [
+        (torch.int16, 3, 50001, 0, 0), (torch.int16, 2, 70000, 3, 1), (torch.int16, 82, 3000, 5, 3), (torch.int16, 1, 40000, 1, 1),
+        (torch.int16, 127, 1500, 0, 0), (torch.int32, 19, 9000, 1, 1), (torch.int32, 3, 40000, 0, 0), (torch.int32, 63, 700, 2, 1),
+        (torch.int64, 12, 30011, 1, 0), (torch.int64, 5, 20000, 0, 0), (torch.uint8, 7, 60013, 5, 2), (torch.uint8, 100, 5000, 9, 7),
+        (torch.int16, 8, 33, 0, 0), (torch.int32, 2, 1, 0, 0),
+    ]:
+        views.append(base(n_l, n_c + off + extra, dtype)[:, off : off + n_c].t())
+    views.append(torch.randint(0, 250, (37, 11, 700), generator=g, dtype=torch.int64).to(torch.int16).cuda().transpose(1, 2))  # batched
+    views.append(torch.randint(0, 250, (5, 3, 30000), generator=g, dtype=torch.int64).to(torch.int32).cuda().transpose(1, 2))
+    for first_offset in (0, 1, 7):
+        _pack_and_unpack_against_oracle(views, first_offset=first_offset)
