@@ -484,7 +484,7 @@ def run_transpose_probe(args) -> None:
     """Kernel-only throughput of transposed views, pack and unpack, through the C ABI (one plan, one
     launch per direction, CUDA events, L2 flushed between launches), each result checked against
     torch. Read + write bytes per second. ``MLF_TRANSPOSE_FORM`` selects the form of wide pack
-    transposes (matrix | vector | async | element)."""
+    transposes (matrix | vector | element)."""
     from ml_flashpoint import _native
     from ml_flashpoint.core.gpu_engine import _Plan, c_strides, fill_desc
 

@@ -255,34 +255,7 @@ __device__ __noinline__ void transpose_tile_v(const Seg& g, uint32_t local, uint
   }
 }
 
-// Asynchronous form of the wide TRANSPOSE tile (pack direction; segments planned with g.reserved == 3,
-// bulk kernels only). Tensor rows stream into shared memory as aligned 16-byte granules with
-// cp.async, two 32 KiB stages deep (128 tensor rows of 256 bytes each, of which the 240 bytes behind
-// any misalignment of the row start are delivered), so the loads of the next stage are in flight,
-// without holding registers, while this stage is written out. The image side is produced straight
-// from the staged tensor rows: a lane owns one image row, gathers the 16 / E elements of an aligned
-// 16-byte image vector column-wise (consecutive lanes read consecutive elements of one tensor row),
-// shifts by the image's byte misalignment and stores the vector. Image vectors that straddle two
-// stages take their leading bytes from a per-row carry of the previous stage's last 16 bytes; only
-// the first bytes and the last bytes of a tile's image rows are written bytewise.
-template <int E>
-struct TransA {
-  static constexpr int kLoadBytes = 256;
-  static constexpr int kOutBytes = 240;
-  static constexpr int kC = kOutBytes / E;            // image rows per tile: 240, 120, 60, 30
-  static constexpr int kL = 128;                      // tensor rows (elements along L) per stage
-  static constexpr int kStageBytes = kL * kLoadBytes; // 32 KiB
-  static constexpr int kPer = 16 / E;
-  static constexpr int kSegBytes = kL * E;            // bytes of one image row per full stage
-};
-constexpr int kTransASub = 8;                          // stages per tile
-constexpr int kTransAL = 128;
-constexpr int kTransACarryBytes = 240 * 16;            // one 16-byte carry per image row
-inline uint32_t trans_a_cols(uint32_t esize) { return 240u / esize; }
-
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(mlf::smem_addr(smem_dst)), "l"(gmem_src) : "memory");
-}
+// cp.async and shared-memory helpers of the staged transposes.
 // Shared-memory accesses by 32-bit shared-window address (mlf::smem_addr): pointers that reach a
 // non-inlined tile function are generic, and generic loads and stores cost 64-bit address arithmetic.
 __device__ __forceinline__ void sts_b8(uint32_t a, uint32_t v) { asm volatile("st.shared.b8 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory"); }
@@ -314,153 +287,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-// `stages`: 2 x 32 KiB; `aux`: 2 x kTransACarryBytes of carry followed by 2 x 128 bytes of row shifts.
-template <typename T>
-__device__ __noinline__ void transpose_tile_a(const Seg& g, uint32_t local, uint8_t* image, uint8_t* stages, uint8_t* aux) {
-  constexpr int E = (int)sizeof(T);
-  using A = TransA<E>;
-  const int L = (int)g.ndim - 1;
-  const int C = (int)g.c;
-  const uint32_t tiles_per_batch = (uint32_t)g.a;
-  uint64_t batch = local / tiles_per_batch;
-  const uint32_t in_batch = local % tiles_per_batch;
-  int64_t toff = 0, ioff = 0;
-  for (int d = L - 1; d >= 0; --d) {
-    if (d == C) continue;
-    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[d]);
-    batch /= (uint64_t)g.shape[d];
-    toff += idx * g.tstride[d];
-    ioff += idx * g.istride[d];
-  }
-  const int64_t nC = g.shape[C], nL = g.shape[L];
-  const int64_t tsL = g.tstride[L], isC = g.istride[C];
-  const int64_t c0 = (int64_t)(in_batch / g.b) * A::kC;
-  const int64_t lfirst = (int64_t)(in_batch % g.b) * (A::kL * kTransASub);
-  const int nsub = (int)min((int64_t)kTransASub, (nL - lfirst + A::kL - 1) / A::kL);
-  const int nc = (int)min((int64_t)A::kC, nC - c0);
-  const uint32_t row_bytes = (uint32_t)nc * E;
-  const uint8_t* trow0 = reinterpret_cast<const uint8_t*>(g.tensor) + toff + c0 * (int64_t)E + lfirst * tsL;
-  uint8_t* ibase = image + g.image_off + ioff + c0 * isC + lfirst * (int64_t)E;  // image row c0 at element lfirst
-  const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-  uint8_t* carry_buf = aux;
-  uint8_t* shift_tab = aux + 2 * kTransACarryBytes;
-  auto elems_of = [&](int s) { return (int)min((int64_t)A::kL, nL - (lfirst + (int64_t)s * A::kL)); };
-
-  auto issue = [&](int s) {
-    const int nl = elems_of(s);
-    uint8_t* stage = stages + (s & 1) * A::kStageBytes;
-    uint8_t* shifts = shift_tab + (s & 1) * A::kL;
-    const unsigned j = tid & 15u, lr = tid >> 4;  // granule within the row; row within a pass of 16 rows
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int l = (int)lr + 16 * k;
-      if (l < nl) {
-        const uint8_t* row = trow0 + ((int64_t)s * A::kL + l) * tsL;
-        const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
-        if (j == 0) shifts[l] = (uint8_t)m;
-        // only granules that hold at least one byte of the row are touched
-        if (16u * j < m + row_bytes) cp_async16(stage + l * A::kLoadBytes + 16u * j, row - m + 16u * j);
-      }
-    }
-    cp_async_commit();
-  };
-
-  issue(0);
-  if (nsub > 1) issue(1); else cp_async_commit();
-  for (int s = 0; s < nsub; ++s) {
-    if (s + 1 < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
-    __syncthreads();  // stage s and its shift table are complete for every thread
-    const int nl = elems_of(s);
-    const int seg_len = nl * E;
-    const bool first = s == 0, last = s == nsub - 1;
-    const uint8_t* stage = stages + (s & 1) * A::kStageBytes;
-    const uint8_t* shifts = shift_tab + (s & 1) * A::kL;
-    const uint8_t* carry_in = carry_buf + ((s + 1) & 1) * kTransACarryBytes;  // written by stage s - 1
-    uint8_t* carry_out = carry_buf + (s & 1) * kTransACarryBytes;
-    // element e of image row c in this stage (e < 0: from the carry of the previous stage)
-    auto elem = [&](int c, int e) -> T {
-      if (e >= 0) return *reinterpret_cast<const T*>(stage + e * A::kLoadBytes + shifts[e] + c * E);
-      return *reinterpret_cast<const T*>(carry_in + c * 16 + (A::kPer + e) * E);
-    };
-    uint8_t* iseg = ibase + (int64_t)s * A::kSegBytes;  // image row c0, first byte of this stage
-    const int nblocks = (nc + 31) >> 5;
-    const int nvmax = (seg_len + 16 + 15) >> 4;
-    for (int item = (int)warp; item < nblocks * nvmax; item += (int)(kThreads >> 5)) {
-      const int c = (item % nblocks) * 32 + (int)lane;
-      const int vq = item / nblocks;
-      if (c >= nc) continue;
-      uint8_t* row = iseg + (int64_t)c * isC;
-      const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);  // the same in every stage: stages are multiples of 16 bytes
-      const int q = (h ? h - 16 : 0) + 16 * vq;  // stage-relative first byte of this aligned vector
-      if (q + 16 > seg_len || (first && q < 0)) continue;
-      const int e0 = q >= 0 ? q / E : -((-q + E - 1) / E);  // floor
-      const int sh = q - e0 * E;                            // 0 .. E - 1
-      uint32_t w[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-#pragma unroll
-      for (int i = 0; i < A::kPer; ++i) {
-        const T x = elem(c, e0 + i);
-        if (E == 8) {
-          w[2 * i] = (uint32_t)((uint64_t)x & 0xffffffffu);
-          w[2 * i + 1] = (uint32_t)((uint64_t)x >> 32);
-        } else if (E == 4) {
-          w[i] = (uint32_t)x;
-        } else if (E == 2) {
-          w[i >> 1] |= (uint32_t)x << ((i & 1) * 16);
-        } else {
-          w[i >> 2] |= (uint32_t)x << ((i & 3) * 8);
-        }
-      }
-      uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
-      if (sh) {  // the image is not aligned to the element size: one more element, then shift
-        const T x = elem(c, e0 + A::kPer);
-        if (E == 8) {
-          w[4] = (uint32_t)((uint64_t)x & 0xffffffffu);
-          w[5] = (uint32_t)((uint64_t)x >> 32);
-        } else {
-          w[4] = (uint32_t)x;
-        }
-        out = mlf::realign(out, make_uint4(w[4], w[5], 0u, 0u), (unsigned)sh);
-      }
-      mlf::st_vec(reinterpret_cast<uint4*>(row + q), out);
-    }
-    if (!last) {
-      // the last 16 bytes of every image row of this stage, for the vectors that straddle into the next one
-      for (int c = (int)tid; c < nc; c += (int)kThreads)
-#pragma unroll
-        for (int i = 0; i < A::kPer; ++i) *reinterpret_cast<T*>(carry_out + c * 16 + i * E) = elem(c, nl - A::kPer + i);
-    }
-    if (first) {
-      // bytes before the first aligned vector of each image row
-      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
-        const int c = idx / 15, k = idx % 15;
-        uint8_t* row = iseg + (int64_t)c * isC;
-        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
-        if (k < h && k < seg_len) row[k] = stage[(k / E) * A::kLoadBytes + shifts[k / E] + c * E + k % E];
-      }
-    }
-    if (last) {
-      // bytes behind the last aligned vector of each image row
-      for (int idx = (int)tid; idx < nc * 15; idx += (int)kThreads) {
-        const int c = idx / 15, k = idx % 15;
-        uint8_t* row = iseg + (int64_t)c * isC;
-        const int h = (int)((16u - (uint32_t)((uintptr_t)row & 15u)) & 15u);
-        // vectors of this stage end at the last 16-byte boundary of the image inside the segment
-        int done = seg_len - (int)(((uintptr_t)row + (uint32_t)seg_len) & 15u);
-        if (first && done < h) done = min(h, seg_len);  // the segment holds no aligned vector at all
-        const int b = done + k;
-        if (b >= seg_len || (first && b < h)) continue;
-        if (b >= 0)
-          row[b] = stage[(b / E) * A::kLoadBytes + shifts[b / E] + c * E + b % E];
-        else if (!first)
-          row[b] = carry_in[c * 16 + 16 + b];  // a last stage shorter than the image's misalignment: the previous stage's tail
-      }
-    }
-    __syncthreads();  // every thread is done with stage s: its buffer may be refilled
-    if (s + 2 < nsub) issue(s + 2); else cp_async_commit();
-  }
-  cp_async_wait<0>();
 }
 
 // Matrix form of the wide TRANSPOSE tile: 16- and 32-bit elements, pack direction, tensor rows that
@@ -818,91 +644,6 @@ __device__ __noinline__ void transpose_tile_ms(const Seg& g, uint32_t local, uin
   __syncthreads();  // the staging area and the carries are free for the next tile
 }
 
-// Narrow transposed rows, pack direction: sub-tile j holds the image rows [cfirst + j d, + d) of
-// nln elements each, one contiguous run of the image, staged in shared memory in image order. The
-// tensor side is read in aligned 16-byte granules: granule q of tensor row l covers bytes
-// [16 q - m, 16 q - m + 16) of that row's run of ncn elements, m being the row's misalignment. Only
-// granules holding at least one byte of the run are read; elements outside it are dropped when the
-// granule is scattered into the staging area. A sub-tile has at most narrow_bytes / 16 + 2 nln such
-// granules, which is below 3 kThreads for every element size (rows are shorter than 256 bytes, 128
-// for single bytes).
-template <typename T>
-__device__ __noinline__ void transpose_narrow_granules(const Seg& g, uint32_t local, uint8_t* image, uint8_t* smem) {
-  constexpr int E = (int)sizeof(T);
-  constexpr int NG = 3;
-  constexpr int EPG = 16 / E;
-  constexpr int LOG_E = E == 1 ? 0 : E == 2 ? 1 : E == 4 ? 2 : 3;
-  constexpr int32_t kNone = 0x40000000;  // as first image row: every element fails the range check
-  const int L = (int)g.ndim - 1;
-  const int C = (int)g.c;
-  const uint32_t tiles_per_batch = (uint32_t)g.a;
-  uint64_t batch = local / tiles_per_batch;
-  const uint32_t in_batch = local % tiles_per_batch;
-  int64_t toff = 0, ioff = 0;
-  for (int k = L - 1; k >= 0; --k) {
-    if (k == C) continue;
-    const int64_t idx = (int64_t)(batch % (uint64_t)g.shape[k]);
-    batch /= (uint64_t)g.shape[k];
-    toff += idx * g.tstride[k];
-    ioff += idx * g.istride[k];
-  }
-  const uint8_t* tbase = reinterpret_cast<const uint8_t*>(g.tensor) + toff;
-  uint8_t* ibase = image + g.image_off + ioff;
-  const int64_t nC = g.shape[C], tsL = g.tstride[L], isC = g.istride[C];
-  const uint32_t nln = (uint32_t)g.shape[L], d = g.d;
-  const int64_t cfirst = (int64_t)in_batch * d * kTransSub;
-  const int nsub = (int)min((int64_t)kTransSub, (nC - cfirst + d - 1) / d);
-  const unsigned tid = threadIdx.x;
-  const uint32_t step = nln * E;  // staging distance between neighbouring image rows
-  uint4 q[NG];
-  int32_t gc[NG];  // image row (within the sub-tile) of the granule's first element; may be negative
-  int32_t at[NG];  // staging offset of that element
-  auto rows_of = [&](int j) { return (uint32_t)min((int64_t)d, nC - (cfirst + (int64_t)j * d)); };
-  auto load = [&](int j) {
-    const uint32_t run = rows_of(j) * E;
-    const uint8_t* trun = tbase + (cfirst + (int64_t)j * d) * E;
-    const uint32_t per_row = ((run + 15u) >> 4) + 1u;
-#pragma unroll
-    for (int k = 0; k < NG; ++k) {
-      const uint32_t idx = tid + (uint32_t)k * kThreads;
-      const uint32_t l = idx / per_row, qi = idx - l * per_row;
-      const uint8_t* row = trun + (int64_t)l * tsL;
-      const uint32_t m = (uint32_t)((uintptr_t)row & 15u);
-      const bool have = l < nln && 16u * qi < m + run;
-      q[k] = have ? mlf::ld_vec(reinterpret_cast<const uint4*>(row - m + 16u * qi)) : make_uint4(0, 0, 0, 0);
-      const int32_t c = ((int32_t)(16u * qi) - (int32_t)m) >> LOG_E;
-      gc[k] = have ? c : kNone;
-      at[k] = c * (int32_t)step + (int32_t)(l * E);
-    }
-  };
-  load(0);
-  for (int j = 0; j < nsub; ++j) {
-    const uint32_t ncn = rows_of(j);
-#pragma unroll
-    for (int k = 0; k < NG; ++k) {
-      const uint32_t w[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
-#pragma unroll
-      for (int i = 0; i < EPG; ++i) {
-        if ((uint32_t)(gc[k] + i) < ncn) {
-          uint8_t* p = smem + swz((uint32_t)(at[k] + i * (int32_t)step));
-          if (E == 8)
-            *reinterpret_cast<uint2*>(p) = make_uint2(w[2 * i], w[2 * i + 1]);
-          else if (E == 4)
-            *reinterpret_cast<uint32_t*>(p) = w[i];
-          else if (E == 2)
-            *reinterpret_cast<uint16_t*>(p) = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
-          else
-            *p = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
-        }
-      }
-    }
-    __syncthreads();
-    if (j + 1 < nsub) load(j + 1);
-    drain_swizzled(ibase + (cfirst + (int64_t)j * d) * isC, smem, ncn * step, tid, kThreads);
-    __syncthreads();
-  }
-}
-
 // drain_swizzled with the staging area given by its shared-window address.
 __device__ __forceinline__ void drain_swizzled_at(uint8_t* __restrict__ dst, uint32_t staged, uint32_t len, unsigned tid, unsigned nthr) {
   const uint32_t head = min((16u - (uint32_t)((uintptr_t)dst & 15u)) & 15u, len);
@@ -924,15 +665,22 @@ __device__ __forceinline__ void drain_swizzled_at(uint8_t* __restrict__ dst, uin
   }
 }
 
-// Pipelined form of the narrow transposed rows (pack direction, bulk kernels; segments planned with
-// g.reserved == 7 and kNarrowASub sub-tiles per tile). The granules of transpose_narrow_granules
-// arrive by cp.async in stages of their own, kNarrowAStages - 1 sub-tiles ahead; every thread reads
-// back exactly the granules it asked for, so a stage needs no barrier. The image-order staging area
+// Narrow transposed rows, pack direction of the bulk kernels (segments planned with
+// g.reserved == 7 and kNarrowASub sub-tiles per tile): sub-tile j holds the image rows
+// [cfirst + j d, + d) of nln elements each, one contiguous run of the image, staged in shared memory
+// in image order. The tensor side is read in aligned 16-byte granules: granule q of tensor row l
+// covers bytes [16 q - m, 16 q - m + 16) of that row's run of d elements, m being the row's
+// misalignment. Only granules holding at least one byte of the run are read; elements outside it
+// are dropped when the granule is scattered into the staging area. A sub-tile has at most
+// narrow_bytes / 16 + 2 nln such granules, which is below 3 kThreads for rows of up to 127 elements.
+// The granules arrive by cp.async in stages of their own, kNarrowAStages - 1 sub-tiles ahead; every
+// thread reads back exactly the granules it asked for, so a stage needs no barrier. The image-order staging area
 // is doubled: while a sub-tile drains, the next one is scattered into the other half, with one
 // barrier per sub-tile. `ring`: the stages, then the two staging halves.
 constexpr int kNarrowASub = 16;
 constexpr int kNarrowAStages = 4;
 constexpr int kNarrowAGranules = 3;  // per thread and sub-tile
+constexpr int kNarrowAMaxRow = 127;  // elements per image row: 8192 / 16 + 2 * 127 granules at most per sub-tile
 constexpr int kNarrowARawBytes = kNarrowAGranules * (int)kThreads * 16;
 constexpr int kNarrowAStagingOff = kNarrowAStages * kNarrowARawBytes;
 constexpr int kNarrowASmemBytes = kNarrowAStagingOff + 2 * 8192;
@@ -1406,18 +1154,7 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
     else
       transpose_tile_m<4, true>(g, local, image, vsmem, tsmem);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 5) {
-    if (g.esize == 2)
-      transpose_tile_ms<2>(g, local, image, vsmem, tsmem);
-    else
-      transpose_tile_ms<4>(g, local, image, vsmem, tsmem);
-  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 3) {
-    // wide rows in asynchronous form: two 32 KiB stages in `vsmem` (the idle ring), carries in `tsmem`
-    switch (g.esize) {
-      case 1: transpose_tile_a<uint8_t>(g, local, image, vsmem, tsmem); break;
-      case 2: transpose_tile_a<uint16_t>(g, local, image, vsmem, tsmem); break;
-      case 4: transpose_tile_a<uint32_t>(g, local, image, vsmem, tsmem); break;
-      default: transpose_tile_a<uint64_t>(g, local, image, vsmem, tsmem); break;
-    }
+    transpose_tile_ms<2>(g, local, image, vsmem, tsmem);
   } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d == 0 && g.reserved == 2) {
     // wide rows in vector form: staged in `vsmem` (kTransVSmemBytes)
     switch (g.esize) {
@@ -1433,14 +1170,6 @@ __device__ MLF_STAGED_ATTR void staged_tile(const Seg& g, uint32_t local, uint8_
       case 2: transpose_narrow_async<uint16_t>(g, local, image, vsmem); break;
       case 4: transpose_narrow_async<uint32_t>(g, local, image, vsmem); break;
       default: transpose_narrow_async<uint64_t>(g, local, image, vsmem); break;
-    }
-  } else if (DIR == MLF_PACK && g.kind == kTranspose && g.d != 0 && g.reserved == 0) {
-    // narrow transposed rows: tensor side read in 16-byte granules
-    switch (g.esize) {
-      case 1: transpose_narrow_granules<uint8_t>(g, local, image, tsmem); break;
-      case 2: transpose_narrow_granules<uint16_t>(g, local, image, tsmem); break;
-      case 4: transpose_narrow_granules<uint32_t>(g, local, image, tsmem); break;
-      default: transpose_narrow_granules<uint64_t>(g, local, image, tsmem); break;
     }
   } else if (g.kind == kTranspose) {
     switch (g.esize) {
@@ -1779,8 +1508,6 @@ __global__ void mlf_wait_selftest_kernel(uint64_t budget_ns, int32_t* __restrict
 
 constexpr size_t kBulkDynSmem = (size_t)mlf::kStages * mlf::kSlotBytes;
 static_assert(kTransVSmemBytes <= (int)mlf::kSlotBytes, "the vector-form transpose stages through one ring slot");
-static_assert(2 * 128 * 256 <= (int)kBulkDynSmem, "the asynchronous transpose uses the ring as two 32 KiB stages");
-static_assert(2 * kTransACarryBytes + 2 * kTransAL <= kTransSmemBytes, "carries and shift tables fit the static staging area");
 static_assert(kTransMStagingOff + TransM<2>::kCols * TransM<2>::kPitch <= (int)kBulkDynSmem &&
                   kTransMStagingOff + TransM<4>::kCols * TransM<4>::kPitch <= (int)kBulkDynSmem,
               "matrix form: two stages and the staging area fit the ring");
@@ -1859,7 +1586,6 @@ int wide_transpose_form() {
     const char* v = getenv("MLF_TRANSPOSE_FORM");
     const std::string want = v ? v : "";
     if (want == "element") return 0;
-    if (want == "async") return 3;
     if (want == "vector") return 2;
     return 4;
   }();
@@ -1895,10 +1621,11 @@ bool matrix_form_eligible(uint32_t esize, uint64_t tensor_ptr, const Canon& c, i
   return true;
 }
 
-// `wide_form`: tile geometry of wide TRANSPOSE boxes: 0 element-wise, 2 vector form, 3 asynchronous
-// form, 4 matrix form for 16- and 32-bit elements (cp.async-fed where every tensor row starts on a
-// 16-byte boundary, register-fed with a shift elsewhere) and vector form for the other element
-// sizes (all but 0 only exist in the bulk kernels, for the pack direction).
+// `wide_form`: tile geometry of TRANSPOSE boxes: 0 element-wise, 2 vector form, 4 matrix form for
+// 16- and 32-bit elements (cp.async-fed by granules where every tensor row starts on a 16-byte
+// boundary, by words where on a 4-byte boundary, register-fed with a shift elsewhere) and vector
+// form for the other element sizes; with 2 and 4 narrow rows take the pipelined form (all but 0
+// only exist in the bulk kernels, for the pack direction).
 int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int wide_form, Seg* seg_out, uint64_t* ntile_out,
                      uint64_t* payload_out, uint64_t* extent_out) {
   *ntile_out = 0;
@@ -2036,7 +1763,10 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
         const uint64_t per_row = row_cap / esize;
         const uint64_t row_bytes = (uint64_t)c.shape[last] * esize;
         uint64_t tc, tl;
-        if (row_bytes < row_cap && (uint64_t)c.is[cdim] == row_bytes) {
+        // The pipelined narrow form takes rows of up to 127 elements (its bound on granules per
+        // sub-tile): 32- and 64-bit rows too short to fill one 128-row stage of the wide forms.
+        const bool narrow = row_bytes < row_cap || (wide_form != 0 && esize >= 4 && c.shape[last] <= kNarrowAMaxRow);
+        if (narrow && (uint64_t)c.is[cdim] == row_bytes) {
           // short image rows lying back to back: a sub-tile is as many whole rows as fit the staging area
           g.d = (uint32_t)std::max<uint64_t>(1, (uint64_t)trans_narrow_bytes(esize) / row_bytes);
           if (wide_form != 0) g.reserved = 7;  // pack plans of the bulk kernels: pipelined form, longer tiles
@@ -2048,17 +1778,12 @@ int32_t plan_segment(const mlf_copy_desc& d, uint64_t i, int32_t direction, int 
           g.reserved = matrix_form_eligible(esize, d.tensor_ptr, c, cdim, 16) ? 4 : 6;  // granule-fed or word-fed
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
-        } else if (wide_form == 4 && (esize == 2 || esize == 4)) {
-          // 16- and 32-bit rows that start anywhere: matrix form behind a register-side shift
+        } else if (wide_form == 4 && esize == 2) {
+          // 16-bit rows on 2-byte boundaries (wider elements are at least word-aligned): matrix form behind a register-side shift
           const uint64_t cols = trans_ms_cols(esize);
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
           tl = ((uint64_t)c.shape[last] + (uint64_t)kTransML * kTransMSub - 1) / ((uint64_t)kTransML * kTransMSub);
           g.reserved = 5;
-        } else if (wide_form == 3) {
-          const uint64_t cols = trans_a_cols(esize);
-          tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;
-          tl = ((uint64_t)c.shape[last] + (uint64_t)kTransAL * kTransASub - 1) / ((uint64_t)kTransAL * kTransASub);
-          g.reserved = 3;
         } else if (wide_form == 2 || wide_form == 4) {
           const uint64_t cols = trans_v_cols(esize);
           tc = ((uint64_t)c.shape[cdim] + cols - 1) / cols;

@@ -950,6 +950,9 @@ def test_narrow_transposed_rows_across_tiles_and_alignments():
         (torch.int16, 127, 1500, 0, 0), (torch.int32, 19, 9000, 1, 1), (torch.int32, 3, 40000, 0, 0), (torch.int32, 63, 700, 2, 1),
         (torch.int64, 12, 30011, 1, 0), (torch.int64, 5, 20000, 0, 0), (torch.uint8, 7, 60013, 5, 2), (torch.uint8, 100, 5000, 9, 7),
         (torch.int16, 8, 33, 0, 0), (torch.int32, 2, 1, 0, 0),
+        # 32- and 64-bit rows of up to 127 elements take the same form
+        (torch.int32, 92, 3000, 0, 0), (torch.int32, 127, 900, 3, 1), (torch.int64, 100, 700, 1, 1), (torch.int64, 127, 300, 0, 0),
+        (torch.int32, 128, 600, 0, 0),
     ]:
         views.append(base(n_l, n_c + off + extra, dtype)[:, off : off + n_c].t())
     views.append(torch.randint(0, 250, (37, 11, 700), generator=g, dtype=torch.int64).to(torch.int16).cuda().transpose(1, 2))  # batched
