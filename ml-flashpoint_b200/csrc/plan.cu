@@ -256,8 +256,8 @@ __device__ __noinline__ void transpose_tile_v(const Seg& g, uint32_t local, uint
 }
 
 // cp.async and shared-memory helpers of the staged transposes.
-// Shared-memory accesses by 32-bit shared-window address (mlf::smem_addr): pointers that reach a
-// non-inlined tile function are generic, and generic loads and stores cost 64-bit address arithmetic.
+// Shared-memory accesses by 32-bit shared-window address (mlf::smem_addr): the staged transposes
+// compute many addresses per byte moved, and these keep that arithmetic in 32 bits.
 __device__ __forceinline__ void sts_b8(uint32_t a, uint32_t v) { asm volatile("st.shared.b8 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory"); }
 __device__ __forceinline__ void sts_b16(uint32_t a, uint32_t v) { asm volatile("st.shared.b16 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory"); }
 __device__ __forceinline__ void sts_b32(uint32_t a, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
