@@ -19,9 +19,16 @@ pointer that was passed in. The receiving buffer is exported with CUDA IPC and o
 sender; peers inside one process exchange the raw device pointer instead.
 
 CUDA IPC works between processes of one host only. Peers on different hosts (or without a CUDA
-device) therefore fall back to streaming the object over the same TCP connection, straight from
-the sender's mapping into the receiver's ``<object>.tmp`` mapping, which is what the reference does
-for every transfer. ``MLFLASHPOINT_REPL_TRANSPORT`` = ``auto`` (default) | ``nvlink`` | ``tcp``.
+device) stream the object over TCP, straight from the sender's mapping into the receiver's
+``<object>.tmp`` mapping, which is what the reference does for every transfer, and in the
+reference's own wire format (``wire.py``; protocol.h:32-72): a rank running this service can
+replicate to, and retrieve from, a rank running the reference's service and the other way round.
+Gets always travel in that format (request, ack, and the holder pushing the object back to the
+requester's listener); the push itself, like every put, goes over NVLink when the destination is a
+CUDA rank of this host that answers this package's own opening message (``wire.NATIVE``, a message
+type the reference ignores). A peer that does not answer it within ``_HELLO_TIMEOUT_S`` is
+remembered as a reference peer. ``MLFLASHPOINT_REPL_TRANSPORT`` = ``auto`` (default) | ``nvlink`` |
+``tcp`` (``tcp``: the reference's wire format for everything, no opening message).
 """
 
 from __future__ import annotations
@@ -40,12 +47,24 @@ from typing import Callable, Dict, Optional, Tuple
 
 from ml_flashpoint import _native
 from ml_flashpoint.core.mlf_logging import get_logger
+from ml_flashpoint.replication.transfer_service import wire
 
 _LOGGER = get_logger(__name__)
 
 METADATA_SIZE = 4096
 _LEN = struct.Struct("<I")
 _MAX_MESSAGE = 1 << 20
+_HELLO_TIMEOUT_S = 3.0  # how long a peer may take to answer the native opening message
+_GET_TIMEOUT_S = 300.0  # how long a get waits for the holder's push after its request was acknowledged
+
+
+def _task_key_and_rank(wire_task_id: str) -> Tuple[str, int]:
+    """Task ids this service puts on the wire are ``<id>~<global rank>``; the reference's are bare
+    UUIDs. Returns the id and the rank (-1 for a reference peer)."""
+    key, sep, rank = wire_task_id.partition("~")
+    if sep and rank.lstrip("-").isdigit():
+        return key, int(rank)
+    return wire_task_id, -1
 
 
 class TransferResult:
@@ -202,6 +221,10 @@ class TransferService:
         self._port = -1
         self._lock = threading.Lock()
         self._pending: Dict[str, concurrent.futures.Future] = {}
+        self._gets: Dict[str, dict] = {}  # acknowledged gets waiting for the holder's push, by task id
+        self._wire_only: set = set()  # addresses that did not answer the native opening message
+        self._local_hosts: Dict[str, bool] = {}
+        self._connections: set = set()  # accepted connections being served
         self._inbound: Dict[int, _DeviceBuffer] = {}  # per source rank
         self._inbound_locks: Dict[int, threading.Lock] = {}
         self._retired: list = []  # outgrown landing buffers, kept until shutdown
@@ -219,8 +242,9 @@ class TransferService:
         """Binds the control socket and starts the workers. Returns the port, or -1 on failure.
 
         The CUDA device current on the calling thread becomes the service's device.
-        ``conn_pool_per_peer`` is accepted for signature compatibility; control connections are
-        short-lived and not pooled.
+        ``conn_pool_per_peer`` is accepted for signature compatibility; outgoing connections are
+        opened per transfer and not pooled (incoming ones may stay open between messages, as the
+        reference's pooled connections do).
         """
         try:
             if self._transport not in ("auto", "nvlink", "tcp"):
@@ -282,9 +306,19 @@ class TransferService:
             self._running = False
             pending = list(self._pending.values())
             self._pending.clear()
+            waiting_gets = list(self._gets.values())
+            connections = list(self._connections)
         for f in pending:
             if not f.done():
                 f.set_exception(RuntimeError("TransferService is shutting down"))
+        for entry in waiting_gets:
+            entry["error"] = RuntimeError("TransferService is shutting down")
+            entry["event"].set()
+        for conn in connections:  # wakes the threads serving them
+            try:
+                conn.shutdown(socket.SHUT_RDWR)
+            except OSError:
+                pass
         if self._accept_thread:
             self._accept_thread.join(timeout=2.0)
         if self._listener:
@@ -411,16 +445,84 @@ class TransferService:
                 self._opened_ipc[key] = int(out.value)
             return self._opened_ipc[key]
 
-    def _run_put(self, task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, exact_path: bool = False) -> None:
-        from ml_flashpoint.core import gpu_engine
+    def _is_local(self, host: str) -> bool:
+        """Whether ``host`` names this machine: only an address of a local interface can be bound."""
+        known = self._local_hosts.get(host)
+        if known is None:
+            try:
+                with socket.socket(socket.AF_INET, socket.SOCK_DGRAM) as probe:
+                    probe.bind((socket.gethostbyname(host), 0))
+                known = True
+            except OSError:
+                known = False
+            self._local_hosts[host] = known
+        return known
 
+    def _native_first(self, dest_address: str) -> bool:
+        """Puts open with this package's own negotiation when it can end in the NVLink transport: a
+        CUDA rank sending to a peer on this host that has not ignored the opening message before."""
+        if self._transport == "nvlink":
+            return True
+        if self._transport == "tcp" or not self._cuda or dest_address in self._wire_only:
+            return False
+        return self._is_local(_split_address(dest_address)[0])
+
+    def _run_put(self, task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, exact_path: bool = False) -> None:
         if data_size <= 0 or not data_ptr:
             raise RuntimeError("Empty buffer or null data_ptr: async_put needs a non-empty source")
+        if self._native_first(dest_address):
+            if self._put_native(task_id, data_ptr, data_size, dest_address, dest_object_id, exact_path):
+                return
+            if self._transport == "nvlink":
+                raise RuntimeError(f"the peer at {dest_address} does not answer the NVLink negotiation")
+        self._put_wire(f"{task_id}~{self._rank}", data_ptr, data_size, dest_address, dest_object_id, respond=exact_path)
+
+    def _put_wire(self, wire_task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, respond: bool) -> None:
+        """The reference's put (transfer_service.cpp:628-690), or with ``respond`` its answer to a get
+        (:838-915): header, the object's bytes from the host mapping, then the peer's ack."""
+        from ml_flashpoint.core import gpu_engine
+
+        with self._connect(dest_address) as sock:
+            self._mark("connection_acquired")
+            gpu_engine.wait_object_on_host(dest_object_id)  # a save of it may still be draining
+            sock.sendall(
+                wire.pack_header(
+                    wire.RESPOND_TO_GET_OBJ if respond else wire.PUT_OBJ, dest_obj_id=dest_object_id, obj_size=data_size,
+                    task_id=wire_task_id, source_address=self.address,
+                )
+            )
+            self._mark("header_sent")
+            source = (ctypes.c_ubyte * data_size).from_address(data_ptr)
+            sock.sendall(memoryview(source).cast("B"))
+            self._mark("data_sent")
+            self.last_put_stats = {"bytes": data_size, "hop_ms": None, "from_hbm_image": False, "transport": "tcp"}
+            answer = wire.recv_header(sock)
+        if answer.type == wire.ERROR:
+            raise RuntimeError(f"Received error from destination for '{dest_object_id}'")
+        if answer.type != wire.ACK:
+            raise RuntimeError(f"Received unexpected ACK (message type {answer.type}) for '{dest_object_id}'")
+
+    def _put_native(self, task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, exact_path: bool) -> bool:
+        """This package's own put: negotiated over the connection, carried by NVLink when both ends are
+        CUDA ranks of one host. Returns False when the peer does not answer the opening message."""
+        from ml_flashpoint.core import gpu_engine
+
         lib = _native.lib()
         if self._cuda:
             _native.check(lib.mlf_set_device(self._device))
         with self._connect(dest_address) as sock:
             self._mark("connection_acquired")
+            sock.sendall(wire.pack_header(wire.NATIVE, task_id=f"{task_id}~{self._rank}", source_address=self.address))
+            sock.settimeout(_HELLO_TIMEOUT_S)
+            try:
+                hello = _recv_msg(sock)
+                if hello.get("hello") != "mlf-b200":
+                    raise ValueError("not this package's greeting")
+            except (socket.timeout, ConnectionError, ValueError, AttributeError):
+                _LOGGER.info("peer %s does not answer the native opening message: using the reference's wire format for it", dest_address)
+                self._wire_only.add(dest_address)
+                return False
+            sock.settimeout(300.0)  # the peer answers only after draining the whole object to its file
             _send_msg(
                 sock,
                 {
@@ -441,13 +543,13 @@ class TransferService:
                 final = _recv_msg(sock)
                 if not final.get("ok"):
                     raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
-                return
+                return True
             peer = self._peer_pointer(reply)
             stream = self._stream
             twin = None if exact_path else gpu_engine.resident_image(dest_object_id, data_size - METADATA_SIZE)
             if reply.get("chunked"):
                 self._put_in_chunks(sock, reply, peer, twin, data_ptr, data_size, dest_object_id)
-                return
+                return True
             t0, t1 = ctypes.c_void_p(), ctypes.c_void_p()
             _native.check(lib.mlf_event_create(ctypes.byref(t0)))
             _native.check(lib.mlf_event_create(ctypes.byref(t1)))
@@ -507,6 +609,7 @@ class TransferService:
             final = _recv_msg(sock)
             if not final.get("ok"):
                 raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
+        return True
 
     def _put_in_chunks(self, sock, reply: dict, peer: int, twin, data_ptr: int, data_size: int, dest_object_id: str) -> None:
         """Sender side of a transfer whose receiver keeps a two-slot landing ring: chunk k goes into
@@ -586,14 +689,46 @@ class TransferService:
             raise RuntimeError(f"peer failed to store '{dest_object_id}': {final.get('error')}")
 
     def _run_get(self, task_id: str, remote_object_id: str, source_address: str, local_object_id: str) -> None:
-        with self._connect(source_address) as sock:
-            self._mark("connection_acquired")
-            _send_msg(sock, {"op": "get", "obj": remote_object_id, "dest_obj": local_object_id, "reply_to": self.address, "task": task_id, "src_rank": self._rank})
-            self._mark("header_sent")
-            reply = _recv_msg(sock)  # arrives once the peer has put the object into this service's file
+        """The reference's get (transfer_service.cpp:782-836): the request names this service's own
+        listener as destination; the holder acknowledges and then pushes the object there, which
+        completes the get (``_finish_get``)."""
+        entry = {"event": threading.Event(), "error": None}
+        with self._lock:
+            self._gets[task_id] = entry
+        try:
+            with self._connect(source_address) as sock:
+                self._mark("connection_acquired")
+                sock.sendall(
+                    wire.pack_header(
+                        wire.GET_OBJ, task_id=f"{task_id}~{self._rank}", source_obj_id=remote_object_id, dest_obj_id=local_object_id,
+                        source_address=source_address, dest_address=self.address,
+                    )
+                )
+                self._mark("header_sent")
+                answer = wire.recv_header(sock)
+            if answer.type == wire.ERROR:
+                raise RuntimeError(f"Received error message from peer: object '{remote_object_id}' is not held here")
+            if answer.type != wire.ACK:
+                raise RuntimeError(f"Received unexpected response (message type {answer.type}) for GET request")
+            deadline = time.monotonic() + _GET_TIMEOUT_S
+            while not entry["event"].wait(0.2):
+                if not self._running:
+                    raise RuntimeError("TransferService is shutting down")
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"the holder of '{remote_object_id}' acknowledged the get but sent nothing")
+            if entry["error"] is not None:
+                raise RuntimeError(f"get of '{remote_object_id}' failed while it was being received: {entry['error']}")
             self._mark("data_received")
-            if not reply.get("ok"):
-                raise RuntimeError(f"Received error message from peer for '{remote_object_id}': {reply.get('error')}")
+        finally:
+            with self._lock:
+                self._gets.pop(task_id, None)
+
+    def _finish_get(self, task_key: str, error) -> None:
+        with self._lock:
+            entry = self._gets.get(task_key)
+        if entry is not None:
+            entry["error"] = error
+            entry["event"].set()
 
     # ------------------------------------------------------------------ receiver side
     def _accept_loop(self) -> None:
@@ -605,28 +740,150 @@ class TransferService:
             except OSError:
                 return
             conn.settimeout(300.0)
-            try:
-                self._workers.submit(self._serve, conn)
-            except RuntimeError:
-                conn.close()
-                return
+            # a thread per connection, not a pool worker: the reference's service keeps its pooled
+            # connections open between messages, and each would pin a worker for as long
+            with self._lock:
+                self._connections.add(conn)
+            threading.Thread(target=self._serve, args=(conn,), name="mlf-xfer-serve", daemon=True).start()
 
     def _serve(self, conn: socket.socket) -> None:
-        with conn:
+        """Messages of one connection, one after the other, until the peer closes it."""
+        try:
+            with conn:
+                while self._running:
+                    try:
+                        header = wire.recv_header(conn, allow_eof=True)
+                    except socket.timeout:
+                        continue  # an idle pooled connection
+                    if header is None or not self._serve_message(conn, header):
+                        return
+        except (ConnectionError, OSError):
+            if self._running:
+                _LOGGER.warning("transfer service connection ended unexpectedly", exc_info=True)
+        finally:
+            with self._lock:
+                self._connections.discard(conn)
+
+    def _serve_message(self, conn: socket.socket, header: "wire.Header") -> bool:
+        """Handles one message; False when the connection cannot carry another one."""
+        if header.type in (wire.PUT_OBJ, wire.RESPOND_TO_GET_OBJ):
+            return self._serve_wire_receive(conn, header, respond=header.type == wire.RESPOND_TO_GET_OBJ)
+        if header.type == wire.GET_OBJ:
+            self._serve_wire_get(conn, header)
+            return True
+        if header.type == wire.ERROR:  # a holder that could not push what it had acknowledged
+            _LOGGER.error("error message received for task %s", header.task_id)
+            self._finish_get(_task_key_and_rank(header.task_id)[0], RuntimeError("Received error message"))
+            return True
+        if header.type == wire.ACK:
+            _LOGGER.error("unexpected ACK message received for task %s", header.task_id)
+            return True
+        if header.type != wire.NATIVE:
+            _LOGGER.error("message of unknown type %d: closing the connection", header.type)
+            return False
+        # this package's own negotiation: greet, then one JSON request and its exchange
+        request: dict = {}
+        try:
+            _send_msg(conn, {"hello": "mlf-b200"})
+            request = _recv_msg(conn)
+            if request.get("op") != "put_begin":
+                raise ValueError(f"unknown op {request.get('op')}")
+            self._serve_put(conn, request)
+            if request.get("exact_path") and request.get("task"):
+                self._finish_get(request["task"], None)  # the push a pending get of ours was waiting for
+        except Exception as e:
+            _LOGGER.exception("transfer service request failed")
+            if request.get("exact_path") and request.get("task"):
+                self._finish_get(request["task"], e)
             try:
-                request = _recv_msg(conn)
-                if request["op"] == "put_begin":
-                    self._serve_put(conn, request)
-                elif request["op"] == "get":
-                    self._serve_get(conn, request)
+                _send_msg(conn, {"ok": False, "error": str(e)})
+            except OSError:
+                pass
+        return False  # native connections carry one transfer
+
+    def _serve_wire_receive(self, conn: socket.socket, header: "wire.Header", respond: bool) -> bool:
+        """Receiver of the reference's put, or of the push that answers a get of ours
+        (transfer_service.cpp:702-780): ``<object>.tmp``, rename, ack."""
+        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+        task_key, source = _task_key_and_rank(header.task_id)
+
+        def refuse(error) -> None:
+            _LOGGER.error("receiving '%s' failed: %s", header.dest_obj_id, error)
+            if respond:
+                self._finish_get(task_key, error)
+            try:
+                conn.sendall(wire.pack_header(wire.ERROR, task_id=header.task_id))
+            except OSError:
+                pass
+
+        if header.obj_size <= 0 or not header.dest_obj_id:
+            refuse(ValueError(f"Invalid obj_size received: {header.obj_size}" if header.dest_obj_id else "empty dest_obj_id"))
+            return True  # no bytes follow such a header
+        final_path = header.dest_obj_id if respond else self._map_path(header.dest_obj_id, source)
+        tmp_path = final_path + ".tmp"
+        target = None
+        try:
+            os.makedirs(os.path.dirname(final_path) or ".", exist_ok=True)
+            target = BufferObject(tmp_path, header.obj_size, overwrite=True)
+            _recv_into(conn, memoryview(target))
+            target.close()
+            target = None
+            os.rename(tmp_path, final_path)
+        except BaseException as e:
+            if target is not None:
+                target.close()
+            try:
+                os.remove(tmp_path)  # never leave a partial object behind
+            except OSError:
+                pass
+            refuse(e)
+            if not isinstance(e, Exception):
+                raise
+            return False  # the rest of the object may still be in the connection
+        conn.sendall(wire.pack_header(wire.ACK, task_id=header.task_id))
+        if respond:
+            self._finish_get(task_key, None)
+        return True
+
+    def _serve_wire_get(self, conn: socket.socket, header: "wire.Header") -> None:
+        """Holder side of a get (transfer_service.cpp:975-1035): error when the object is not here,
+        else an ack at once and the push to the requester's listener from a worker."""
+        _, requester = _task_key_and_rank(header.task_id)
+        # the object itself, or the replica this service keeps on behalf of the asking rank
+        candidates = [header.source_obj_id, self._map_path(header.source_obj_id, requester)]
+        path = next((c for c in candidates if c and os.path.exists(c)), None)
+        if path is None or not header.dest_address or not header.dest_obj_id:
+            _LOGGER.error("get of '%s': object is not held here", header.source_obj_id)
+            conn.sendall(wire.pack_header(wire.ERROR, task_id=header.task_id))
+            return
+        conn.sendall(wire.pack_header(wire.ACK, task_id=header.task_id))
+        try:
+            self._workers.submit(self._respond_to_get, header, path)
+        except RuntimeError:  # shutting down
+            pass
+
+    def _respond_to_get(self, header: "wire.Header", path: str) -> None:
+        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+        task_key, requester = _task_key_and_rank(header.task_id)
+        try:
+            source = BufferObject(path)
+            try:
+                if requester >= 0 or "~" in header.task_id:
+                    # a requester running this package: a put to its exact path, over NVLink when it can be
+                    self._run_put(task_key, source.get_data_ptr(), source.get_capacity(), header.dest_address, header.dest_obj_id, exact_path=True)
                 else:
-                    _send_msg(conn, {"ok": False, "error": f"unknown op {request['op']}"})
-            except Exception as e:
-                _LOGGER.exception("transfer service request failed")
-                try:
-                    _send_msg(conn, {"ok": False, "error": str(e)})
-                except OSError:
-                    pass
+                    self._put_wire(header.task_id, source.get_data_ptr(), source.get_capacity(), header.dest_address, header.dest_obj_id, respond=True)
+            finally:
+                source.close()
+        except Exception:
+            _LOGGER.exception("pushing '%s' to %s for get %s failed", path, header.dest_address, header.task_id)
+            try:  # let the requester fail its get instead of waiting for the push
+                with self._connect(header.dest_address) as sock:
+                    sock.sendall(wire.pack_header(wire.ERROR, task_id=header.task_id))
+            except Exception:
+                pass
 
     def _serve_put(self, conn: socket.socket, request: dict) -> None:
         from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
@@ -793,19 +1050,4 @@ class TransferService:
             raise
         target.close()
         os.rename(tmp_path, final_path)
-        _send_msg(conn, {"ok": True})
-
-    def _serve_get(self, conn: socket.socket, request: dict) -> None:
-        from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
-
-        # the object itself, or the replica this service keeps on behalf of the asking rank
-        candidates = [request["obj"], self._map_path(request["obj"], int(request.get("src_rank", -1)))]
-        path = next((c for c in candidates if os.path.exists(c)), None)
-        if path is None:
-            raise FileNotFoundError(f"object '{request['obj']}' is not held here")
-        source = BufferObject(path)
-        try:
-            self._run_put(request.get("task", ""), source.get_data_ptr(), source.get_capacity(), request["reply_to"], request["dest_obj"], exact_path=True)
-        finally:
-            source.close()
         _send_msg(conn, {"ok": True})

@@ -1,4 +1,5 @@
 """The transfer service's TCP transport (peers on different hosts, or no GPU), on the CPU.
+(``test_transfer_wire_format.py`` checks the bytes on the wire against the reference's format.)
 
 Mirrors the reference's point-to-point service tests: two services on 127.0.0.1, put / get round
 trips, temporary file + rename on the receiver, failures surfacing on the future, shutdown failing
@@ -77,21 +78,17 @@ def test_failures_and_shutdown(pair, tmp_path):
 
 def test_receiver_discards_a_partial_object(pair, tmp_path):
     """A sender that dies in the middle of an object must not leave a file (or a .tmp) behind."""
-    import json
-    import struct
+    from ml_flashpoint.replication.transfer_service import wire
 
     _, b, replicas = pair
     host, port = b.address.split(":")
     with socket.create_connection((host, int(port))) as s:
-        msg = json.dumps({"op": "put_begin", "obj": "/c/step-1_ckpt/o_src5.distcp", "size": 1 << 20, "src_rank": 5, "host": "elsewhere", "gpu": False}).encode()
-        s.sendall(struct.pack("<I", len(msg)) + msg)
-        (n,) = struct.unpack("<I", s.recv(4))
-        assert json.loads(s.recv(n))["transport"] == "tcp"
+        s.sendall(wire.pack_header(wire.PUT_OBJ, dest_obj_id="/c/step-1_ckpt/o_src5.distcp", obj_size=1 << 20, task_id="t~5"))
         s.sendall(b"x" * 1000)  # then the "host" goes away
     target = os.path.join(replicas, "src5", "c/step-1_ckpt/o_src5.distcp")
     deadline = threading.Event()
     for _ in range(100):
-        if not os.path.exists(target + ".tmp"):
+        if os.path.exists(os.path.dirname(target)) and not os.path.exists(target + ".tmp"):
             break
         deadline.wait(0.05)
     assert not os.path.exists(target) and not os.path.exists(target + ".tmp")
