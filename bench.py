@@ -353,10 +353,11 @@ def main() -> None:
     ap.add_argument("--cpu-baseline-budget-s", type=float, default=20.0, help="time budget of the CPU-baseline leg's saves")
     ap.add_argument("--workdir", default=None)
     ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
-    ap.add_argument("--probe", default=None, choices=[None, "host-link", "transpose"],
+    ap.add_argument("--probe", default=None, choices=[None, "host-link", "transpose", "footprint"],
                     help="host-link: plain copies between HBM and driver-allocated pinned memory in a process that "
                     "holds nothing else, rank by rank and all ranks at once; transpose: kernel-only pack / unpack "
-                    "timing of transposed views through the C ABI; each prints one JSON line and exits")
+                    "timing of transposed views through the C ABI; footprint: the pack kernel and the driver's own "
+                    "device-to-device copy on flat buffers of 1 to 12 GiB; each prints one JSON line and exits")
     ap.add_argument("--probe-case", default=None, help="transpose probe: run only the case with this name")
     ap.add_argument("--probe-feed-only", action="store_true", help="host-link probe: only the restore-feed part")
     ap.add_argument("--probe-alone-ranks", default=None,
@@ -367,6 +368,9 @@ def main() -> None:
         return
     if args.probe == "transpose":
         run_transpose_probe(args)
+        return
+    if args.probe == "footprint":
+        run_footprint_probe(args)
         return
     if args.impl == "mlf_b200":
         args.warmup = max(args.warmup, 3)  # fewer warm-up saves would time plan creation and buffer sizing
@@ -567,6 +571,8 @@ def run_transpose_probe(args) -> None:
         "narrow_fp32_rows_of_3": lambda: [rnd((3, 10 << 20), torch.float32).t()],
         "narrow_fp32_rows_of_19": lambda: [rnd((19, 1600000), torch.float32).t()],
         "narrow_int64_rows_of_12": lambda: [rnd((12, 1300000), torch.int64).t()],
+        # the benchmark's own shard (1 164 contiguous tensors, 14.05 GB) through one plan and one launch
+        "llama3_8b_shard": lambda: [t for _, t, _, _ in build_shard(0, device)],
         "microbench_transposed_wide_rows": lambda: microbench_views("wide"),
         "microbench_transposed_all": lambda: microbench_views("transposed"),
         "microbench_all_1024_tensors": lambda: microbench_views("all"),
@@ -586,6 +592,55 @@ def run_transpose_probe(args) -> None:
                 torch.cuda.empty_cache()
     print(json.dumps({"probe": "transpose", "form": os.environ.get("MLF_TRANSPOSE_FORM", "matrix"),
                       "unit": "GB/s of read + write bytes, kernel only, median of 4 launches", "results": results}))
+
+
+def run_footprint_probe(args) -> None:
+    """HBM copy rate against the size of the buffers: one flat tensor packed by ``mlf_plan_kernel_stream``
+    (one plan, one launch) beside the driver's device-to-device copy of the same bytes, for 1, 4 and
+    12 GiB, image and tensor aligned to one another and 7 bytes apart. CUDA events, L2 flushed between launches, median of 4. Read + write bytes per second.
+    Shows how much of the distance between a 14 GB shard and the copy peak measured on a small
+    buffer belongs to the footprint and how much to the kernel."""
+    from ml_flashpoint import _native
+    from ml_flashpoint.core.gpu_engine import _Plan, c_strides, fill_desc
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+    results = {}
+    for gib, offset in ((1, 0), (4, 0), (12, 0), (4, 7), (12, 7)):
+        nbytes = gib << 30
+        src = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        src.random_(0, 255)
+        image = torch.zeros(nbytes + 64, dtype=torch.uint8, device=device)
+        descs = (_native.CopyDesc * 1)()
+        fill_desc(descs[0], src.data_ptr(), offset, 1, src.shape, src.stride(), c_strides(src.shape))
+        plan = _Plan(descs, 1, _native.MLF_PACK)
+
+        def timed(fn):
+            times = []
+            for it in range(5):
+                flush.fill_(it)
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                fn()
+                t1.record()
+                torch.cuda.synchronize()
+                times.append(t0.elapsed_time(t1))
+            return sorted(times[1:])[2]
+
+        pack_ms = timed(lambda: plan.launch(image.data_ptr(), image.numel(), stream))
+        plan.status()
+        assert torch.equal(image[offset : offset + nbytes], src), "pack differs from the source"
+        image.zero_()
+        copy_ms = timed(lambda: image[offset : offset + nbytes].copy_(src))
+        results[f"flat_{gib}gib_image_offset_{offset}"] = {
+            "pack_kernel_gbs": round(2 * nbytes / 1e9 / (pack_ms / 1e3)),
+            "driver_d2d_copy_gbs": round(2 * nbytes / 1e9 / (copy_ms / 1e3)),
+        }
+        del plan, src, image
+        torch.cuda.empty_cache()
+    print(json.dumps({"probe": "footprint", "unit": "GB/s of read + write bytes, median of 4 launches", "results": results}))
 
 
 def run_host_link_probe(args) -> None:

@@ -73,10 +73,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 // Global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned),
 // completion counted on `bar`.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+#ifdef MLF_BULK_L2_EVICT_FIRST
+  // tuning variant: the source lines are read once, so they may leave L2 first
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_addr(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+#else
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)),
       "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
       : "memory");
+#endif
 }
 
 __device__ __forceinline__ uint4 lds_vec(const uint8_t* slot, uint32_t vec_index) {

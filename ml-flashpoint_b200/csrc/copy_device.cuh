@@ -26,8 +26,12 @@ __device__ __forceinline__ uint4 ld_vec_keep(const uint4* p) {
   asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
+// MLF_STORE_OP is a tuning knob of the build: the cache operator of the payload stores.
+#ifndef MLF_STORE_OP
+#define MLF_STORE_OP ".cs"
+#endif
 __device__ __forceinline__ void st_vec(uint4* p, const uint4& v) {
-  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  asm volatile("st.global" MLF_STORE_OP ".v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 // The vector held by the next higher lane (undefined for lane 31).
