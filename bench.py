@@ -360,6 +360,9 @@ def main() -> None:
                     "device-to-device copy on flat buffers of 1 to 12 GiB; each prints one JSON line and exits")
     ap.add_argument("--probe-case", default=None, help="transpose probe: run only the case with this name")
     ap.add_argument("--probe-feed-only", action="store_true", help="host-link probe: only the restore-feed part")
+    ap.add_argument("--probe-idle-ms", type=float, default=0.0,
+                    help="transpose probe: leave the GPU idle this long before every timed launch (a save's pack kernel "
+                    "starts after the previous object's host transfer, with the SMs idle)")
     ap.add_argument("--probe-alone-ranks", default=None,
                     help="host-link probe: comma-separated ranks measured one at a time (default: every rank)")
     args = ap.parse_args()
@@ -523,6 +526,9 @@ def run_transpose_probe(args) -> None:
             times = []
             for it in range(5):
                 flush.fill_(it)
+                if args.probe_idle_ms > 0:
+                    torch.cuda.synchronize()
+                    time.sleep(args.probe_idle_ms / 1e3)
                 t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 t0.record()
                 plan.launch(image.data_ptr(), image.numel(), stream)
