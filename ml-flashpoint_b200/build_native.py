@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUT = os.path.join(HERE, "ml_flashpoint", "libmlf_b200.so")
 SOURCES = ["buffer_object.cpp", "plan.cu", "movers.cu"]
-HEADERS = ["common.h", "copy_device.cuh", "bulk_pipeline.cuh"]
+HEADERS = ["common.h", "copy_device.cuh", "bulk_pipeline.cuh", "plan_seg.cuh", "transpose_tiles.cuh"]
 
 
 def _nvcc() -> str:
