@@ -353,11 +353,14 @@ def main() -> None:
     ap.add_argument("--cpu-baseline-budget-s", type=float, default=20.0, help="time budget of the CPU-baseline leg's saves")
     ap.add_argument("--workdir", default=None)
     ap.add_argument("--share-gpu", action="store_true", help="debug aid: all ranks use cuda:0 and gloo collectives")
-    ap.add_argument("--probe", default=None, choices=[None, "host-link", "transpose", "footprint"],
+    ap.add_argument("--probe", default=None, choices=[None, "host-link", "transpose", "footprint", "d2h-targets"],
                     help="host-link: plain copies between HBM and driver-allocated pinned memory in a process that "
                     "holds nothing else, rank by rank and all ranks at once; transpose: kernel-only pack / unpack "
                     "timing of transposed views through the C ABI; footprint: the pack kernel and the driver's own "
-                    "device-to-device copy on flat buffers of 1 to 12 GiB; each prints one JSON line and exits")
+                    "device-to-device copy on flat buffers of 1 to 12 GiB; d2h-targets: the device-to-host copy of a shard-sized "
+                    "buffer into driver-allocated pinned memory and into a page-locked tmpfs file, all ranks at once; each "
+                    "prints one JSON line and exits")
+    ap.add_argument("--probe-target-gb", type=float, default=14.0, help="d2h-targets probe: size of the large targets")
     ap.add_argument("--probe-case", default=None, help="transpose probe: run only the case with this name")
     ap.add_argument("--probe-feed-only", action="store_true", help="host-link probe: only the restore-feed part")
     ap.add_argument("--probe-idle-ms", type=float, default=0.0,
@@ -374,6 +377,9 @@ def main() -> None:
         return
     if args.probe == "footprint":
         run_footprint_probe(args)
+        return
+    if args.probe == "d2h-targets":
+        run_d2h_targets_probe(args)
         return
     if args.impl == "mlf_b200":
         args.warmup = max(args.warmup, 3)  # fewer warm-up saves would time plan creation and buffer sizing
@@ -647,6 +653,95 @@ def run_footprint_probe(args) -> None:
         del plan, src, image
         torch.cuda.empty_cache()
     print(json.dumps({"probe": "footprint", "unit": "GB/s of read + write bytes, median of 4 launches", "results": results}))
+
+
+def run_d2h_targets_probe(args) -> None:
+    """Device-to-host copy rate against what the host side of the copy is, in a fresh process per
+    rank, all ranks at once: (a) the 2 GiB driver-allocated pinned buffer of the host-link probe,
+    (b) a driver-allocated pinned buffer the size of a shard, (c) a tmpfs file of that size created and
+    page-locked the way the buffer pool does it (``BufferObject.register_cuda``), written by the same
+    ``mlf_memcpy_async`` a save uses, and (a) again while (b) and (c) still exist. Separates a limit of
+    the host's inbound-write path from a cost of large or file-backed page-locked targets."""
+    import ctypes
+
+    from ml_flashpoint import _native
+    from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
+
+    rank, local_rank, world_size = world()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world_size > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _native.lib()
+    small = 2 << 30
+    large = int(args.probe_target_gb * (1 << 30)) // 4096 * 4096
+    dev = torch.empty(large, dtype=torch.uint8, device=device)
+    dev.random_(0, 255)
+    stream = torch.cuda.Stream()
+    raw = ctypes.c_void_p(stream.cuda_stream)
+
+    def d2h(host_ptr, nbytes, reps):
+        best = 0.0
+        for _ in range(reps):
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0.record(stream)
+            _native.check(lib.mlf_memcpy_async(ctypes.c_void_p(host_ptr), ctypes.c_void_p(dev.data_ptr()), nbytes, _native.MLF_COPY_D2H, raw))
+            t1.record(stream)
+            stream.synchronize()
+            best = max(best, nbytes / 1e9 / (t0.elapsed_time(t1) / 1e3))
+        return best
+
+    rates, seconds = {}, {}
+    host_small = ctypes.c_void_p()
+    _native.check(lib.mlf_host_alloc(small, ctypes.byref(host_small)))
+    ctypes.memset(host_small, 1, small)
+    d2h(host_small.value, small, 1)
+    rates["pinned_2gib"] = d2h(host_small.value, small, 3)
+
+    t = time.perf_counter()
+    host_large = ctypes.c_void_p()
+    _native.check(lib.mlf_host_alloc(large, ctypes.byref(host_large)))
+    seconds["alloc_pinned_large"] = time.perf_counter() - t
+    d2h(host_large.value, large, 1)  # first touch
+    rates["pinned_large"] = d2h(host_large.value, large, 2)
+
+    shm_root = "/dev/shm" if os.path.isdir("/dev/shm") else "/tmp"
+    path = os.path.join(shm_root, f"mlf_probe_target_{os.getuid()}_{rank}.bin")
+    file_obj = None
+    try:
+        t = time.perf_counter()
+        file_obj = BufferObject(path, large, overwrite=True)
+        file_obj.register_cuda()
+        seconds["create_and_lock_tmpfs_file"] = time.perf_counter() - t
+        d2h(file_obj.get_data_ptr(), large, 1)
+        rates["locked_tmpfs_file_large"] = d2h(file_obj.get_data_ptr(), large, 2)
+        rates["pinned_2gib_again"] = d2h(host_small.value, small, 3)
+    finally:
+        if file_obj is not None:
+            file_obj.close()
+        if os.path.exists(path):
+            os.remove(path)
+    lib.mlf_host_free(host_large)
+    lib.mlf_host_free(host_small)
+    gathered = [None] * world_size
+    if world_size > 1:
+        dist.all_gather_object(gathered, (rates, seconds))
+    else:
+        gathered = [(rates, seconds)]
+    if rank == 0:
+        out = {
+            "probe": "d2h-targets", "n_gpus": world_size, "large_bytes": large, "host_cpus": os.cpu_count(),
+            "what": "cudaMemcpyAsync device to host, all ranks at once, fresh process per rank, best of the repetitions, GB/s per rank",
+            "results": {k: [round(g[0][k], 2) for g in gathered] for k in rates},
+            "aggregate_gbs": {k: round(sum(g[0][k] for g in gathered), 1) for k in rates},
+            "setup_seconds_rank0": {k: round(v, 2) for k, v in seconds.items()},
+        }
+        print(json.dumps(out))
+    if world_size > 1:
+        barrier()
+        dist.destroy_process_group()
 
 
 def run_host_link_probe(args) -> None:
