@@ -768,11 +768,13 @@ def run_host_link_probe(args) -> None:
     stream = torch.cuda.Stream()
     raw = ctypes.c_void_p(stream.cuda_stream)
 
-    def timed(fn, reps=3):
+    def timed(fn, reps=3, lockstep=False):
         best = 0.0
         for _ in range(reps):
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            if lockstep:
+                barrier()  # every repetition starts on all ranks together: ranks that drift apart would overstate a shared ceiling
             t0.record(stream)
             fn()
             t1.record(stream)
@@ -801,7 +803,7 @@ def run_host_link_probe(args) -> None:
                 alone = timed(fn)
             barrier()
         barrier()
-        together = timed(fn)  # everybody at once
+        together = timed(fn, lockstep=True)  # everybody at once
         barrier()
         gathered = [None] * world_size
         if world_size > 1:
