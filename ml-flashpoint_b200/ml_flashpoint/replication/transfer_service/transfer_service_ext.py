@@ -848,7 +848,7 @@ class TransferService:
 
     def _serve_wire_get(self, conn: socket.socket, header: "wire.Header") -> None:
         """Holder side of a get (transfer_service.cpp:975-1035): error when the object is not here,
-        else an ack at once and the push to the requester's listener from a worker."""
+        else an ack at once and the push to the requester's listener from a thread of its own."""
         _, requester = _task_key_and_rank(header.task_id)
         # the object itself, or the replica this service keeps on behalf of the asking rank
         candidates = [header.source_obj_id, self._map_path(header.source_obj_id, requester)]
@@ -858,10 +858,9 @@ class TransferService:
             conn.sendall(wire.pack_header(wire.ERROR, task_id=header.task_id))
             return
         conn.sendall(wire.pack_header(wire.ACK, task_id=header.task_id))
-        try:
-            self._workers.submit(self._respond_to_get, header, path)
-        except RuntimeError:  # shutting down
-            pass
+        # a thread of its own, not a pool worker: the workers of two services that get from each other
+        # may all be waiting for exactly these pushes
+        threading.Thread(target=self._respond_to_get, args=(header, path), name="mlf-xfer-respond", daemon=True).start()
 
     def _respond_to_get(self, header: "wire.Header", path: str) -> None:
         from ml_flashpoint.checkpoint_object_manager.buffer_object.buffer_object_ext import BufferObject
