@@ -139,3 +139,32 @@ def test_every_transfer_logs_the_result_line_the_reference_logs(pair, tmp_path):
     assert by_task[got.task_id].group(2, 4) == ("GET", "1")
     failed = [m for m in parsed if m.group(4) == "0"]
     assert len(failed) == 1 and "not held here" in failed[0].group(5)
+
+
+def test_services_that_get_from_each_other_with_every_worker_busy(tmp_path, monkeypatch):
+    """Two services with two workers each ask each other for four objects at once: every worker is a
+    get waiting for the other side's push. The pushes must not queue behind those workers."""
+    monkeypatch.setenv("MLFLASHPOINT_REPL_TRANSPORT", "tcp")
+    from ml_flashpoint.replication.transfer_service.transfer_service_ext import TransferService
+
+    a, b = TransferService(), TransferService()
+    assert a.initialize(0, threads=2, global_rank=0) > 0 and b.initialize(0, threads=2, global_rank=1) > 0
+    try:
+        held = {}
+        for owner in ("a", "b"):
+            for k in range(4):
+                path = tmp_path / owner / f"o{k}.distcp"
+                os.makedirs(path.parent, exist_ok=True)
+                held[(owner, k)] = (str(path), _object(path, 50000 + k, k))
+        futures = []
+        for k in range(4):
+            futures.append((("b", k), a.async_get(held[("b", k)][0], b.address, str(tmp_path / "a_got" / f"o{k}"))))
+            futures.append((("a", k), b.async_get(held[("a", k)][0], a.address, str(tmp_path / "b_got" / f"o{k}"))))
+        for key, f in futures:
+            assert f.result(timeout=60).success
+        for k in range(4):
+            assert open(tmp_path / "a_got" / f"o{k}", "rb").read() == held[("b", k)][1]
+            assert open(tmp_path / "b_got" / f"o{k}", "rb").read() == held[("a", k)][1]
+    finally:
+        a.shutdown()
+        b.shutdown()
