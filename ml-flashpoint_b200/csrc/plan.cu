@@ -613,7 +613,7 @@ bool use_bulk_kernel() {
   return bulk;
 }
 
-// Form of the wide transposes in pack plans: MLF_TRANSPOSE_FORM = matrix (default) | vector | async | element.
+// Form of the transposes in pack plans of the bulk kernels: MLF_TRANSPOSE_FORM = matrix (default) | vector | element.
 int wide_transpose_form() {
   static const int form = []() {
     const char* v = getenv("MLF_TRANSPOSE_FORM");
