@@ -565,6 +565,8 @@ def run_transpose_probe(args) -> None:
 
     cases = {
         "flat_bf16_1gib": lambda: [rnd((512 << 20,), torch.bfloat16)],
+        # the same flat tensor beside one small transposed view: the plan then runs as mlf_plan_kernel_bulk
+        "flat_bf16_1gib_in_a_bulk_plan": lambda: [rnd((512 << 20,), torch.bfloat16), rnd((64, 64), torch.bfloat16).t()],
         "uint8_square": lambda: [rnd((16384, 16384), torch.uint8).t()],
         "bf16_square_odd_pitch": lambda: [rnd((11585, 11585), torch.bfloat16).t()],
         "bf16_square_word_pitch": lambda: [rnd((11586, 11586), torch.bfloat16).t()],
