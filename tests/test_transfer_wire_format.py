@@ -235,3 +235,42 @@ def test_a_peer_that_ignores_the_native_opening_is_remembered_as_a_reference_pee
         assert any(h["type"] == 0x42 for h in peer.headers) and str(src) not in peer.objects
     finally:
         peer.close()
+
+
+def test_an_error_message_from_the_holder_fails_the_pending_get(service, tmp_path):
+    """A holder that acknowledged a get and then cannot push the object sends an error header with
+    the task id to the requester's listener (the reference fails the task on it,
+    transfer_service.cpp:608-611); the get must fail then, not wait for its timeout."""
+    svc, _ = service
+    listener = socket.socket()
+    listener.bind(("127.0.0.1", 0))
+    listener.listen(4)
+    holder = f"127.0.0.1:{listener.getsockname()[1]}"
+
+    def play_holder():
+        conn, _ = listener.accept()
+        with conn:
+            request = ref_parse(recv_exact(conn, HEADER_SIZE))
+            conn.sendall(ref_header(ACK, task_id=request["task_id"]))
+            with connect(request["dest_address"]) as back:
+                back.sendall(ref_header(ERROR, task_id=request["task_id"]))
+
+    thread = threading.Thread(target=play_holder, daemon=True)
+    thread.start()
+    with pytest.raises(RuntimeError, match="Received error message"):
+        svc.async_get("/held/elsewhere", holder, str(tmp_path / "never")).result(timeout=30)
+    thread.join(timeout=10)
+    listener.close()
+    assert not os.path.exists(tmp_path / "never")
+
+
+def test_a_message_of_unknown_type_ends_the_connection(service):
+    svc, _ = service
+    with connect(svc.address) as s:
+        s.sendall(bytes([99]) + b"\0" * (HEADER_SIZE - 1))
+        s.settimeout(10)
+        assert s.recv(1) == b""  # closed by the service, nothing sent
+    # the service itself keeps working
+    with connect(svc.address) as s:
+        s.sendall(ref_header(PUT, dest_obj_id="/after/unknown.distcp", obj_size=2) + b"ok")
+        assert ref_parse(recv_exact(s, HEADER_SIZE))["type"] == ACK
