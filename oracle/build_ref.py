@@ -28,7 +28,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REFERENCE_ROOT = os.environ.get("MLF_REFERENCE_ROOT", "/root/reference")
+# a checkout of the reference project next to this repository, unless MLF_REFERENCE_ROOT names another place
+DEFAULT_REFERENCE_ROOT = os.environ.get("MLF_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def reference_available(ref_root: str = DEFAULT_REFERENCE_ROOT) -> bool:
