@@ -27,7 +27,7 @@ Gets always travel in that format (request, ack, and the holder pushing the obje
 requester's listener); the push itself, like every put, goes over NVLink when the destination is a
 CUDA rank of this host that answers this package's own opening message (``wire.NATIVE``, a message
 type the reference ignores). A peer that does not answer it within ``_HELLO_TIMEOUT_S`` is
-remembered as a reference peer. ``MLFLASHPOINT_REPL_TRANSPORT`` = ``auto`` (default) | ``nvlink`` |
+taken for a reference peer for the next ``_WIRE_ONLY_S`` seconds. ``MLFLASHPOINT_REPL_TRANSPORT`` = ``auto`` (default) | ``nvlink`` |
 ``tcp`` (``tcp``: the reference's wire format for everything, no opening message).
 """
 
@@ -56,6 +56,7 @@ _LEN = struct.Struct("<I")
 _MAX_MESSAGE = 1 << 20
 _HELLO_TIMEOUT_S = 3.0  # how long a peer may take to answer the native opening message
 _GET_TIMEOUT_S = 300.0  # how long a get waits for the holder's push after its request was acknowledged
+_WIRE_ONLY_S = 60.0  # how long a peer that ignored the opening message is spoken to in the wire format before it is asked again
 
 
 def _task_key_and_rank(wire_task_id: str) -> Tuple[str, int]:
@@ -222,7 +223,7 @@ class TransferService:
         self._lock = threading.Lock()
         self._pending: Dict[str, concurrent.futures.Future] = {}
         self._gets: Dict[str, dict] = {}  # acknowledged gets waiting for the holder's push, by task id
-        self._wire_only: set = set()  # addresses that did not answer the native opening message
+        self._wire_only: Dict[str, float] = {}  # addresses that did not answer the native opening message, and when
         self._local_hosts: Dict[str, bool] = {}
         self._connections: set = set()  # accepted connections being served
         self._inbound: Dict[int, _DeviceBuffer] = {}  # per source rank
@@ -463,8 +464,11 @@ class TransferService:
         CUDA rank sending to a peer on this host that has not ignored the opening message before."""
         if self._transport == "nvlink":
             return True
-        if self._transport == "tcp" or not self._cuda or dest_address in self._wire_only:
+        if self._transport == "tcp" or not self._cuda:
             return False
+        ignored_at = self._wire_only.get(dest_address)
+        if ignored_at is not None and time.monotonic() - ignored_at < _WIRE_ONLY_S:
+            return False  # a busy peer of this package may have missed the greeting: it is asked again later
         return self._is_local(_split_address(dest_address)[0])
 
     def _run_put(self, task_id: str, data_ptr: int, data_size: int, dest_address: str, dest_object_id: str, exact_path: bool = False) -> None:
@@ -520,7 +524,7 @@ class TransferService:
                     raise ValueError("not this package's greeting")
             except (socket.timeout, ConnectionError, ValueError, AttributeError):
                 _LOGGER.info("peer %s does not answer the native opening message: using the reference's wire format for it", dest_address)
-                self._wire_only.add(dest_address)
+                self._wire_only[dest_address] = time.monotonic()
                 return False
             sock.settimeout(300.0)  # the peer answers only after draining the whole object to its file
             _send_msg(

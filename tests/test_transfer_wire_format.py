@@ -231,8 +231,14 @@ def test_a_peer_that_ignores_the_native_opening_is_remembered_as_a_reference_pee
         ro = BufferObject(str(src))
         assert svc._put_native("task", ro.get_data_ptr(), ro.get_capacity(), peer.address, str(src), False) is False
         ro.close()
-        assert peer.address in svc._wire_only and not svc._native_first(peer.address)
+        assert peer.address in svc._wire_only
         assert any(h["type"] == 0x42 for h in peer.headers) and str(src) not in peer.objects
+        # a CUDA rank would now use the wire format for this peer, and ask again once the mark has aged
+        monkeypatch.setattr(svc, "_cuda", True)
+        monkeypatch.setattr(svc, "_transport", "auto")
+        assert not svc._native_first(peer.address)
+        svc._wire_only[peer.address] -= mod._WIRE_ONLY_S + 1
+        assert svc._native_first(peer.address)
     finally:
         peer.close()
 
