@@ -280,3 +280,34 @@ def test_a_message_of_unknown_type_ends_the_connection(service):
     with connect(svc.address) as s:
         s.sendall(ref_header(PUT, dest_obj_id="/after/unknown.distcp", obj_size=2) + b"ok")
         assert ref_parse(recv_exact(s, HEADER_SIZE))["type"] == ACK
+
+
+def test_replication_manager_replicates_to_and_recovers_from_a_reference_peer(service, tmp_path, monkeypatch):
+    """The manager-level flow of a mixed fleet: rank 0 runs this package, its ring partner rank 1 the
+    reference's service. ``async_replicate`` leaves the whole object with the partner;
+    after the local copy is lost ``sync_bulk_retrieve`` brings it back, byte for byte."""
+    from ml_flashpoint.checkpoint_object_manager.checkpoint_object_manager import CheckpointObjectManager
+    from ml_flashpoint.core.checkpoint_id_types import CheckpointObjectId
+    from ml_flashpoint.replication import replication_manager as rm
+
+    svc, _ = service
+    peer = _ReferencePeer()
+    try:
+        monkeypatch.setattr(rm.dist, "get_rank", lambda: 0)
+        manager = rm.ReplicationManager()
+        manager.initialize(CheckpointObjectManager(), replication_transfer_service=svc,
+                           repl_strategy=rm.RingReplicationStrategy([svc.address, peer.address]))
+        com = CheckpointObjectManager()
+        oid = CheckpointObjectId(str(tmp_path / "step-7_ckpt" / "o_src0.distcp"))
+        payload = random.Random(11).randbytes(200003)
+        with com.acquire_buffer(oid, len(payload) + 8192) as w:
+            w.write(payload)
+        on_disk = open(str(oid), "rb").read()
+        futures = manager.async_replicate(com.get_buffer(oid))
+        assert len(futures) == 1 and futures[0].result(timeout=60).success
+        assert peer.objects[str(oid)] == on_disk
+        os.remove(str(oid))
+        assert manager.sync_bulk_retrieve(1, [oid], []) is True
+        assert open(str(oid), "rb").read() == on_disk
+    finally:
+        peer.close()
